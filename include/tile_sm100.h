@@ -1,0 +1,235 @@
+/* tile_sm100.h — C ABI of libtile_sm100, the sm_100a (B200) implementation of
+ * tile-rs's matmul / row-softmax / fused-attention hot path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an
+ * int32 status (TSM100_OK == 0) and never throws or aborts.  On failure a
+ * human-readable message is kept per thread and read with tsm100_last_error().
+ * There is no CPU fallback: without a CUDA device every compute and runtime
+ * entry point returns TSM100_ERR_NO_DEVICE.
+ *
+ * The comment on each declaration names the reference interface it stands in
+ * for (paths are relative to the tile-rs source tree).
+ */
+#ifndef TILE_SM100_H_
+#define TILE_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TSM100_VERSION 100 /* major*100 + minor */
+
+/* ---- status codes ------------------------------------------------------- */
+/* The reference reports failures as HalError variants
+ * (crates/tile_hal/src/error.rs:5-35); each code names the variant a binding
+ * should raise. */
+enum {
+  TSM100_OK = 0,
+  TSM100_ERR_INVALID = 1,     /* bad argument / unsupported shape -> KernelError   */
+  TSM100_ERR_NO_DEVICE = 2,   /* no CUDA device / driver          -> BackendNotAvailable */
+  TSM100_ERR_MEMORY = 3,      /* allocation or copy failed        -> MemoryError   */
+  TSM100_ERR_LAUNCH = 4,      /* kernel load or launch failed     -> KernelError   */
+  TSM100_ERR_STREAM = 5,      /* stream / event failure           -> StreamError   */
+  TSM100_ERR_RUNTIME = 6,     /* any other CUDA runtime error     -> RuntimeError  */
+  TSM100_ERR_TIMEOUT = 7,     /* a bounded device-side wait ran out -> RuntimeError */
+  TSM100_ERR_BUFFER = 8,      /* caller's output buffer too small (size returned) */
+  TSM100_ERR_EMIT = 9         /* MLIR not accepted by the cuda_sm100 target -> Err(String) */
+};
+
+/* ---- element types ------------------------------------------------------ */
+/* tile_hal's TileDtype (crates/tile_hal/src/kernel.rs:85-92) plus bf16, which
+ * tile_std spells only as u16 bit patterns (crates/tile_std/src/tile.rs:2593-2601). */
+enum {
+  TSM100_F32 = 0,
+  TSM100_F16 = 1,
+  TSM100_BF16 = 2
+};
+
+typedef struct tsm100_device_s* tsm100_device_t; /* opaque */
+typedef struct tsm100_module_s* tsm100_module_t; /* opaque */
+
+/* ---- library / errors --------------------------------------------------- */
+int32_t tsm100_version(void);
+/* Copies the calling thread's last error message (NUL-terminated, truncated to
+ * `cap`) and returns its full length.  Replaces the String carried by HalError
+ * (crates/tile_hal/src/error.rs:5-35) and by CodegenTarget::emit's Err
+ * (crates/tile_codegen/src/target.rs:64). */
+size_t tsm100_last_error(char* buf, size_t cap);
+
+/* ---- devices: crates/tile_hal/src/device.rs:25-57, cuda.rs:293-417 ------- */
+/* cuDeviceGetCount (cuda.rs:330-337 `device_count`). */
+int32_t tsm100_device_count(int32_t* count);
+/* CudaDevice::new (cuda.rs:300-328): binds the device's primary context; any
+ * number of devices may be open in one process, each call made with the right
+ * device current (the reference creates one context and never re-selects it). */
+int32_t tsm100_device_open(int32_t ordinal, tsm100_device_t* out);
+int32_t tsm100_device_close(tsm100_device_t dev); /* Drop for CudaDevice, cuda.rs:411-417 */
+int32_t tsm100_device_ordinal(tsm100_device_t dev, int32_t* ordinal); /* Device::ordinal */
+int32_t tsm100_device_name(tsm100_device_t dev, char* buf, size_t cap); /* Device::name   */
+/* Device::mem_info -> MemInfo{free,total} (device.rs:9-15, cuda.rs:373-380). */
+int32_t tsm100_mem_info(tsm100_device_t dev, size_t* free_bytes, size_t* total_bytes);
+/* Number of SMs; no counterpart in the reference (its grids are fixed by the emitter). */
+int32_t tsm100_device_sm_count(tsm100_device_t dev, int32_t* sms);
+/* Synchronises `stream`, then reads and clears the device's kernel status word:
+ * 0, or 0x1000|site when a kernel gave up one of its bounded waits (mbarrier,
+ * tensor-core completion).  The reference has no device-side error channel;
+ * check_cu (crates/tile_hal/src/cuda.rs:124-130) sees driver codes only. */
+int32_t tsm100_device_status(tsm100_device_t dev, void* stream, uint32_t* status);
+
+/* ---- streams and events: crates/tile_hal/src/stream.rs:7-10, cuda.rs:134-166 */
+/* A stream is a raw cudaStream_t carried as void*; NULL is the default stream,
+ * so a stream made by another runtime in the same process can be passed. */
+int32_t tsm100_stream_create(tsm100_device_t dev, void** stream);   /* Device::create_stream */
+int32_t tsm100_stream_destroy(tsm100_device_t dev, void* stream);    /* Drop for CudaStream   */
+int32_t tsm100_stream_synchronize(tsm100_device_t dev, void* stream); /* Stream::synchronize   */
+/* 1 if all work on the stream has finished, 0 if not; the reference has no query. */
+int32_t tsm100_stream_query(tsm100_device_t dev, void* stream, int32_t* done);
+/* Events time kernels on the device; the reference HAL has no timing facility. */
+int32_t tsm100_event_create(tsm100_device_t dev, void** event);
+int32_t tsm100_event_record(tsm100_device_t dev, void* event, void* stream);
+int32_t tsm100_event_synchronize(tsm100_device_t dev, void* event);
+int32_t tsm100_event_elapsed_ms(tsm100_device_t dev, void* start, void* stop, float* ms);
+int32_t tsm100_event_destroy(tsm100_device_t dev, void* event);
+
+/* ---- buffers: crates/tile_hal/src/buffer.rs:32-55, cuda.rs:170-218, :339-371 */
+int32_t tsm100_alloc(tsm100_device_t dev, size_t bytes, void** dptr); /* Device::alloc (cuMemAlloc) */
+int32_t tsm100_free(tsm100_device_t dev, void* dptr);                  /* Drop for CudaBuffer        */
+/* Page-locked host staging memory, so that copies can overlap kernels. */
+int32_t tsm100_host_alloc(size_t bytes, void** hptr);
+int32_t tsm100_host_free(void* hptr);
+/* DeviceBuffer::copy_from_host / copy_to_host (cuda.rs:181-199).  Ordered on
+ * `stream`; asynchronous with respect to the host when `host` is page-locked,
+ * otherwise the call returns once the host buffer may be reused / is filled. */
+int32_t tsm100_memcpy_h2d(tsm100_device_t dev, void* dst, const void* host, size_t bytes, void* stream);
+int32_t tsm100_memcpy_d2h(tsm100_device_t dev, void* host, const void* src, size_t bytes, void* stream);
+int32_t tsm100_memset(tsm100_device_t dev, void* dst, int32_t byte, size_t bytes, void* stream);
+
+/* ---- kernel modules: crates/tile_hal/src/kernel.rs:23-42, cuda.rs:222-289 - */
+/* KernelLauncher::load: `path` is a shared library built from the source
+ * tsm100_emit() produced ("device object file or shared library",
+ * kernel.rs:27-28). */
+int32_t tsm100_module_load(tsm100_device_t dev, const char* path, tsm100_module_t* out);
+int32_t tsm100_module_unload(tsm100_module_t mod);
+/* KernelLauncher::launch(name, LaunchGrid, args, stream) (kernel.rs:35-41,
+ * cuda.rs:245-288).  `blocks` is LaunchGrid::blocks = the number of per-block
+ * tiles of the #[tile_kernel] contract (crates/tile_std_macros/src/lib.rs:237-254);
+ * threads_per_block and shared_mem_bytes of LaunchGrid are chosen by the module
+ * and therefore ignored.  `args` are the kernel's global-memory pointers in
+ * declaration order. */
+int32_t tsm100_launch(tsm100_module_t mod, const char* name, uint32_t blocks, void** args,
+                      uint32_t nargs, void* stream);
+
+/* ---- operators on device memory ---------------------------------------- */
+/* Row softmax, y[r,:] = softmax(x[r,:]).  __tile_softmax_f32 / _f16
+ * (crates/tile_std/src/tile.rs:189-190, :2162-2163; wrappers :2295-2305,
+ * :2912-2920); semantics `linalg.softmax dimension(1)`
+ * (crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1305-1343).  Replaces the
+ * lowering at crates/rustc_codegen_tile/src/mlir_to_gpu.rs:1242-1336. */
+typedef struct {
+  int32_t dtype; /* TSM100_F32 | TSM100_F16 | TSM100_BF16 (storage; math is f32) */
+  int64_t rows;
+  int64_t cols;
+} tsm100_softmax_desc;
+int32_t tsm100_softmax(tsm100_device_t dev, const tsm100_softmax_desc* desc, const void* x, void* y,
+                       void* stream);
+
+/* GEMM, C[M,N] = A[M,K] * B, all row-major, C overwritten (zero-initialised
+ * accumulator).  __tile_matmul_f32 (tile.rs:192-193, :2307-2319),
+ * __tile_matmul_f16 (tile.rs:1982-1986, :2593-2601, :2666-2674) and, with
+ * b_transposed, __tile_matmul_transposed_* (tile.rs:2017-2031, :2682-2702;
+ * B stored [N,K]); semantics linalg.fill 0 + linalg.matmul
+ * (mlir_to_linalg.rs:1345-1393).  Replaces mlir_to_gpu.rs:1373-1397 (a TODO
+ * comment) and :1584-1622.  16-bit inputs accumulate in f32 on the tensor
+ * cores; out_dtype is the input dtype or TSM100_F32.  `batch` independent
+ * problems are stored back to back (the per-block tile stride of
+ * #[tile_kernel], tile_std_macros/src/lib.rs:237-254). */
+typedef struct {
+  int32_t dtype;     /* element type of A and B */
+  int32_t out_dtype; /* element type of C */
+  int32_t b_transposed;
+  int32_t batch;
+  int64_t m, n, k;
+} tsm100_gemm_desc;
+int32_t tsm100_gemm(tsm100_device_t dev, const tsm100_gemm_desc* desc, const void* a, const void* b,
+                    void* c, void* stream);
+
+/* Fused attention forward, O = softmax(Q K^T / sqrt(d)) V per (batch, head).
+ * Q,O: [batch][heads_q][seq][head_dim]; K,V: [batch][heads_kv][seq][head_dim].
+ * heads_q == heads_kv, causal = 0: __tile_attention_f32 (tile.rs:218-224,
+ * :2389-2410; mlir_to_linalg.rs:1781-1902).  causal = 1 adds
+ * __tile_causal_mask_f32 (tile.rs:1876-1877; mlir_to_linalg.rs:1191-1244)
+ * between the scale and the softmax.  heads_q > heads_kv is
+ * __tile_attention_gqa_* as the NVIDIA emitter defines it
+ * (mlir_to_gpu.rs:1624-1711): kv_head = h / (heads_q/heads_kv), always causal
+ * there.  Replaces mlir_to_gpu.rs:1976-1979 (unhandled) and :1624-1711.
+ * 16-bit Q/K/V use tensor cores with f32 softmax statistics. */
+typedef struct {
+  int32_t dtype; /* TSM100_BF16 | TSM100_F16 | TSM100_F32 */
+  int32_t causal;
+  int32_t batch;
+  int32_t heads_q;
+  int32_t heads_kv;
+  int32_t seq;
+  int32_t head_dim;
+} tsm100_attention_desc;
+int32_t tsm100_attention(tsm100_device_t dev, const tsm100_attention_desc* desc, const void* q,
+                         const void* k, const void* v, void* o, void* stream);
+
+/* ---- operators on HOST memory (upload, compute, download in one call) ---- */
+/* The path a tile_hal host program takes per kernel: alloc_from_slice ->
+ * launch -> copy_to_host (crates/tile_hal/src/cuda.rs:348-371, :245-288,
+ * :190-199), here chunked through page-locked staging so that copies in both
+ * directions overlap the kernel.  Pointers are ordinary host memory. */
+int32_t tsm100_softmax_host(tsm100_device_t dev, const tsm100_softmax_desc* desc, const void* x,
+                            void* y);
+int32_t tsm100_gemm_host(tsm100_device_t dev, const tsm100_gemm_desc* desc, const void* a,
+                         const void* b, void* c);
+int32_t tsm100_attention_host(tsm100_device_t dev, const tsm100_attention_desc* desc, const void* q,
+                              const void* k, const void* v, void* o);
+
+/* ---- sharding across GPUs ---------------------------------------------- */
+/* Splits `units` independent work units (softmax rows, GEMM batches or
+ * N-column blocks, attention (batch, kv-head) groups) over `world` ranks in
+ * contiguous blocks; the first units % world ranks get one more.  The reference
+ * is single-device (crates/tile_hal/src/backend.rs:95-112); the unit is the
+ * per-block tile of #[tile_kernel] (tile_std_macros/src/lib.rs:237-254). */
+int32_t tsm100_shard_range(int64_t units, int32_t world, int32_t rank, int64_t* first, int64_t* count);
+
+/* ---- cuda_sm100 CodegenTarget ------------------------------------------ */
+/* CodegenTarget::emit for the target named "cuda_sm100"
+ * (crates/tile_codegen/src/target.rs:57-65; supersedes convert_mlir_to_gpu,
+ * crates/rustc_codegen_tile/src/mlir_to_gpu.rs:62-99).  Pure and deterministic:
+ * reads `mlir` only.  Writes the CUDA translation unit (EmitOut.source, ext
+ * "cu") to `source`, and the entry kernel names (TargetMeta.kernel_names,
+ * target.rs:33-38) to `names`, separated by '\n'.  *source_len / *names_len
+ * receive the full lengths (without NUL); TSM100_ERR_BUFFER if a buffer is too
+ * small (call again with larger ones).  TSM100_ERR_EMIT for an empty module, a
+ * module with no `hacc.entry` kernel, or an intrinsic outside the target's
+ * scope — never a silent TODO comment. */
+int32_t tsm100_emit(const char* mlir, size_t mlir_len, char* source, size_t source_cap,
+                    size_t* source_len, char* names, size_t names_cap, size_t* names_len);
+const char* tsm100_target_name(void); /* CodegenTarget::name -> "cuda_sm100" */
+const char* tsm100_target_ext(void);  /* EmitOut.ext        -> "cu"         */
+
+/* ---- seeded synthetic inputs (host) ------------------------------------- */
+/* Counter-based generator shared by tests and benchmarks, so that the GPU and
+ * the CPU oracle read identical host buffers.  Element i of a stream with seed
+ * s is a function of (s, i) only.  No counterpart in the reference.
+ *   uniform: [-1, 1) from the top 24 bits of SplitMix64(s ^ i*0x9E3779B97F4A7C15)
+ *   normal : Box-Muller in f64 on the index pair (2p, 2p+1), times sigma
+ *   outliers: element i := value where SplitMix64(s ^ i*golden) % period == 0 */
+int32_t tsm100_fill_uniform_f32(float* dst, int64_t n, uint64_t seed, int64_t first_index);
+int32_t tsm100_fill_normal_f32(float* dst, int64_t n, uint64_t seed, int64_t first_index, double sigma);
+int32_t tsm100_plant_outliers_f32(float* dst, int64_t n, uint64_t seed, int64_t first_index,
+                                  uint32_t period, float value);
+int32_t tsm100_scale_f32(float* dst, int64_t n, float factor);
+int32_t tsm100_f32_to_bf16(const float* src, uint16_t* dst, int64_t n); /* arith.truncf, RNE */
+int32_t tsm100_bf16_to_f32(const uint16_t* src, float* dst, int64_t n); /* arith.extf */
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* TILE_SM100_H_ */

@@ -1,0 +1,353 @@
+// CPU oracle for the tile_std matmul / row-softmax / fused-attention hot path.
+//
+// TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA kernels are
+// compared with and the timed CPU baseline; nothing on the product path may
+// link, load or call it.
+//
+// PARITY UNPINNED: the reference holds no golden numeric vector, known-answer
+// test or data file for these operators (its tests assert emitted text only),
+// and its CPU executor for the linalg bridge is not part of its tree.  The
+// functions below therefore restate the arithmetic of the linalg operators the
+// reference's bridge emits, each citing the emitter lines it follows, and are
+// cross-checked against an independent numpy/float64 statement in the tests.
+//
+// Conventions: every matrix is row-major and contiguous.  bf16 values travel
+// as uint16_t bit patterns, widened exactly to f32 on load (arith.extf) and
+// narrowed with round-to-nearest-even on store (arith.truncf), as
+// crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1249-1303 lowers the casts.
+//
+// Build: see oracle/Makefile (g++ -O3 -march=x86-64-v3 -fopenmp -shared -fPIC).
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <limits>
+#include <vector>
+
+#if defined(_OPENMP)
+#include <omp.h>
+#endif
+
+namespace {
+
+inline float bf16_to_f32(uint16_t h) {
+  uint32_t u = static_cast<uint32_t>(h) << 16;
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+
+// Round-to-nearest-even narrowing; NaN stays NaN (quiet bit forced).
+inline uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((u >> 16) | 0x0040u);
+  uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7fffu + lsb;
+  return static_cast<uint16_t>(u >> 16);
+}
+
+// One softmax row: linalg.softmax dimension(1)
+// (crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1305-1343):
+//   m = max_j x_j ; e_j = exp(x_j - m) ; s = sum_j e_j ; y_j = e_j / s.
+template <typename Acc>
+inline void softmax_row(const float* x, float* y, int64_t n) {
+  Acc m = -std::numeric_limits<Acc>::infinity();
+  for (int64_t j = 0; j < n; ++j) m = x[j] > m ? static_cast<Acc>(x[j]) : m;
+  Acc s = 0;
+  if (sizeof(Acc) == 4) {
+    for (int64_t j = 0; j < n; ++j) {
+      float e = expf(x[j] - static_cast<float>(m));
+      y[j] = e;
+      s += e;
+    }
+    for (int64_t j = 0; j < n; ++j) y[j] = y[j] / static_cast<float>(s);
+  } else {
+    std::vector<double> e(n);
+    for (int64_t j = 0; j < n; ++j) {
+      e[j] = std::exp(static_cast<double>(x[j]) - static_cast<double>(m));
+      s += e[j];
+    }
+    for (int64_t j = 0; j < n; ++j) y[j] = static_cast<float>(e[j] / s);
+  }
+}
+
+// Attention for one (head) slice, restating the decomposition the bridge emits
+// for __tile_attention_f32 (mlir_to_linalg.rs:1781-1902): Kt = transpose(K);
+// S = Q*Kt (linalg.matmul, f32, zero-filled); S *= (float)(1/sqrt((double)D));
+// P = softmax rows; O = P*V.  With `causal`, the mask of
+// __tile_causal_mask_f32 (mlir_to_linalg.rs:1191-1244) is applied between the
+// scale and the softmax: S[i][j] = -inf where j > i.
+// Rows are independent, so the S x S score tile is produced one row at a time;
+// per element the sequence of f32 operations is the one written above.
+void attention_slice(const float* q, const float* k, const float* v, float* o,
+                     int64_t s_q, int64_t s_kv, int64_t d, bool causal) {
+  const float scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(d)));
+#pragma omp parallel
+  {
+    std::vector<float> sc(s_kv), p(s_kv), acc(d);
+#pragma omp for schedule(dynamic, 8)
+    for (int64_t i = 0; i < s_q; ++i) {
+      const float* qi = q + i * d;
+      const int64_t lim = causal ? (i + 1 < s_kv ? i + 1 : s_kv) : s_kv;
+      for (int64_t j = 0; j < lim; ++j) {
+        const float* kj = k + j * d;
+        float a = 0.f;
+        for (int64_t c = 0; c < d; ++c) a += qi[c] * kj[c];
+        sc[j] = a * scale;
+      }
+      // masked entries are -inf: exp(-inf - m) = 0 contributes nothing, so the
+      // softmax over the unmasked prefix equals the softmax over the full row.
+      softmax_row<float>(sc.data(), p.data(), lim);
+      for (int64_t c = 0; c < d; ++c) acc[c] = 0.f;
+      for (int64_t j = 0; j < lim; ++j) {
+        const float pj = p[j];
+        const float* vj = v + j * d;
+        for (int64_t c = 0; c < d; ++c) acc[c] += pj * vj[c];
+      }
+      std::memcpy(o + i * d, acc.data(), sizeof(float) * d);
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int orc_num_threads(void) {
+#if defined(_OPENMP)
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+void orc_bf16_to_f32(const uint16_t* src, float* dst, int64_t n) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) dst[i] = bf16_to_f32(src[i]);
+}
+
+void orc_f32_to_bf16(const float* src, uint16_t* dst, int64_t n) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) dst[i] = f32_to_bf16(src[i]);
+}
+
+// C[M,N] = A[M,K] * B[K,N]; linalg.fill 0 then linalg.matmul
+// (mlir_to_linalg.rs:1345-1393): C starts at zero and accumulates in f32, k
+// ascending for every (i,j).  The i-k-j loop order keeps that per-element
+// order while letting the compiler vectorise over j.
+// With b_transposed != 0, B is stored [N,K] (the __tile_matmul_transposed_*
+// weight layout, crates/tile_std/src/tile.rs:2017-2031).
+void orc_gemm_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                  int b_transposed) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < m; ++i) {
+    float* ci = c + i * n;
+    for (int64_t j = 0; j < n; ++j) ci[j] = 0.f;
+    if (!b_transposed) {
+      for (int64_t kk = 0; kk < k; ++kk) {
+        const float aik = a[i * k + kk];
+        const float* bk = b + kk * n;
+        for (int64_t j = 0; j < n; ++j) ci[j] += aik * bk[j];
+      }
+    } else {
+      for (int64_t j = 0; j < n; ++j) {
+        const float* bj = b + j * k;
+        float acc = 0.f;
+        for (int64_t kk = 0; kk < k; ++kk) acc += a[i * k + kk] * bj[kk];
+        ci[j] = acc;
+      }
+    }
+  }
+}
+
+// Same contraction with f64 accumulation: the "truth" the error bounds of the
+// f32 configuration are stated against.
+void orc_gemm_f64acc(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                     int b_transposed) {
+#pragma omp parallel
+  {
+    std::vector<double> row(n);
+#pragma omp for schedule(static)
+    for (int64_t i = 0; i < m; ++i) {
+      for (int64_t j = 0; j < n; ++j) row[j] = 0.0;
+      if (!b_transposed) {
+        for (int64_t kk = 0; kk < k; ++kk) {
+          const double aik = a[i * k + kk];
+          const float* bk = b + kk * n;
+          for (int64_t j = 0; j < n; ++j) row[j] += aik * static_cast<double>(bk[j]);
+        }
+      } else {
+        for (int64_t j = 0; j < n; ++j) {
+          const float* bj = b + j * k;
+          double acc = 0.0;
+          for (int64_t kk = 0; kk < k; ++kk) acc += static_cast<double>(a[i * k + kk]) * bj[kk];
+          row[j] = acc;
+        }
+      }
+      for (int64_t j = 0; j < n; ++j) c[i * n + j] = static_cast<float>(row[j]);
+    }
+  }
+}
+
+// 16-bit-input contraction (__tile_matmul_f16 family, tile.rs:1982-1986,
+// :2593-2601, :2666-2674; accumulate f32 per the comment at :2657-2664) on
+// bf16 bit patterns: inputs widened exactly, f32 accumulate, the unrounded f32
+// result written to c_f32 and, if c_bf16 != NULL, one RNE narrowing to bf16.
+void orc_gemm_bf16(const uint16_t* a, const uint16_t* b, float* c_f32, uint16_t* c_bf16,
+                   int64_t m, int64_t n, int64_t k, int b_transposed) {
+  std::vector<float> bf(static_cast<size_t>(k) * n);
+  orc_bf16_to_f32(b, bf.data(), k * n);
+#pragma omp parallel
+  {
+    std::vector<float> arow(k);
+#pragma omp for schedule(static)
+    for (int64_t i = 0; i < m; ++i) {
+      for (int64_t kk = 0; kk < k; ++kk) arow[kk] = bf16_to_f32(a[i * k + kk]);
+      float* ci = c_f32 + i * n;
+      for (int64_t j = 0; j < n; ++j) ci[j] = 0.f;
+      if (!b_transposed) {
+        for (int64_t kk = 0; kk < k; ++kk) {
+          const float aik = arow[kk];
+          const float* bk = bf.data() + kk * n;
+          for (int64_t j = 0; j < n; ++j) ci[j] += aik * bk[j];
+        }
+      } else {
+        for (int64_t j = 0; j < n; ++j) {
+          const float* bj = bf.data() + j * k;
+          float acc = 0.f;
+          for (int64_t kk = 0; kk < k; ++kk) acc += arow[kk] * bj[kk];
+          ci[j] = acc;
+        }
+      }
+      if (c_bf16)
+        for (int64_t j = 0; j < n; ++j) c_bf16[i * n + j] = f32_to_bf16(ci[j]);
+    }
+  }
+}
+
+// Row softmax, f32 (mlir_to_linalg.rs:1305-1343; the same five steps appear in
+// crates/tile_std/src/kernel_ops.rs:245-271 and mlir_to_gpu.rs:1266-1326).
+void orc_softmax_f32(const float* x, float* y, int64_t rows, int64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) softmax_row<float>(x + r * cols, y + r * cols, cols);
+}
+
+// f64-internal variant, used as the truth for the f32 error bound.
+void orc_softmax_f64acc(const float* x, float* y, int64_t rows, int64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) softmax_row<double>(x + r * cols, y + r * cols, cols);
+}
+
+// bf16-I/O row softmax: widen, f32 math, unrounded f32 to y_f32 (may be NULL)
+// and RNE bf16 to y_bf16 (may be NULL).
+void orc_softmax_bf16(const uint16_t* x, float* y_f32, uint16_t* y_bf16, int64_t rows,
+                      int64_t cols) {
+#pragma omp parallel
+  {
+    std::vector<float> xr(cols), yr(cols);
+#pragma omp for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+      for (int64_t j = 0; j < cols; ++j) xr[j] = bf16_to_f32(x[r * cols + j]);
+      softmax_row<float>(xr.data(), yr.data(), cols);
+      if (y_f32) std::memcpy(y_f32 + r * cols, yr.data(), sizeof(float) * cols);
+      if (y_bf16)
+        for (int64_t j = 0; j < cols; ++j) y_bf16[r * cols + j] = f32_to_bf16(yr[j]);
+    }
+  }
+}
+
+// Batched attention on f32 tensors: Q,O [batch][hq][s][d], K,V [batch][hkv][s][d].
+// hq == hkv gives __tile_attention_f32 per (batch, head) slice
+// (mlir_to_linalg.rs:1781-1902), non-causal unless `causal`.  hq > hkv is the
+// grouped-query form of __tile_attention_gqa_* as the NVIDIA emitter defines it
+// (mlir_to_gpu.rs:1624-1711): kv_head = h / (hq / hkv), scale 1/sqrt(d); that
+// intrinsic is always causal there, so callers pass causal = 1 for it.
+void orc_attention_f32(const float* q, const float* k, const float* v, float* o, int64_t batch,
+                       int64_t hq, int64_t hkv, int64_t s, int64_t d, int causal) {
+  const int64_t group = hq / hkv;
+  for (int64_t b = 0; b < batch; ++b)
+    for (int64_t h = 0; h < hq; ++h) {
+      const int64_t g = h / group;
+      attention_slice(q + ((b * hq + h) * s) * d, k + ((b * hkv + g) * s) * d,
+                      v + ((b * hkv + g) * s) * d, o + ((b * hq + h) * s) * d, s, s, d,
+                      causal != 0);
+    }
+}
+
+// bf16-input attention: Q,K,V widened to f32, all statistics and accumulation
+// in f32, unrounded f32 output to o_f32 and (if non-NULL) RNE bf16 to o_bf16.
+// `q_rows`/`q_row0` restrict the computed query rows to [q_row0, q_row0+q_rows)
+// of every head so that long sequences can be spot-checked; outputs are then
+// [batch][hq][q_rows][d].
+void orc_attention_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, float* o_f32,
+                        uint16_t* o_bf16, int64_t batch, int64_t hq, int64_t hkv, int64_t s,
+                        int64_t d, int causal, int64_t q_row0, int64_t q_rows) {
+  const int64_t group = hq / hkv;
+  std::vector<float> qf(static_cast<size_t>(q_rows) * d), kf(static_cast<size_t>(s) * d),
+      vf(static_cast<size_t>(s) * d), of(static_cast<size_t>(q_rows) * d);
+  const float scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(d)));
+  for (int64_t b = 0; b < batch; ++b)
+    for (int64_t h = 0; h < hq; ++h) {
+      const int64_t g = h / group;
+      orc_bf16_to_f32(q + ((b * hq + h) * s + q_row0) * d, qf.data(), q_rows * d);
+      if (h % group == 0 || h == 0) {
+        orc_bf16_to_f32(k + ((b * hkv + g) * s) * d, kf.data(), s * d);
+        orc_bf16_to_f32(v + ((b * hkv + g) * s) * d, vf.data(), s * d);
+      }
+#pragma omp parallel
+      {
+        std::vector<float> sc(s), p(s), acc(d);
+#pragma omp for schedule(dynamic, 8)
+        for (int64_t i = 0; i < q_rows; ++i) {
+          const int64_t gi = q_row0 + i;  // global query row decides the mask
+          const float* qi = qf.data() + i * d;
+          const int64_t lim = causal ? (gi + 1 < s ? gi + 1 : s) : s;
+          for (int64_t j = 0; j < lim; ++j) {
+            const float* kj = kf.data() + j * d;
+            float a = 0.f;
+            for (int64_t c = 0; c < d; ++c) a += qi[c] * kj[c];
+            sc[j] = a * scale;
+          }
+          softmax_row<float>(sc.data(), p.data(), lim);
+          for (int64_t c = 0; c < d; ++c) acc[c] = 0.f;
+          for (int64_t j = 0; j < lim; ++j) {
+            const float pj = p[j];
+            const float* vj = vf.data() + j * d;
+            for (int64_t c = 0; c < d; ++c) acc[c] += pj * vj[c];
+          }
+          std::memcpy(of.data() + i * d, acc.data(), sizeof(float) * d);
+        }
+      }
+      const int64_t off = ((b * hq + h) * q_rows) * d;
+      if (o_f32) std::memcpy(o_f32 + off, of.data(), sizeof(float) * q_rows * d);
+      if (o_bf16) orc_f32_to_bf16(of.data(), o_bf16 + off, q_rows * d);
+    }
+}
+
+// Parity metrics between a result y and the oracle r (n elements):
+//   out[0] = max|y-r|, out[1] = max|r|, out[2] = ||y-r||_F, out[3] = ||r||_F,
+//   out[4] = max over r_i >= floor of |y_i-r_i|/r_i (0 if none).
+void orc_compare_f32(const float* y, const float* r, int64_t n, double floor_r, double* out) {
+  double mad = 0, mr = 0, se = 0, sr = 0, mrel = 0;
+#pragma omp parallel for reduction(max : mad, mr, mrel) reduction(+ : se, sr) schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    const double yi = y[i], ri = r[i];
+    const double dlt = std::fabs(yi - ri);
+    mad = dlt > mad ? dlt : mad;
+    mr = std::fabs(ri) > mr ? std::fabs(ri) : mr;
+    se += dlt * dlt;
+    sr += ri * ri;
+    if (ri >= floor_r && floor_r > 0) {
+      const double rel = dlt / ri;
+      mrel = rel > mrel ? rel : mrel;
+    }
+  }
+  out[0] = mad;
+  out[1] = mr;
+  out[2] = std::sqrt(se);
+  out[3] = std::sqrt(sr);
+  out[4] = mrel;
+}
+
+}  // extern "C"

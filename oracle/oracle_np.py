@@ -1,0 +1,55 @@
+"""Independent float64 numpy statement of the same operators, for small cases.
+
+Used to cross-check the C++ oracle (which is what the CUDA kernels are compared
+with).  TEST INFRASTRUCTURE ONLY.  Each function cites the reference lines whose
+semantics it states.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def bf16_bits_to_f32(x: np.ndarray) -> np.ndarray:
+    """arith.extf (crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1249-1303)."""
+    return (x.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """arith.truncf, round-to-nearest-even."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    r = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return r.astype(np.uint16)
+
+
+def gemm(a: np.ndarray, b: np.ndarray, b_transposed: bool = False) -> np.ndarray:
+    """linalg.fill 0 + linalg.matmul (mlir_to_linalg.rs:1345-1393), in float64."""
+    b64 = b.astype(np.float64)
+    return a.astype(np.float64) @ (b64.T if b_transposed else b64)
+
+
+def softmax(x: np.ndarray) -> np.ndarray:
+    """linalg.softmax dimension(1) (mlir_to_linalg.rs:1305-1343), in float64."""
+    x = x.astype(np.float64)
+    e = np.exp(x - x.max(axis=-1, keepdims=True))
+    return e / e.sum(axis=-1, keepdims=True)
+
+
+def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, causal: bool) -> np.ndarray:
+    """transpose, matmul, scale 1/sqrt(D), [causal mask col > row -> -inf], softmax, matmul
+    (mlir_to_linalg.rs:1781-1902, :1191-1244); grouped KV heads with
+    kv_head = h // (hq // hkv) (crates/rustc_codegen_tile/src/mlir_to_gpu.rs:1657-1673).
+    q: [batch, hq, s, d]; k, v: [batch, hkv, s, d]."""
+    q, k, v = (t.astype(np.float64) for t in (q, k, v))
+    b, hq, s, d = q.shape
+    hkv = k.shape[1]
+    group = hq // hkv
+    out = np.empty_like(q)
+    scale = 1.0 / np.sqrt(float(d))
+    for bi in range(b):
+        for h in range(hq):
+            g = h // group
+            sc = (q[bi, h] @ k[bi, g].T) * scale
+            if causal:
+                sc = np.where(np.triu(np.ones((s, s), bool), 1), -np.inf, sc)
+            out[bi, h] = softmax(sc) @ v[bi, g]
+    return out

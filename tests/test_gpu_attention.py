@@ -1,0 +1,142 @@
+"""Fused attention forward on the GPU through the C ABI against the CPU oracle."""
+import numpy as np
+import pytest
+
+import util
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def run_attention(dev, capi, q, k, v, dtype, causal):
+    b, hq, s, d = q.shape
+    qd, kd, vd = (util.dev_tensor(torch, t) for t in (q, k, v))
+    od = torch.full_like(qd, 12345 if qd.dtype == torch.int16 else float("nan"))
+    dev.attention(dtype, b, hq, k.shape[1], s, d, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), od.data_ptr(),
+                  causal=causal, stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    assert dev.status() == 0
+    return od.cpu().numpy()
+
+
+def bf16_qkv(capi, b, hq, hkv, s, d, seed=401):
+    q = util.to_bf16(capi, util.gen_normal(capi, (b, hq, s, d), seed))
+    k = util.to_bf16(capi, util.gen_normal(capi, (b, hkv, s, d), seed + 1))
+    v = util.to_bf16(capi, util.gen_normal(capi, (b, hkv, s, d), seed + 2))
+    return q, k, v
+
+
+TC_CASES = [
+    (1, 1, 1, 128), (1, 1, 1, 256), (1, 2, 2, 512), (2, 2, 2, 384),   # 384: second query tile half empty
+    (1, 2, 2, 200), (1, 1, 1, 1000),                                    # ragged tails
+    (1, 8, 2, 512), (2, 4, 1, 768),                                     # grouped KV heads
+    (1, 2, 2, 2048),
+]
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("b,hq,hkv,s", TC_CASES)
+def test_attention_bf16_tensor_core(dev, pkg, oracle, b, hq, hkv, s, causal):
+    capi = pkg.capi
+    q, k, v = bf16_qkv(capi, b, hq, hkv, s, 128)
+    o = run_attention(dev, capi, q, k, v, capi.BF16, causal).view(np.uint16)
+    ref32, _ = oracle.attention_bf16(q, k, v, causal)
+    m = oracle.compare(oracle.bf16_to_f32(o), ref32)
+    assert m["max_abs"] <= util.BF16_MAX_ABS, m
+    assert m["rel_fro"] <= util.BF16_REL_FRO, m
+
+
+def test_attention_gqa_scaled_heads(dev, pkg, oracle):
+    """Per-head scales in [0.5, 2] on Q and K/V (the grouped-query configuration's law), causal."""
+    capi = pkg.capi
+    b, hq, hkv, s, d = 1, 8, 2, 1024, 128
+    qf = util.gen_normal(capi, (b, hq, s, d), 501)
+    kf = util.gen_normal(capi, (b, hkv, s, d), 502)
+    vf = util.gen_normal(capi, (b, hkv, s, d), 503)
+    uq = 0.5 + 0.75 * (util.gen_uniform(capi, (hq,), 504) + 1.0)
+    ukv = 0.5 + 0.75 * (util.gen_uniform(capi, (hkv,), 504, first=hq) + 1.0)
+    qf *= uq[None, :, None, None]
+    kf *= ukv[None, :, None, None]
+    vf *= ukv[None, :, None, None]
+    q, k, v = (util.to_bf16(capi, t) for t in (qf, kf, vf))
+    o = run_attention(dev, capi, q, k, v, capi.BF16, True).view(np.uint16)
+    ref32, _ = oracle.attention_bf16(q, k, v, True)
+    m = oracle.compare(oracle.bf16_to_f32(o), ref32)
+    assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, m
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_f32_fp32_pipe(dev, pkg, oracle, causal):
+    capi = pkg.capi
+    b, hq, hkv, s, d = 2, 4, 2, 100, 64
+    q = util.gen_normal(capi, (b, hq, s, d), 411)
+    k = util.gen_normal(capi, (b, hkv, s, d), 412)
+    v = util.gen_normal(capi, (b, hkv, s, d), 413)
+    o = run_attention(dev, capi, q, k, v, capi.F32, causal)
+    m = oracle.compare(o, oracle.attention_f32(q, k, v, causal))
+    assert m["rel_max"] <= 1e-5 and m["rel_fro"] <= 1e-5, m
+
+
+def test_attention_f16_and_other_head_dim(dev, pkg, oracle):
+    capi = pkg.capi
+    b, h, s, d = 1, 2, 96, 80  # head_dim 80: FP32-pipe kernel on 16-bit data
+    q, k, v = bf16_qkv(capi, b, h, h, s, d, seed=421)
+    o = run_attention(dev, capi, q, k, v, capi.BF16, True).view(np.uint16)
+    ref32, _ = oracle.attention_bf16(q, k, v, True)
+    m = oracle.compare(oracle.bf16_to_f32(o), ref32)
+    assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, m
+    # f16 inputs on the tensor-core kernel
+    qf, kf, vf = (util.gen_normal(capi, (1, 2, 256, 128), 430 + i) for i in range(3))
+    qh, kh, vh = (util.f32_to_f16_bits(t) for t in (qf, kf, vf))
+    oh = run_attention(dev, capi, qh, kh, vh, capi.F16, False).view(np.float16).astype(np.float32)
+    ref = oracle.attention_f32(*(t.view(np.float16).astype(np.float32) for t in (qh, kh, vh)), False)
+    m = oracle.compare(oh, ref)
+    assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, m
+
+
+def test_attention_bad_args(dev, pkg):
+    capi = pkg.capi
+    t = torch.zeros(1024, dtype=torch.int16, device="cuda:0")
+    p = t.data_ptr()
+    dev.attention(capi.BF16, 0, 1, 1, 128, 128, p, p, p, p)  # empty batch: no-op
+    with pytest.raises(pkg.hal.KernelError):
+        dev.attention(capi.BF16, 1, 3, 2, 128, 128, p, p, p, p)  # heads_q not a multiple of heads_kv
+    with pytest.raises(pkg.hal.KernelError):
+        dev.attention(capi.BF16, 1, 1, 1, 128, 512, p, p, p, p)  # head_dim too large
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_long_sequence_sampled_rows(dev, pkg, oracle, causal):
+    """seq 4096 (the attention configuration's length): sampled query rows per head against the oracle."""
+    capi = pkg.capi
+    b, hq, hkv, s, d = 1, 4, 4, 4096, 128
+    q, k, v = bf16_qkv(capi, b, hq, hkv, s, d)
+    o = run_attention(dev, capi, q, k, v, capi.BF16, causal).view(np.uint16)
+    for row0 in (0, 1920, 4032):
+        ref32, _ = oracle.attention_bf16(q, k, v, causal, q_row0=row0, q_rows=64)
+        m = oracle.compare(oracle.bf16_to_f32(np.ascontiguousarray(o[:, :, row0:row0 + 64])), ref32)
+        assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, (row0, m)
+
+
+def test_attention_gqa_16k_sampled_rows(dev, pkg, oracle):
+    """One KV group of the 16384-long grouped-query configuration (8 query heads, causal)."""
+    capi = pkg.capi
+    b, hq, hkv, s, d = 1, 8, 1, 16384, 128
+    q, k, v = bf16_qkv(capi, b, hq, hkv, s, d, seed=501)
+    o = run_attention(dev, capi, q, k, v, capi.BF16, True).view(np.uint16)
+    for row0 in (0, 8128, 16320):
+        ref32, _ = oracle.attention_bf16(q, k, v, True, q_row0=row0, q_rows=64)
+        m = oracle.compare(oracle.bf16_to_f32(np.ascontiguousarray(o[:, :, row0:row0 + 64])), ref32)
+        assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, (row0, m)
+
+
+def test_attention_host_path(dev, pkg, oracle):
+    capi = pkg.capi
+    b, hq, hkv, s, d = 2, 4, 2, 512, 128
+    q, k, v = bf16_qkv(capi, b, hq, hkv, s, d, seed=441)
+    o = np.zeros_like(q)
+    dev.attention_host(capi.BF16, b, hq, hkv, s, d, q.ctypes.data, k.ctypes.data, v.ctypes.data, o.ctypes.data,
+                       causal=True)
+    ref32, _ = oracle.attention_bf16(q, k, v, True)
+    m = oracle.compare(oracle.bf16_to_f32(o), ref32)
+    assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, m

@@ -1,0 +1,66 @@
+"""Helpers for the parity tests: seeded inputs from the library's generator,
+torch tensors as device memory, tolerances of the hot-path contract."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+# Tolerances (f32 GEMM and softmax: relative error <= 1e-5; 16-bit GEMM and
+# attention: max-abs <= 2e-2 and relative Frobenius <= 1e-2 against the
+# unrounded f32 oracle).
+F32_REL = 1e-5
+BF16_MAX_ABS = 2e-2
+BF16_REL_FRO = 1e-2
+
+
+def gen_uniform(capi, shape, seed, first=0):
+    out = np.empty(shape, np.float32)
+    assert capi.lib().tsm100_fill_uniform_f32(out.ctypes.data, out.size, seed, first) == 0
+    return out
+
+
+def gen_normal(capi, shape, seed, sigma=1.0, first=0):
+    out = np.empty(shape, np.float32)
+    assert capi.lib().tsm100_fill_normal_f32(out.ctypes.data, out.size, seed, first, float(sigma)) == 0
+    return out
+
+
+def plant_outliers(capi, arr, seed, period=100, value=20.0, first=0):
+    assert capi.lib().tsm100_plant_outliers_f32(arr.ctypes.data, arr.size, seed, first, period, float(value)) == 0
+    return arr
+
+
+def to_bf16(capi, arr):
+    arr = np.ascontiguousarray(arr, np.float32)
+    out = np.empty(arr.shape, np.uint16)
+    assert capi.lib().tsm100_f32_to_bf16(arr.ctypes.data, out.ctypes.data, arr.size) == 0
+    return out
+
+
+def softmax_input(capi, rows, cols, seed=201):
+    """3*N(0,1) with about 1 % of the positions set to +20 (the softmax configuration's law)."""
+    x = gen_normal(capi, (rows, cols), seed, sigma=3.0)
+    return plant_outliers(capi, x, seed + 1)
+
+
+def f32_to_f16_bits(arr):
+    return np.ascontiguousarray(arr, np.float32).astype(np.float16).view(np.uint16)
+
+
+def dev_tensor(torch, arr):
+    """Uploads a numpy array (uint16 arrays travel as int16) to cuda:0."""
+    if arr.dtype == np.uint16:
+        arr = arr.view(np.int16)
+    return torch.from_numpy(np.ascontiguousarray(arr)).to("cuda:0")
+
+
+def host_array(t, dtype=None):
+    a = t.cpu().numpy()
+    if dtype is not None:
+        a = a.view(dtype)
+    return a
+
+
+def cur_stream(torch):
+    return torch.cuda.current_stream().cuda_stream

@@ -1,0 +1,381 @@
+// Fused attention forward for sm_100a: O = softmax(Q K^T / sqrt(d)) V, flash
+// style (the S x S score tile is never written to memory).
+//
+// Semantics: __tile_attention_f32 (crates/tile_std/src/tile.rs:218-224) as the
+// linalg bridge decomposes it — transpose(K), matmul, scale by 1/sqrt(D), row
+// softmax, matmul (crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1781-1902);
+// `causal` applies __tile_causal_mask_f32 (mlir_to_linalg.rs:1191-1244: column >
+// row -> -inf) between the scale and the softmax; heads_q > heads_kv is the
+// grouped-query form of __tile_attention_gqa_* with kv_head = h / (heads_q /
+// heads_kv) (crates/rustc_codegen_tile/src/mlir_to_gpu.rs:1657-1673).  The
+// reference has no fused NVIDIA lowering: __tile_attention_f32 is unhandled
+// (mlir_to_gpu.rs:1976-1979) and the GQA form recomputes every q.k dot product
+// three times per output element (mlir_to_gpu.rs:1624-1711).
+//
+// Layout: Q,O [batch*heads_q][seq][128], K,V [batch*heads_kv][seq][128], 16-bit.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row tiles A and B
+// that take turns on the tensor core while the other is in its softmax.
+//   warp 0      TMA producer: Q once, then K_0,V_0,K_1,V_1,... (128 x 128 tiles,
+//               128-byte swizzle) through a 3-deep ring.  No multicast.
+//   warp 1      MMA issuer (one thread): S_g = Q_g K_j^T and O_g += P_g V_j with
+//               tcgen05.mma, S and O in tensor memory (4 x 128 columns).  V is
+//               consumed as an MN-major operand straight from its row-major form.
+//   warps 2..5  softmax of tile A, warps 6..9 of tile B: one thread per query
+//               row (TMEM lane), so row max and row sum need no shuffles.  The
+//               running max is only raised when it grows by more than 2^8 (the
+//               accumulator in TMEM is then rescaled); probabilities are written
+//               to shared memory as the 16-bit A operand of the PV product.
+// Roofline: tensor pipe; 4*seq^2*d flop per head (half of it when causal).
+#pragma once
+
+#include "ptx.cuh"
+
+namespace tsm100 {
+namespace attn {
+
+constexpr int kD = 128;          // head_dim
+constexpr int kBQ = 128;         // query rows per tile (two tiles per CTA)
+constexpr int kBKV = 128;        // key/value rows per step
+constexpr int kThreads = 320;
+constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: any 128 x 128 16-bit tile
+constexpr int kHalfBytes = kTileBytes / 2; // one 128-row x 64-column swizzled half
+constexpr int kRing = 3;
+constexpr int kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct alignas(8) Barriers {
+  uint64_t q_full;
+  uint64_t kv_full[kRing];
+  uint64_t kv_empty[kRing];
+  uint64_t s_full[2];
+  uint64_t p_ready[2];
+  uint64_t pv_done[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+// Q_A, Q_B, P_A, P_B, ring
+constexpr int kSmemBytes = (4 + kRing) * kTileBytes + sizeof(Barriers) + 1024;
+
+struct Params {
+  int32_t seq;
+  int32_t heads_q, heads_kv, batch;
+  int32_t causal;
+  int32_t q_blocks;        // ceil(seq / 256)
+  float scale_log2;        // (1/sqrt(d)) * log2(e)
+  uint32_t* status;
+};
+
+template <bool kIsBf16>
+__device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
+  if (kIsBf16) return ptx::pack_bf16x2(lo, hi);
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <bool kIsBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, uint16_t* __restrict__ o, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_q = smem;                         // 2 tiles
+  uint8_t* smem_p = smem + 2 * kTileBytes;        // 2 tiles
+  uint8_t* smem_kv = smem + 4 * kTileBytes;       // ring
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + (4 + kRing) * kTileBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  // Heaviest (latest) query blocks first when causal; heads of one KV group adjacent.
+  const int bh_total = p.batch * p.heads_q;
+  const int bh = blockIdx.x % bh_total;
+  const int qb_raw = blockIdx.x / bh_total;
+  const int qb = p.causal ? (p.q_blocks - 1 - qb_raw) : qb_raw;
+  const int b = bh / p.heads_q;
+  const int h = bh - b * p.heads_q;
+  const int kvh = b * p.heads_kv + h / (p.heads_q / p.heads_kv);
+  const int q0 = qb * 2 * kBQ;
+  const int n_kv_all = (p.seq + kBKV - 1) / kBKV;
+  // number of KV steps each tile needs (causal: up to and including its diagonal step)
+  const int n_a = p.causal ? min(n_kv_all, q0 / kBKV + 1) : n_kv_all;
+  const int n_b = p.causal ? min(n_kv_all, q0 / kBKV + 2) : n_kv_all;
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < kRing; ++s) {
+      ptx::mbar_init(&bars->kv_full[s], 1);
+      ptx::mbar_init(&bars->kv_empty[s], 1);
+    }
+    for (int g = 0; g < 2; ++g) {
+      ptx::mbar_init(&bars->s_full[g], 1);
+      ptx::mbar_init(&bars->p_ready[g], 128);
+      ptx::mbar_init(&bars->pv_done[g], 1);
+    }
+    bars->abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&bars->tmem_base, kTmemCols);
+    ptx::tmem_relinquish_alloc_permit();
+  }
+  ptx::tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  ptx::tcgen05_fence_after_thread_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t tmem_s = tmem_base;        // S_A at +0,   S_B at +128
+  const uint32_t tmem_o = tmem_base + 256;  // O_A at +256, O_B at +384
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_q);
+      ptx::prefetch_tensormap(&tmap_k);
+      ptx::prefetch_tensormap(&tmap_v);
+      ptx::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          ptx::tma_load_3d(smem_q + g * kTileBytes + c * kHalfBytes, &tmap_q, &bars->q_full, c * 64,
+                           q0 + g * kBQ, bh);
+      const int total = 2 * n_b;  // K_0, V_0, K_1, V_1, ...
+      for (int idx = 0; idx < total; ++idx) {
+        const int slot = idx % kRing;
+        const uint32_t phase = (idx / kRing) & 1u;
+        if (!ptx::mbar_wait(&bars->kv_empty[slot], phase ^ 1u, abort_flag, p.status, 11)) break;
+        ptx::mbar_arrive_expect_tx(&bars->kv_full[slot], kTileBytes);
+        const CUtensorMap* tm = (idx & 1) ? &tmap_v : &tmap_k;
+        const int row0 = (idx >> 1) * kBKV;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          ptx::tma_load_3d(smem_kv + slot * kTileBytes + c * kHalfBytes, tm, &bars->kv_full[slot], c * 64,
+                           row0, kvh);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBQ, kBKV, false, false, kIsBf16);
+      constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBQ, kD, false, true, kIsBf16);
+      constexpr uint64_t kmajor = ptx::make_smem_desc_base(16, 1024);
+      constexpr uint64_t v_mnmajor = ptx::make_smem_desc_base(kHalfBytes, 1024);
+      bool ok = ptx::mbar_wait(&bars->q_full, 0, abort_flag, p.status, 12);
+      ptx::tcgen05_fence_after_thread_sync();
+
+      auto wait_kv = [&](int idx) -> bool {
+        const bool r = ptx::mbar_wait(&bars->kv_full[idx % kRing], (idx / kRing) & 1u, abort_flag, p.status, 13);
+        ptx::tcgen05_fence_after_thread_sync();
+        return r;
+      };
+      // S_g = Q_g K^T : both operands K-major, K = head_dim in two 64-wide halves
+      auto issue_qk = [&](int g, int idx) {
+        const uint32_t qa = ptx::smem_u32(smem_q + g * kTileBytes);
+        const uint32_t ka = ptx::smem_u32(smem_kv + (idx % kRing) * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+          ptx::tcgen05_mma_f16_ss(tmem_s + g * 128, ptx::smem_desc(kmajor, qa + off),
+                                  ptx::smem_desc(kmajor, ka + off), idesc_qk, kk != 0 ? 1u : 0u);
+        }
+        ptx::tcgen05_commit(&bars->s_full[g]);
+      };
+      // O_g (+)= P_g V : P K-major (K = kv index), V MN-major (N = head_dim)
+      auto issue_pv = [&](int g, int idx, bool accumulate) {
+        const uint32_t pa = ptx::smem_u32(smem_p + g * kTileBytes);
+        const uint32_t va = ptx::smem_u32(smem_kv + (idx % kRing) * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kBKV / 16; ++kk) {
+          const uint32_t poff = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+          ptx::tcgen05_mma_f16_ss(tmem_o + g * 128, ptx::smem_desc(kmajor, pa + poff),
+                                  ptx::smem_desc(v_mnmajor, va + kk * 2048), idesc_pv,
+                                  (accumulate || kk != 0) ? 1u : 0u);
+        }
+        ptx::tcgen05_commit(&bars->pv_done[g]);
+      };
+      auto wait_p = [&](int g, int j) -> bool {
+        const bool r = ptx::mbar_wait(&bars->p_ready[g], j & 1u, abort_flag, p.status, 14 + g);
+        ptx::tcgen05_fence_after_thread_sync();
+        return r;
+      };
+
+      for (int j = 0; j < n_b && ok; ++j) {
+        const int k_idx = 2 * j, v_idx = 2 * j + 1;
+        if (j < n_a) {
+          if (!(ok = wait_kv(k_idx))) break;
+          issue_qk(0, k_idx);
+        }
+        if (j >= 1) {  // PV_B(j-1): last reader of V_{j-1}
+          if (!(ok = wait_kv(v_idx - 2))) break;
+          if (!(ok = wait_p(1, j - 1))) break;
+          issue_pv(1, v_idx - 2, j - 1 > 0);
+          ptx::tcgen05_commit(&bars->kv_empty[(v_idx - 2) % kRing]);
+        }
+        if (!(ok = wait_kv(k_idx))) break;
+        issue_qk(1, k_idx);  // last reader of K_j
+        ptx::tcgen05_commit(&bars->kv_empty[k_idx % kRing]);
+        if (j < n_a) {
+          if (!(ok = wait_kv(v_idx))) break;
+          if (!(ok = wait_p(0, j))) break;
+          issue_pv(0, v_idx, j > 0);
+        }
+      }
+      if (ok) {
+        const int v_idx = 2 * (n_b - 1) + 1;
+        if (wait_kv(v_idx) && wait_p(1, n_b - 1)) {
+          issue_pv(1, v_idx, n_b - 1 > 0);
+          ptx::tcgen05_commit(&bars->kv_empty[v_idx % kRing]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------ softmax / output ---------------------------
+    const int g = (warp - 2) >> 2;          // 0: tile A, 1: tile B
+    const int quad = warp & 3;              // TMEM lanes this warp may touch
+    const int r = quad * 32 + lane;         // row inside the tile == TMEM lane
+    const int n_g = g == 0 ? n_a : n_b;
+    const int qrow = q0 + g * kBQ + r;
+    const int limit = p.causal ? min(qrow, p.seq - 1) : (p.seq - 1);  // last visible column
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t ts = tmem_s + g * 128 + lane_base;
+    const uint32_t to = tmem_o + g * 128 + lane_base;
+    uint8_t* prow = smem_p + g * kTileBytes + r * 128;
+    const int sw = r & 7;
+    const float sl2 = p.scale_log2;
+
+    float m_used = -INFINITY;  // running max in raw score units
+    float l = 0.f;
+    bool alive = true;
+    for (int j = 0; j < n_g; ++j) {
+      bool ready = ptx::mbar_wait(&bars->s_full[g], j & 1u, abort_flag, p.status, 16 + g);
+      if (!__all_sync(0xffffffffu, ready)) {
+        alive = false;
+        break;
+      }
+      ptx::tcgen05_fence_after_thread_sync();
+      const int col0 = j * kBKV;
+      const bool masked = col0 + kBKV - 1 > limit;
+
+      // pass 1: row max of this step
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(ts + c * 32, v);
+        ptx::tmem_ld_wait();
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            mx = fmaxf(mx, (col0 + c * 32 + i <= limit) ? __uint_as_float(v[i]) : -INFINITY);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      }
+      const float m_new = fmaxf(m_used, mx);
+      bool need = false;
+      if (j == 0) {
+        m_used = m_new;
+      } else {
+        need = (m_new - m_used) * sl2 > kRescaleThreshold;
+        // PV of the previous step must have retired: it reads P and updates O.
+        ready = ptx::mbar_wait(&bars->pv_done[g], (j - 1) & 1u, abort_flag, p.status, 18 + g);
+        if (!__all_sync(0xffffffffu, ready)) {
+          alive = false;
+          break;
+        }
+        ptx::tcgen05_fence_after_thread_sync();
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = need ? ptx::ex2_approx((m_used - m_new) * sl2) : 1.0f;
+          if (need) m_used = m_new;
+          l *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32b_x32(to + c * 32, v);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            ptx::tmem_st_32x32b_x32(to + c * 32, v);
+          }
+          ptx::tmem_st_wait();
+        }
+      }
+
+      // pass 2: probabilities -> shared memory (K-major, 128-byte swizzle), row sum
+      const float ms = m_used * sl2;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(ts + c * 32, v);
+        ptx::tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = ptx::ex2_approx(fmaf(__uint_as_float(v[i]), sl2, -ms));
+          if (masked && (col0 + c * 32 + i > limit)) e = 0.f;
+          pr[i] = e;
+          l += e;
+        }
+        uint8_t* half_base = prow + (c >> 1) * kHalfBytes;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          uint4 w;
+          w.x = pack16x2<kIsBf16>(pr[8 * t + 0], pr[8 * t + 1]);
+          w.y = pack16x2<kIsBf16>(pr[8 * t + 2], pr[8 * t + 3]);
+          w.z = pack16x2<kIsBf16>(pr[8 * t + 4], pr[8 * t + 5]);
+          w.w = pack16x2<kIsBf16>(pr[8 * t + 6], pr[8 * t + 7]);
+          const int i16 = (c & 1) * 4 + t;
+          *reinterpret_cast<uint4*>(half_base + ((i16 ^ sw) << 4)) = w;
+        }
+      }
+      ptx::fence_proxy_async_smem();            // P visible to the tensor core's reads
+      ptx::tcgen05_fence_before_thread_sync();  // S reads and O writes ordered before the arrive
+      ptx::mbar_arrive(&bars->p_ready[g]);
+    }
+
+    if (alive && n_g > 0) {
+      bool ready = ptx::mbar_wait(&bars->pv_done[g], (n_g - 1) & 1u, abort_flag, p.status, 20 + g);
+      if (__all_sync(0xffffffffu, ready)) {
+        ptx::tcgen05_fence_after_thread_sync();
+        const float inv = 1.0f / l;
+        uint16_t* orow = o + (static_cast<int64_t>(bh) * p.seq + qrow) * kD;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(to + c * 32, v);
+          ptx::tmem_ld_wait();
+          if (qrow < p.seq) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              uint4 w;
+              w.x = pack16x2<kIsBf16>(__uint_as_float(v[8 * t + 0]) * inv, __uint_as_float(v[8 * t + 1]) * inv);
+              w.y = pack16x2<kIsBf16>(__uint_as_float(v[8 * t + 2]) * inv, __uint_as_float(v[8 * t + 3]) * inv);
+              w.z = pack16x2<kIsBf16>(__uint_as_float(v[8 * t + 4]) * inv, __uint_as_float(v[8 * t + 5]) * inv);
+              w.w = pack16x2<kIsBf16>(__uint_as_float(v[8 * t + 6]) * inv, __uint_as_float(v[8 * t + 7]) * inv);
+              reinterpret_cast<uint4*>(orow + c * 32)[t] = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  if (*abort_flag != 0u) {
+    const unsigned long long t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 1000000ull) {
+    }
+  }
+  ptx::tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tcgen05_fence_after_thread_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace attn
+}  // namespace tsm100

@@ -1,0 +1,236 @@
+// C-ABI operators: tsm100_softmax / tsm100_gemm / tsm100_attention on device
+// memory, and their *_host forms that take ordinary host pointers and overlap
+// upload, kernel and download in chunks (the alloc_from_slice -> launch ->
+// copy_to_host sequence of a tile_hal host program,
+// crates/tile_hal/src/cuda.rs:348-371, :245-288, :190-199).
+#include <algorithm>
+
+#include "common.hpp"
+#include "ops.cuh"
+
+using namespace tsm100;
+
+namespace {
+
+int32_t finish(int32_t st, const std::string& err) {
+  if (st != TSM100_OK) last_error_ref() = err;
+  return st;
+}
+
+// Streams, events and a grow-only device workspace for the *_host operators.
+int32_t ensure_pipe(tsm100_device_t dev, size_t dev_bytes) {
+  HostPipe& p = dev->pipe;
+  if (!p.ready) {
+    for (int i = 0; i < HostPipe::kSlots; ++i) {
+      TSM_CUDA(cudaStreamCreateWithFlags(&p.stream[i], cudaStreamNonBlocking), TSM100_ERR_STREAM);
+      TSM_CUDA(cudaEventCreateWithFlags(&p.done[i], cudaEventDisableTiming), TSM100_ERR_STREAM);
+    }
+    p.ready = true;
+  }
+  if (dev_bytes > p.dev_bytes) {
+    if (p.dev_buf) {
+      TSM_CUDA(cudaDeviceSynchronize(), TSM100_ERR_RUNTIME);
+      TSM_CUDA(cudaFree(p.dev_buf), TSM100_ERR_MEMORY);
+      p.dev_buf = nullptr;
+      p.dev_bytes = 0;
+    }
+    TSM_CUDA(cudaMalloc(&p.dev_buf, dev_bytes), TSM100_ERR_MEMORY);
+    p.dev_bytes = dev_bytes;
+  }
+  return TSM100_OK;
+}
+
+int32_t sync_pipe(tsm100_device_t dev) {
+  HostPipe& p = dev->pipe;
+  for (int i = 0; i < HostPipe::kSlots; ++i) TSM_CUDA(cudaStreamSynchronize(p.stream[i]), TSM100_ERR_STREAM);
+  uint32_t v = 0;
+  int32_t st = read_status(dev, p.stream[0], &v);
+  if (st != TSM100_OK) return st;
+  if (v != 0) return fail(TSM100_ERR_TIMEOUT, "a kernel gave up a bounded device-side wait (status 0x%x)", v);
+  return TSM100_OK;
+}
+
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" {
+
+int32_t tsm100_softmax(tsm100_device_t dev, const tsm100_softmax_desc* desc, const void* x, void* y, void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::softmax(&err, desc, x, y, stream), err);
+}
+
+int32_t tsm100_gemm(tsm100_device_t dev, const tsm100_gemm_desc* desc, const void* a, const void* b, void* c,
+                    void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::gemm(&err, desc, a, b, c, dev->status, stream), err);
+}
+
+int32_t tsm100_attention(tsm100_device_t dev, const tsm100_attention_desc* desc, const void* q, const void* k,
+                         const void* v, void* o, void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::attention(&err, desc, q, k, v, o, dev->status, stream), err);
+}
+
+// ---------------------------------------------------------------------------
+// host-memory operators
+// ---------------------------------------------------------------------------
+int32_t tsm100_softmax_host(tsm100_device_t dev, const tsm100_softmax_desc* desc, const void* x, void* y) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  if (!desc || !ops::dtype_valid(desc->dtype) || desc->rows < 0 || desc->cols < 0)
+    return fail(TSM100_ERR_INVALID, "softmax_host: bad descriptor");
+  if (desc->rows == 0 || desc->cols == 0) return TSM100_OK;
+  if (!x || !y) return fail(TSM100_ERR_INVALID, "softmax_host: null buffer");
+  std::lock_guard<std::mutex> lock(dev->mu);
+  const size_t row_bytes = static_cast<size_t>(desc->cols) * ops::dtype_size(desc->dtype);
+  constexpr size_t kChunkTarget = 32u << 20;
+  const int64_t rows_per_chunk = std::max<int64_t>(1, std::min<int64_t>(desc->rows, kChunkTarget / std::max<size_t>(row_bytes, 1)));
+  const size_t chunk_bytes = round_up(static_cast<size_t>(rows_per_chunk) * row_bytes, 256);
+  st = ensure_pipe(dev, chunk_bytes * 2 * HostPipe::kSlots);
+  if (st != TSM100_OK) return st;
+  HostPipe& p = dev->pipe;
+  std::string err;
+  int64_t row = 0;
+  for (int i = 0; row < desc->rows; ++i, row += rows_per_chunk) {
+    const int slot = i % HostPipe::kSlots;
+    cudaStream_t s = p.stream[slot];
+    char* din = static_cast<char*>(p.dev_buf) + static_cast<size_t>(slot) * 2 * chunk_bytes;
+    char* dout = din + chunk_bytes;
+    tsm100_softmax_desc d = *desc;
+    d.rows = std::min<int64_t>(rows_per_chunk, desc->rows - row);
+    const size_t bytes = static_cast<size_t>(d.rows) * row_bytes;
+    const size_t off = static_cast<size_t>(row) * row_bytes;
+    TSM_CUDA(cudaMemcpyAsync(din, static_cast<const char*>(x) + off, bytes, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
+    st = ops::softmax(&err, &d, din, dout, s);
+    if (st != TSM100_OK) return finish(st, err);
+    TSM_CUDA(cudaMemcpyAsync(static_cast<char*>(y) + off, dout, bytes, cudaMemcpyDeviceToHost, s), TSM100_ERR_MEMORY);
+  }
+  return sync_pipe(dev);
+}
+
+int32_t tsm100_gemm_host(tsm100_device_t dev, const tsm100_gemm_desc* desc, const void* a, const void* b, void* c) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  if (!desc || !ops::dtype_valid(desc->dtype) || !ops::dtype_valid(desc->out_dtype) || desc->m < 0 || desc->n < 0 ||
+      desc->k < 0 || desc->batch < 0)
+    return fail(TSM100_ERR_INVALID, "gemm_host: bad descriptor");
+  if (desc->m == 0 || desc->n == 0 || desc->batch == 0) return TSM100_OK;
+  if (!a || !b || !c) return fail(TSM100_ERR_INVALID, "gemm_host: null buffer");
+  std::lock_guard<std::mutex> lock(dev->mu);
+  const size_t es = ops::dtype_size(desc->dtype), os = ops::dtype_size(desc->out_dtype);
+  const size_t b_bytes = round_up(static_cast<size_t>(desc->k) * desc->n * es, 256);
+  std::string err;
+  if (desc->batch == 1) {
+    // B stays resident; A and C stream through in row blocks.
+    int64_t rows_per_chunk = std::max<int64_t>(128, (16ll << 20) / std::max<int64_t>(1, desc->k * static_cast<int64_t>(es)));
+    rows_per_chunk = std::min<int64_t>(desc->m, (rows_per_chunk + 127) / 128 * 128);
+    const size_t a_chunk = round_up(static_cast<size_t>(rows_per_chunk) * desc->k * es, 256);
+    const size_t c_chunk = round_up(static_cast<size_t>(rows_per_chunk) * desc->n * os, 256);
+    st = ensure_pipe(dev, b_bytes + (a_chunk + c_chunk) * HostPipe::kSlots);
+    if (st != TSM100_OK) return st;
+    HostPipe& p = dev->pipe;
+    char* db = static_cast<char*>(p.dev_buf);
+    TSM_CUDA(cudaMemcpyAsync(db, b, static_cast<size_t>(desc->k) * desc->n * es, cudaMemcpyHostToDevice, p.stream[0]), TSM100_ERR_MEMORY);
+    TSM_CUDA(cudaEventRecord(p.done[0], p.stream[0]), TSM100_ERR_STREAM);
+    int64_t row = 0;
+    for (int i = 0; row < desc->m; ++i, row += rows_per_chunk) {
+      const int slot = i % HostPipe::kSlots;
+      cudaStream_t s = p.stream[slot];
+      char* da = db + b_bytes + static_cast<size_t>(slot) * (a_chunk + c_chunk);
+      char* dc = da + a_chunk;
+      tsm100_gemm_desc d = *desc;
+      d.m = std::min<int64_t>(rows_per_chunk, desc->m - row);
+      TSM_CUDA(cudaMemcpyAsync(da, static_cast<const char*>(a) + static_cast<size_t>(row) * desc->k * es,
+                               static_cast<size_t>(d.m) * desc->k * es, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
+      TSM_CUDA(cudaStreamWaitEvent(s, p.done[0], 0), TSM100_ERR_STREAM);
+      st = ops::gemm(&err, &d, da, db, dc, dev->status, s);
+      if (st != TSM100_OK) return finish(st, err);
+      TSM_CUDA(cudaMemcpyAsync(static_cast<char*>(c) + static_cast<size_t>(row) * desc->n * os, dc,
+                               static_cast<size_t>(d.m) * desc->n * os, cudaMemcpyDeviceToHost, s), TSM100_ERR_MEMORY);
+    }
+    return sync_pipe(dev);
+  }
+  // batched: one problem per slot
+  const size_t a_bytes = round_up(static_cast<size_t>(desc->m) * desc->k * es, 256);
+  const size_t c_bytes = round_up(static_cast<size_t>(desc->m) * desc->n * os, 256);
+  const size_t unit = a_bytes + b_bytes + c_bytes;
+  st = ensure_pipe(dev, unit * HostPipe::kSlots);
+  if (st != TSM100_OK) return st;
+  HostPipe& p = dev->pipe;
+  for (int i = 0; i < desc->batch; ++i) {
+    const int slot = i % HostPipe::kSlots;
+    cudaStream_t s = p.stream[slot];
+    char* da = static_cast<char*>(p.dev_buf) + static_cast<size_t>(slot) * unit;
+    char* db = da + a_bytes;
+    char* dc = db + b_bytes;
+    const size_t an = static_cast<size_t>(desc->m) * desc->k * es, bn = static_cast<size_t>(desc->k) * desc->n * es,
+                 cn = static_cast<size_t>(desc->m) * desc->n * os;
+    tsm100_gemm_desc d = *desc;
+    d.batch = 1;
+    TSM_CUDA(cudaMemcpyAsync(da, static_cast<const char*>(a) + i * an, an, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
+    TSM_CUDA(cudaMemcpyAsync(db, static_cast<const char*>(b) + i * bn, bn, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
+    st = ops::gemm(&err, &d, da, db, dc, dev->status, s);
+    if (st != TSM100_OK) return finish(st, err);
+    TSM_CUDA(cudaMemcpyAsync(static_cast<char*>(c) + i * cn, dc, cn, cudaMemcpyDeviceToHost, s), TSM100_ERR_MEMORY);
+  }
+  return sync_pipe(dev);
+}
+
+int32_t tsm100_attention_host(tsm100_device_t dev, const tsm100_attention_desc* desc, const void* q, const void* k,
+                              const void* v, void* o) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  if (!desc || !ops::dtype_valid(desc->dtype) || desc->batch < 0 || desc->heads_q < 0 || desc->heads_kv < 0 ||
+      desc->seq < 0 || desc->head_dim < 0)
+    return fail(TSM100_ERR_INVALID, "attention_host: bad descriptor");
+  if (desc->batch == 0 || desc->heads_q == 0 || desc->seq == 0 || desc->head_dim == 0) return TSM100_OK;
+  if (desc->heads_kv <= 0 || desc->heads_q % desc->heads_kv != 0)
+    return fail(TSM100_ERR_INVALID, "attention_host: heads_q must be a positive multiple of heads_kv");
+  if (!q || !k || !v || !o) return fail(TSM100_ERR_INVALID, "attention_host: null buffer");
+  std::lock_guard<std::mutex> lock(dev->mu);
+  const size_t es = ops::dtype_size(desc->dtype);
+  const int group = desc->heads_q / desc->heads_kv;
+  const int64_t units = static_cast<int64_t>(desc->batch) * desc->heads_kv;  // (batch, kv head) groups
+  const size_t head_bytes = static_cast<size_t>(desc->seq) * desc->head_dim * es;
+  const size_t unit_q = head_bytes * group;
+  // enough units per chunk to move >= 16 MiB of Q and to fill the SMs
+  int64_t upc = std::max<int64_t>(1, (16ll << 20) / static_cast<int64_t>(unit_q));
+  upc = std::min<int64_t>(upc, units);
+  const size_t cq = round_up(unit_q * upc, 256), ckv = round_up(head_bytes * upc, 256);
+  const size_t per_slot = 2 * cq + 2 * ckv;
+  st = ensure_pipe(dev, per_slot * HostPipe::kSlots);
+  if (st != TSM100_OK) return st;
+  HostPipe& p = dev->pipe;
+  std::string err;
+  int64_t u0 = 0;
+  for (int i = 0; u0 < units; ++i, u0 += upc) {
+    const int slot = i % HostPipe::kSlots;
+    cudaStream_t s = p.stream[slot];
+    const int64_t nu = std::min<int64_t>(upc, units - u0);
+    char* dq = static_cast<char*>(p.dev_buf) + static_cast<size_t>(slot) * per_slot;
+    char* dk = dq + cq;
+    char* dv = dk + ckv;
+    char* dout = dv + ckv;
+    TSM_CUDA(cudaMemcpyAsync(dq, static_cast<const char*>(q) + u0 * unit_q, nu * unit_q, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
+    TSM_CUDA(cudaMemcpyAsync(dk, static_cast<const char*>(k) + u0 * head_bytes, nu * head_bytes, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
+    TSM_CUDA(cudaMemcpyAsync(dv, static_cast<const char*>(v) + u0 * head_bytes, nu * head_bytes, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
+    tsm100_attention_desc d = *desc;
+    d.batch = static_cast<int32_t>(nu);
+    d.heads_q = group;
+    d.heads_kv = 1;
+    st = ops::attention(&err, &d, dq, dk, dv, dout, dev->status, s);
+    if (st != TSM100_OK) return finish(st, err);
+    TSM_CUDA(cudaMemcpyAsync(static_cast<char*>(o) + u0 * unit_q, dout, nu * unit_q, cudaMemcpyDeviceToHost, s), TSM100_ERR_MEMORY);
+  }
+  return sync_pipe(dev);
+}
+
+}  // extern "C"

@@ -1,0 +1,349 @@
+// Host-side launch logic for the three operators: argument validation, kernel
+// selection, tensor-map construction, launch.  Header-only so that both the
+// library (capi_ops.cu) and the translation units the cuda_sm100 target emits
+// instantiate the same kernels with the same dispatch.
+//
+// Every function returns a TSM100_* status and, on failure, writes a message
+// to *err.  Nothing here allocates device memory or synchronises.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "../../include/tile_sm100.h"
+#include "attention_simt.cuh"
+#include "attention_tc.cuh"
+#include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+#include "softmax.cuh"
+
+namespace tsm100 {
+namespace ops {
+
+inline int32_t op_fail(std::string* err, int32_t code, const std::string& msg) {
+  if (err) *err = msg;
+  return code;
+}
+
+inline int32_t cuda_ok(std::string* err, cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return TSM100_OK;
+  const int32_t code = (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) ? TSM100_ERR_NO_DEVICE
+                                                                                      : TSM100_ERR_LAUNCH;
+  return op_fail(err, code, std::string(what) + " failed: " + cudaGetErrorString(e));
+}
+
+inline size_t dtype_size(int32_t dtype) { return dtype == TSM100_F32 ? 4 : 2; }
+inline bool dtype_valid(int32_t dtype) { return dtype == TSM100_F32 || dtype == TSM100_F16 || dtype == TSM100_BF16; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---------------------------------------------------------------------------
+// tensor maps
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline int32_t encode_fn(std::string* err, EncodeTiledFn* out) {
+  static EncodeTiledFn cached = nullptr;
+  if (!cached) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+      return op_fail(err, TSM100_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    cached = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  *out = cached;
+  return TSM100_OK;
+}
+
+// 16-bit elements, dims (x contiguous, y, z), strides in elements, box (box_x, box_y, 1),
+// 128-byte swizzle, out-of-range elements read as zero.
+inline int32_t make_tmap_16bit_3d(std::string* err, CUtensorMap* out, const void* base, uint64_t dim_x,
+                                  uint64_t dim_y, uint64_t dim_z, uint64_t stride_y, uint64_t stride_z,
+                                  uint32_t box_x, uint32_t box_y, bool is_bf16) {
+  EncodeTiledFn fn;
+  int32_t st = encode_fn(err, &fn);
+  if (st != TSM100_OK) return st;
+  cuuint64_t dims[3] = {dim_x, dim_y, dim_z};
+  cuuint64_t strides[2] = {stride_y * 2, stride_z * 2};  // bytes; dimension 0 is contiguous
+  cuuint32_t box[3] = {box_x, box_y, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if ((strides[0] & 15u) || (strides[1] & 15u) || !aligned16(base))
+    return op_fail(err, TSM100_ERR_INVALID, "tensor map needs a 16-byte aligned base and 16-byte-multiple strides");
+  CUresult r = fn(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[96];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed: CUresult %d", static_cast<int>(r));
+    return op_fail(err, TSM100_ERR_LAUNCH, buf);
+  }
+  return TSM100_OK;
+}
+
+inline int32_t sm_count(std::string* err, int* sms) {
+  static int cached[64] = {0};
+  int dev = 0;
+  int32_t st = cuda_ok(err, cudaGetDevice(&dev), "cudaGetDevice");
+  if (st != TSM100_OK) return st;
+  if (dev < 64 && cached[dev]) {
+    *sms = cached[dev];
+    return TSM100_OK;
+  }
+  int n = 0;
+  st = cuda_ok(err, cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
+  if (st != TSM100_OK) return st;
+  if (dev < 64) cached[dev] = n;
+  *sms = n;
+  return TSM100_OK;
+}
+
+// ---------------------------------------------------------------------------
+// softmax
+// ---------------------------------------------------------------------------
+template <typename T, int CHUNKS>
+inline cudaError_t launch_softmax_warp(const T* x, T* y, int64_t rows, int32_t cols, cudaStream_t s) {
+  constexpr int WARPS = 4;
+  const int64_t grid = (rows + WARPS - 1) / WARPS;
+  softmax::softmax_rows_warp<T, CHUNKS, WARPS><<<static_cast<unsigned>(grid), WARPS * 32, 0, s>>>(x, y, rows, cols);
+  return cudaGetLastError();
+}
+
+template <typename T>
+inline int32_t softmax_typed(std::string* err, const T* x, T* y, int64_t rows, int64_t cols, cudaStream_t s) {
+  constexpr int PV = softmax::Elem<T>::kPerVec;
+  const bool vec_ok = (cols % PV == 0) && aligned16(x) && aligned16(y);
+  const int64_t nvec = cols / PV;
+  cudaError_t e;
+  // a lane keeps at most 128 f32 values in registers: 32 vectors of 4, or 16 of 8
+  constexpr int kMaxChunks = PV == 4 ? 32 : 16;
+  if (vec_ok && nvec <= 32 * kMaxChunks && rows <= 4ll * 0x7fffffff) {
+    const int32_t c = static_cast<int32_t>(cols);
+    if (nvec <= 32 * 1) e = launch_softmax_warp<T, 1>(x, y, rows, c, s);
+    else if (nvec <= 32 * 2) e = launch_softmax_warp<T, 2>(x, y, rows, c, s);
+    else if (nvec <= 32 * 4) e = launch_softmax_warp<T, 4>(x, y, rows, c, s);
+    else if (nvec <= 32 * 8) e = launch_softmax_warp<T, 8>(x, y, rows, c, s);
+    else if (nvec <= 32 * 16) e = launch_softmax_warp<T, 16>(x, y, rows, c, s);
+    else e = launch_softmax_warp<T, kMaxChunks>(x, y, rows, c, s);
+    return cuda_ok(err, e, "softmax_rows_warp launch");
+  }
+  int sms = 0;
+  int32_t st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  constexpr int64_t kMaxBlockCols = 56 * 1024;  // 224 KiB of f32 in shared memory
+  if (vec_ok && cols <= kMaxBlockCols) {
+    constexpr int THREADS = 512;
+    const size_t smem = static_cast<size_t>(cols) * sizeof(float);
+    auto kern = softmax::softmax_rows_block<T, THREADS>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(softmax_rows_block)");
+    const int per_sm = static_cast<int>(std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / (smem + 1024))));
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(rows, static_cast<int64_t>(sms) * per_sm));
+    kern<<<grid, THREADS, smem, s>>>(x, y, rows, static_cast<int32_t>(cols));
+    return cuda_ok(err, cudaGetLastError(), "softmax_rows_block launch");
+  }
+  constexpr int THREADS = 512;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(rows, static_cast<int64_t>(sms) * 4));
+  softmax::softmax_rows_stream<T, THREADS><<<grid, THREADS, 0, s>>>(x, y, rows, cols);
+  return cuda_ok(err, cudaGetLastError(), "softmax_rows_stream launch");
+}
+
+inline int32_t softmax(std::string* err, const tsm100_softmax_desc* d, const void* x, void* y, void* stream) {
+  if (!d || !x || !y) return op_fail(err, TSM100_ERR_INVALID, "softmax: null argument");
+  if (!dtype_valid(d->dtype)) return op_fail(err, TSM100_ERR_INVALID, "softmax: unknown dtype");
+  if (d->rows < 0 || d->cols < 0) return op_fail(err, TSM100_ERR_INVALID, "softmax: negative shape");
+  if (d->rows == 0 || d->cols == 0) return TSM100_OK;  // empty tile: nothing to do
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (d->dtype) {
+    case TSM100_F32:
+      return softmax_typed<float>(err, static_cast<const float*>(x), static_cast<float*>(y), d->rows, d->cols, s);
+    case TSM100_BF16:
+      return softmax_typed<__nv_bfloat16>(err, static_cast<const __nv_bfloat16*>(x),
+                                          static_cast<__nv_bfloat16*>(y), d->rows, d->cols, s);
+    default:
+      return softmax_typed<__half>(err, static_cast<const __half*>(x), static_cast<__half*>(y), d->rows, d->cols, s);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// GEMM
+// ---------------------------------------------------------------------------
+template <typename InT, typename OutT>
+inline int32_t gemm_simt_launch(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
+                                cudaStream_t s) {
+  gemm_simt::Params p{static_cast<int32_t>(d->m), static_cast<int32_t>(d->n), static_cast<int32_t>(d->k), d->batch,
+                      d->b_transposed};
+  int sms = 0;
+  int32_t st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  const int64_t big_tiles = ((d->m + 63) / 64) * ((d->n + 63) / 64) * d->batch;
+  if (big_tiles >= 2ll * sms) {
+    dim3 grid(static_cast<unsigned>((d->n + 63) / 64), static_cast<unsigned>((d->m + 63) / 64),
+              static_cast<unsigned>(d->batch));
+    gemm_simt::gemm_simt_kernel<InT, OutT, 64, 64, 16, 4, 4><<<grid, 256, 0, s>>>(
+        static_cast<const InT*>(a), static_cast<const InT*>(b), static_cast<OutT*>(c), p);
+  } else {
+    dim3 grid(static_cast<unsigned>((d->n + 31) / 32), static_cast<unsigned>((d->m + 31) / 32),
+              static_cast<unsigned>(d->batch));
+    gemm_simt::gemm_simt_kernel<InT, OutT, 32, 32, 16, 4, 4><<<grid, 64, 0, s>>>(
+        static_cast<const InT*>(a), static_cast<const InT*>(b), static_cast<OutT*>(c), p);
+  }
+  return cuda_ok(err, cudaGetLastError(), "gemm_simt launch");
+}
+
+template <typename OutT, bool kBT, bool kBf16>
+inline int32_t gemm_tc_launch(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
+                              uint32_t* status, cudaStream_t s) {
+  namespace g = gemm_tc;
+  CUtensorMap ta, tb;
+  const uint64_t M = d->m, N = d->n, K = d->k, B = d->batch;
+  int32_t st = make_tmap_16bit_3d(err, &ta, a, K, M, B, K, M * K, g::kBK, g::kBM, kBf16);
+  if (st != TSM100_OK) return st;
+  if (kBT)
+    st = make_tmap_16bit_3d(err, &tb, b, K, N, B, K, N * K, g::kBK, g::kBN, kBf16);
+  else
+    st = make_tmap_16bit_3d(err, &tb, b, N, K, B, N, K * N, 64, g::kBK, kBf16);
+  if (st != TSM100_OK) return st;
+  g::Params p;
+  p.m = static_cast<int32_t>(M);
+  p.n = static_cast<int32_t>(N);
+  p.k = static_cast<int32_t>(K);
+  p.batch = d->batch;
+  p.m_blocks = static_cast<int32_t>((M + g::kBM - 1) / g::kBM);
+  p.n_blocks = static_cast<int32_t>((N + g::kBN - 1) / g::kBN);
+  p.c_batch_stride = static_cast<int64_t>(M * N);
+  p.status = status;
+  int sms = 0;
+  st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  const int64_t tiles = static_cast<int64_t>(p.m_blocks) * p.n_blocks * p.batch;
+  auto kern = g::gemm_tc_kernel<OutT, kBT, kBf16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
+  if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(gemm_tc_kernel)");
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sms));
+  kern<<<grid, g::kThreads, g::kSmemBytes, s>>>(ta, tb, static_cast<OutT*>(c), p);
+  return cuda_ok(err, cudaGetLastError(), "gemm_tc_kernel launch");
+}
+
+// `status` is a device word the tensor-core kernel writes if one of its bounded
+// waits runs out; it must be zero when the launch starts.
+inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
+                    uint32_t* status, void* stream) {
+  if (!d || !a || !b || !c) return op_fail(err, TSM100_ERR_INVALID, "gemm: null argument");
+  if (!dtype_valid(d->dtype) || !dtype_valid(d->out_dtype)) return op_fail(err, TSM100_ERR_INVALID, "gemm: unknown dtype");
+  if (d->m < 0 || d->n < 0 || d->k < 0 || d->batch < 0) return op_fail(err, TSM100_ERR_INVALID, "gemm: negative shape");
+  if (d->m > 0x7fffffff || d->n > 0x7fffffff || d->k > 0x7fffffff)
+    return op_fail(err, TSM100_ERR_INVALID, "gemm: dimension exceeds 2^31-1");
+  if (d->dtype == TSM100_F32 && d->out_dtype != TSM100_F32)
+    return op_fail(err, TSM100_ERR_INVALID, "gemm: f32 inputs produce f32 output");
+  if (d->dtype != TSM100_F32 && d->out_dtype != TSM100_F32 && d->out_dtype != d->dtype)
+    return op_fail(err, TSM100_ERR_INVALID, "gemm: 16-bit inputs produce the same 16-bit type or f32");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (d->m == 0 || d->n == 0 || d->batch == 0) return TSM100_OK;
+  if (d->k == 0) {  // empty contraction: C = 0 (linalg.fill)
+    const size_t bytes = static_cast<size_t>(d->batch) * d->m * d->n * dtype_size(d->out_dtype);
+    return cuda_ok(err, cudaMemsetAsync(c, 0, bytes, s), "cudaMemsetAsync");
+  }
+  if (d->dtype == TSM100_F32) return gemm_simt_launch<float, float>(err, d, a, b, c, s);
+
+  const bool bf16 = d->dtype == TSM100_BF16;
+  const bool out_f32 = d->out_dtype == TSM100_F32;
+  // TMA needs 16-byte-multiple row pitches; the epilogue stores 16-byte vectors.
+  const bool tma_ok = status != nullptr && aligned16(a) && aligned16(b) && aligned16(c) && (d->k % 8 == 0) &&
+                      (d->b_transposed || d->n % 8 == 0) && (d->n * dtype_size(d->out_dtype)) % 16 == 0 &&
+                      (static_cast<int64_t>((d->m + 127) / 128) * ((d->n + 255) / 256) * d->batch < 0x7fffffff);
+  if (tma_ok) {
+#define TSM_GEMM_TC(OUT, BT, BF) return gemm_tc_launch<OUT, BT, BF>(err, d, a, b, c, status, s)
+    if (bf16) {
+      if (out_f32) { if (d->b_transposed) TSM_GEMM_TC(float, true, true); else TSM_GEMM_TC(float, false, true); }
+      else { if (d->b_transposed) TSM_GEMM_TC(__nv_bfloat16, true, true); else TSM_GEMM_TC(__nv_bfloat16, false, true); }
+    } else {
+      if (out_f32) { if (d->b_transposed) TSM_GEMM_TC(float, true, false); else TSM_GEMM_TC(float, false, false); }
+      else { if (d->b_transposed) TSM_GEMM_TC(__half, true, false); else TSM_GEMM_TC(__half, false, false); }
+    }
+#undef TSM_GEMM_TC
+  }
+  if (bf16) {
+    if (out_f32) return gemm_simt_launch<__nv_bfloat16, float>(err, d, a, b, c, s);
+    return gemm_simt_launch<__nv_bfloat16, __nv_bfloat16>(err, d, a, b, c, s);
+  }
+  if (out_f32) return gemm_simt_launch<__half, float>(err, d, a, b, c, s);
+  return gemm_simt_launch<__half, __half>(err, d, a, b, c, s);
+}
+
+// ---------------------------------------------------------------------------
+// attention
+// ---------------------------------------------------------------------------
+template <typename T>
+inline int32_t attention_simt_launch(std::string* err, const tsm100_attention_desc* d, const void* q, const void* k,
+                                     const void* v, void* o, cudaStream_t s) {
+  attn_simt::Params p{d->seq, d->head_dim, d->heads_q, d->heads_kv, d->batch, d->causal,
+                      static_cast<float>(1.0 / std::sqrt(static_cast<double>(d->head_dim)))};
+  const int64_t rows = static_cast<int64_t>(d->batch) * d->heads_q * d->seq;
+  const int64_t grid = (rows + attn_simt::kWarps - 1) / attn_simt::kWarps;
+  if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many query rows for one launch");
+  attn_simt::attention_simt_kernel<T><<<static_cast<unsigned>(grid), attn_simt::kWarps * 32, 0, s>>>(
+      static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(o), p);
+  return cuda_ok(err, cudaGetLastError(), "attention_simt launch");
+}
+
+template <bool kBf16>
+inline int32_t attention_tc_launch(std::string* err, const tsm100_attention_desc* d, const void* q, const void* k,
+                                   const void* v, void* o, uint32_t* status, cudaStream_t s) {
+  namespace at = attn;
+  CUtensorMap tq, tk, tv;
+  const uint64_t S = d->seq, D = at::kD;
+  const uint64_t nq = static_cast<uint64_t>(d->batch) * d->heads_q, nkv = static_cast<uint64_t>(d->batch) * d->heads_kv;
+  int32_t st = make_tmap_16bit_3d(err, &tq, q, D, S, nq, D, S * D, 64, at::kBQ, kBf16);
+  if (st == TSM100_OK) st = make_tmap_16bit_3d(err, &tk, k, D, S, nkv, D, S * D, 64, at::kBKV, kBf16);
+  if (st == TSM100_OK) st = make_tmap_16bit_3d(err, &tv, v, D, S, nkv, D, S * D, 64, at::kBKV, kBf16);
+  if (st != TSM100_OK) return st;
+  at::Params p;
+  p.seq = d->seq;
+  p.heads_q = d->heads_q;
+  p.heads_kv = d->heads_kv;
+  p.batch = d->batch;
+  p.causal = d->causal ? 1 : 0;
+  p.q_blocks = (d->seq + 2 * at::kBQ - 1) / (2 * at::kBQ);
+  p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
+  p.status = status;
+  const int64_t grid = static_cast<int64_t>(p.q_blocks) * nq;
+  if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many tiles for one launch");
+  auto kern = at::attention_fwd_kernel<kBf16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, at::kSmemBytes);
+  if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_fwd_kernel)");
+  kern<<<static_cast<unsigned>(grid), at::kThreads, at::kSmemBytes, s>>>(tq, tk, tv, static_cast<uint16_t*>(o), p);
+  return cuda_ok(err, cudaGetLastError(), "attention_fwd_kernel launch");
+}
+
+inline int32_t attention(std::string* err, const tsm100_attention_desc* d, const void* q, const void* k,
+                         const void* v, void* o, uint32_t* status, void* stream) {
+  if (!d || !q || !k || !v || !o) return op_fail(err, TSM100_ERR_INVALID, "attention: null argument");
+  if (!dtype_valid(d->dtype)) return op_fail(err, TSM100_ERR_INVALID, "attention: unknown dtype");
+  if (d->batch < 0 || d->heads_q < 0 || d->heads_kv < 0 || d->seq < 0 || d->head_dim < 0)
+    return op_fail(err, TSM100_ERR_INVALID, "attention: negative shape");
+  if (d->batch == 0 || d->heads_q == 0 || d->seq == 0 || d->head_dim == 0) return TSM100_OK;
+  if (d->heads_kv <= 0 || d->heads_q % d->heads_kv != 0)
+    return op_fail(err, TSM100_ERR_INVALID, "attention: heads_q must be a positive multiple of heads_kv");
+  if (d->head_dim > attn_simt::kMaxD) return op_fail(err, TSM100_ERR_INVALID, "attention: head_dim > 256 unsupported");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc_ok = d->dtype != TSM100_F32 && d->head_dim == attn::kD && status != nullptr && aligned16(q) &&
+                     aligned16(k) && aligned16(v) && aligned16(o);
+  if (tc_ok) {
+    if (d->dtype == TSM100_BF16) return attention_tc_launch<true>(err, d, q, k, v, o, status, s);
+    return attention_tc_launch<false>(err, d, q, k, v, o, status, s);
+  }
+  if (d->dtype == TSM100_F32) return attention_simt_launch<float>(err, d, q, k, v, o, s);
+  if (d->dtype == TSM100_BF16) return attention_simt_launch<__nv_bfloat16>(err, d, q, k, v, o, s);
+  return attention_simt_launch<__half>(err, d, q, k, v, o, s);
+}
+
+}  // namespace ops
+}  // namespace tsm100
