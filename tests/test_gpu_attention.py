@@ -41,9 +41,7 @@ def test_attention_bf16_tensor_core(dev, pkg, oracle, b, hq, hkv, s, causal):
     q, k, v = bf16_qkv(capi, b, hq, hkv, s, 128)
     o = run_attention(dev, capi, q, k, v, capi.BF16, causal).view(np.uint16)
     ref32, _ = oracle.attention_bf16(q, k, v, causal)
-    m = oracle.compare(oracle.bf16_to_f32(o), ref32)
-    assert m["max_abs"] <= util.BF16_MAX_ABS, m
-    assert m["rel_fro"] <= util.BF16_REL_FRO, m
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(o), ref32)
 
 
 def test_attention_gqa_scaled_heads(dev, pkg, oracle):
@@ -61,8 +59,7 @@ def test_attention_gqa_scaled_heads(dev, pkg, oracle):
     q, k, v = (util.to_bf16(capi, t) for t in (qf, kf, vf))
     o = run_attention(dev, capi, q, k, v, capi.BF16, True).view(np.uint16)
     ref32, _ = oracle.attention_bf16(q, k, v, True)
-    m = oracle.compare(oracle.bf16_to_f32(o), ref32)
-    assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, m
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(o), ref32)
 
 
 @pytest.mark.parametrize("causal", [False, True])
@@ -83,15 +80,13 @@ def test_attention_f16_and_other_head_dim(dev, pkg, oracle):
     q, k, v = bf16_qkv(capi, b, h, h, s, d, seed=421)
     o = run_attention(dev, capi, q, k, v, capi.BF16, True).view(np.uint16)
     ref32, _ = oracle.attention_bf16(q, k, v, True)
-    m = oracle.compare(oracle.bf16_to_f32(o), ref32)
-    assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, m
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(o), ref32)
     # f16 inputs on the tensor-core kernel
     qf, kf, vf = (util.gen_normal(capi, (1, 2, 256, 128), 430 + i) for i in range(3))
     qh, kh, vh = (util.f32_to_f16_bits(t) for t in (qf, kf, vf))
     oh = run_attention(dev, capi, qh, kh, vh, capi.F16, False).view(np.float16).astype(np.float32)
     ref = oracle.attention_f32(*(t.view(np.float16).astype(np.float32) for t in (qh, kh, vh)), False)
-    m = oracle.compare(oh, ref)
-    assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, m
+    util.assert_16bit_close(oracle, oh, ref)
 
 
 def test_attention_bad_args(dev, pkg):
@@ -114,8 +109,7 @@ def test_attention_long_sequence_sampled_rows(dev, pkg, oracle, causal):
     o = run_attention(dev, capi, q, k, v, capi.BF16, causal).view(np.uint16)
     for row0 in (0, 1920, 4032):
         ref32, _ = oracle.attention_bf16(q, k, v, causal, q_row0=row0, q_rows=64)
-        m = oracle.compare(oracle.bf16_to_f32(np.ascontiguousarray(o[:, :, row0:row0 + 64])), ref32)
-        assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, (row0, m)
+        util.assert_16bit_close(oracle, oracle.bf16_to_f32(np.ascontiguousarray(o[:, :, row0:row0 + 64])), ref32, row0)
 
 
 def test_attention_gqa_16k_sampled_rows(dev, pkg, oracle):
@@ -126,8 +120,7 @@ def test_attention_gqa_16k_sampled_rows(dev, pkg, oracle):
     o = run_attention(dev, capi, q, k, v, capi.BF16, True).view(np.uint16)
     for row0 in (0, 8128, 16320):
         ref32, _ = oracle.attention_bf16(q, k, v, True, q_row0=row0, q_rows=64)
-        m = oracle.compare(oracle.bf16_to_f32(np.ascontiguousarray(o[:, :, row0:row0 + 64])), ref32)
-        assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, (row0, m)
+        util.assert_16bit_close(oracle, oracle.bf16_to_f32(np.ascontiguousarray(o[:, :, row0:row0 + 64])), ref32, row0)
 
 
 def test_attention_host_path(dev, pkg, oracle):
@@ -138,5 +131,4 @@ def test_attention_host_path(dev, pkg, oracle):
     dev.attention_host(capi.BF16, b, hq, hkv, s, d, q.ctypes.data, k.ctypes.data, v.ctypes.data, o.ctypes.data,
                        causal=True)
     ref32, _ = oracle.attention_bf16(q, k, v, True)
-    m = oracle.compare(oracle.bf16_to_f32(o), ref32)
-    assert m["max_abs"] <= util.BF16_MAX_ABS and m["rel_fro"] <= util.BF16_REL_FRO, m
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(o), ref32)

@@ -52,10 +52,10 @@ def test_gemm_bf16_tensor_core(dev, pkg, oracle, m, n, k, bt):
     c = run_gemm(dev, capi, a, b, m, n, k, capi.BF16, b_transposed=bt)[0].view(np.uint16)
     ref32, ref16 = oracle.gemm_bf16(a, b, bt)
     got = oracle.bf16_to_f32(c)
-    mt = oracle.compare(got, ref32)
-    assert mt["max_abs"] <= util.BF16_MAX_ABS, mt
-    assert mt["rel_fro"] <= util.BF16_REL_FRO, mt
-    assert np.abs(c.astype(np.int32) - ref16.astype(np.int32)).max() <= 1  # at most one bf16 ulp apart
+    util.assert_16bit_close(oracle, got, ref32)
+    # the rounded results agree with the oracle's own rounding except where the f32 sums
+    # (accumulated in a different order) straddle a rounding boundary
+    assert np.count_nonzero(c != ref16) <= c.size // 50
 
 
 def test_gemm_bf16_f32_out_and_batch(dev, pkg, oracle):
@@ -90,8 +90,7 @@ def test_gemm_bf16_odd_shape_falls_to_fp32_pipe(dev, pkg, oracle):
     b = util.to_bf16(capi, util.gen_normal(capi, (k, n), 331, 0.5))
     c = run_gemm(dev, capi, a, b, m, n, k, capi.BF16)[0].view(np.uint16)
     ref32, _ = oracle.gemm_bf16(a, b)
-    mt = oracle.compare(oracle.bf16_to_f32(c), ref32)
-    assert mt["max_abs"] <= util.BF16_MAX_ABS and mt["rel_fro"] <= util.BF16_REL_FRO, mt
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(c), ref32)
 
 
 def test_gemm_edge_cases(dev, pkg):
@@ -124,8 +123,7 @@ def test_gemm_bf16_full_size_sampled_rows(dev, pkg, oracle):
     rows = np.array([0, 1, 127, 128, 4095, 4096, 5000, 8191])
     got = oracle.bf16_to_f32(cd[torch.from_numpy(rows).to("cuda:0")].cpu().numpy().view(np.uint16))
     ref32, _ = oracle.gemm_bf16(np.ascontiguousarray(a[rows]), b)
-    mt = oracle.compare(got, ref32)
-    assert mt["max_abs"] <= util.BF16_MAX_ABS and mt["rel_fro"] <= util.BF16_REL_FRO, mt
+    util.assert_16bit_close(oracle, got, ref32)
     # scaling A by two is exact in bf16 and in f32 accumulation
     a2 = (ad.view(torch.bfloat16) * 2).view(torch.int16)
     c2 = torch.empty_like(cd)
@@ -142,5 +140,4 @@ def test_gemm_host_path(dev, pkg, oracle):
     c = np.zeros((m, n), np.uint16)
     dev.gemm_host(capi.BF16, m, n, k, a.ctypes.data, b.ctypes.data, c.ctypes.data)
     ref32, _ = oracle.gemm_bf16(a, b)
-    mt = oracle.compare(oracle.bf16_to_f32(c), ref32)
-    assert mt["max_abs"] <= util.BF16_MAX_ABS and mt["rel_fro"] <= util.BF16_REL_FRO, mt
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(c), ref32)

@@ -1,0 +1,110 @@
+"""The tile_hal mirror and emitted kernel modules on a real device, through the C ABI."""
+import numpy as np
+import pytest
+
+import mlir_fixtures as F
+import util
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def test_device_queries(dev, pkg):
+    assert pkg.hal.CudaSm100Device.device_count() >= 1
+    assert dev.ordinal() == 0 and "B200" in dev.name() or dev.sm_count() > 0
+    mi = dev.mem_info()
+    assert 0 < mi.free <= mi.total and mi.total > 100 << 30
+    sel = pkg.hal.BackendSelector(pkg.hal.BackendKind.from_codegen_path("cuda_sm100"))
+    d2 = sel.device(0)
+    assert d2.name() == dev.name()
+    d2.close()
+    with pytest.raises(pkg.hal.KernelError):
+        pkg.hal.CudaSm100Device(9999)
+
+
+def test_buffer_round_trip_and_streams(dev):
+    s = dev.create_stream()
+    host = np.arange(100000, dtype=np.float32)
+    buf = dev.alloc_from_slice(host, s)
+    assert buf.len() == host.size and not buf.is_empty() and buf.as_raw_ptr() != 0
+    assert np.array_equal(buf.copy_to_host(s), host)
+    buf.copy_from_host(host[::-1].copy(), s)
+    assert np.array_equal(buf.copy_to_host(s), host[::-1])
+    empty = dev.alloc_f32(0)
+    assert empty.is_empty() and empty.copy_to_host(s).size == 0
+    s.synchronize()
+    assert s.query()
+    with pytest.raises(Exception):
+        buf.copy_from_host(np.zeros(3, np.float32), s)
+
+
+def test_events_time_a_kernel(dev, pkg):
+    s = dev.create_stream()
+    x = dev.alloc_from_slice(util.softmax_input(pkg.capi, 4096, 4096), s)
+    y = dev.alloc(4096 * 4096, np.float32)
+    e0, e1 = dev.create_event(), dev.create_event()
+    e0.record(s)
+    dev.softmax(pkg.capi.F32, 4096, 4096, x.as_raw_ptr(), y.as_raw_mut_ptr(), stream=s.raw)
+    e1.record(s)
+    e1.synchronize()
+    ms = e0.elapsed_ms(e1)
+    assert 0.0 < ms < 50.0
+    assert abs(float(y.copy_to_host(s)[:4096].sum()) - 1.0) < 1e-5
+
+
+def _module(pkg, tmp_path, mlir, name):
+    out = pkg.codegen.CudaSm100Target().emit(mlir)
+    so = pkg.build.build_module(out.source, tmp_path / f"{name}.so")
+    return out, so
+
+
+def test_emitted_softmax_module_launches(dev, pkg, oracle, tmp_path):
+    """emit -> nvcc -> KernelLauncher.load -> launch(name, LaunchGrid, args, stream): the reference's flow."""
+    rows_per_block, cols, blocks = 2, 1024, 37
+    out, so = _module(pkg, tmp_path, F.softmax("softmax_tiles", rows_per_block, cols), "sm")
+    launcher = dev.create_launcher()
+    launcher.load(so, pkg.hal.KernelMode.Vector)
+    s = dev.create_stream()
+    x = util.softmax_input(pkg.capi, blocks * rows_per_block, cols)
+    xb = dev.alloc_from_slice(x, s)
+    yb = dev.alloc(x.size, np.float32)
+    launcher.launch(out.meta.kernel_names[0], pkg.hal.LaunchGrid.blocks_(blocks), [xb.as_raw_ptr(), yb.as_raw_mut_ptr()], s)
+    y = yb.copy_to_host(s).reshape(x.shape)
+    m = oracle.compare(y, oracle.softmax_f32(x), floor_r=1e-30)
+    assert m["rel_max"] <= util.F32_REL and m["max_elem_rel"] <= util.F32_REL, m
+    with pytest.raises(pkg.hal.KernelError):
+        launcher.launch("no_such_kernel", pkg.hal.LaunchGrid.blocks_(1), [0, 0], s)
+    with pytest.raises(pkg.hal.KernelError):
+        launcher.launch(out.meta.kernel_names[0], pkg.hal.LaunchGrid.blocks_(1), [xb.as_raw_ptr()], s)  # wrong arity
+
+
+def test_emitted_gemm_and_attention_modules(dev, pkg, oracle, tmp_path):
+    capi = pkg.capi
+    two = (F.matmul("mm_bf16", 256, 192, 256, dt="bf16").rsplit("}", 1)[0]
+           + F.attention_gqa("gqa_bf16", 4, 2, 256, 128, dt="bf16").split("module {", 1)[1])
+    out, so = _module(pkg, tmp_path, two, "two")
+    assert out.meta.kernel_names == ["mm_bf16", "gqa_bf16"]
+    launcher = dev.create_launcher()
+    launcher.load(so, pkg.hal.KernelMode.Matrix)
+    s = dev.create_stream()
+    blocks = 3  # three independent problems, one per block tile
+    a = util.to_bf16(capi, util.gen_normal(capi, (blocks, 256, 192), 1, 0.3))
+    b = util.to_bf16(capi, util.gen_normal(capi, (blocks, 192, 256), 2, 0.3))
+    ab, bb = dev.alloc_from_slice(a, s), dev.alloc_from_slice(b, s)
+    cb = dev.alloc(blocks * 256 * 256, np.uint16)
+    launcher.launch("mm_bf16", pkg.hal.LaunchGrid.blocks_(blocks), [ab.as_raw_ptr(), bb.as_raw_ptr(), cb.as_raw_mut_ptr()], s)
+    c = cb.copy_to_host(s).reshape(blocks, 256, 256)
+    assert dev.status(s) == 0
+    for i in range(blocks):
+        ref32, _ = oracle.gemm_bf16(a[i], b[i])
+        util.assert_16bit_close(oracle, oracle.bf16_to_f32(c[i]), ref32, i)
+    q = util.to_bf16(capi, util.gen_normal(capi, (2, 4, 256, 128), 3))
+    k = util.to_bf16(capi, util.gen_normal(capi, (2, 2, 256, 128), 4))
+    v = util.to_bf16(capi, util.gen_normal(capi, (2, 2, 256, 128), 5))
+    qb, kb, vb = (dev.alloc_from_slice(t, s) for t in (q, k, v))
+    ob = dev.alloc(q.size, np.uint16)
+    launcher.launch("gqa_bf16", pkg.hal.LaunchGrid.blocks_(2), [qb.as_raw_ptr(), kb.as_raw_ptr(), vb.as_raw_ptr(), ob.as_raw_mut_ptr()], s)
+    o = ob.copy_to_host(s).reshape(q.shape)
+    assert dev.status(s) == 0
+    ref32, _ = oracle.attention_bf16(q, k, v, True)
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(o), ref32)

@@ -1,0 +1,105 @@
+"""The CPU oracle against the committed float64 golden vectors, an independent
+numpy statement, known answers and the edge cases of the domain."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import oracle_np as onp
+
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def test_softmax_matches_golden(oracle):
+    g = np.load(GOLD / "softmax.npz")
+    y = oracle.softmax_f32(g["x"])
+    assert np.abs(y / g["y"] - 1).max() <= 2e-6  # f32 arithmetic against float64
+    assert np.abs(oracle.softmax_f32(g["x"], f64_acc=True) / g["y"] - 1).max() <= 6.1e-8  # one f32 rounding
+
+
+def test_gemm_matches_golden(oracle):
+    g = np.load(GOLD / "gemm.npz")
+    assert np.abs(oracle.gemm_f32(g["a"], g["b"]) - g["c"]).max() <= 2e-6
+    assert np.abs(oracle.gemm_f32(g["a"], np.ascontiguousarray(g["b"].T), True) - g["c_t"]).max() <= 2e-6
+    assert np.abs(oracle.gemm_f32(g["a"], g["b"], f64_acc=True) - g["c"]).max() <= 5e-7
+    c32, c16 = oracle.gemm_bf16(g["a_bf16"], g["b_bf16"])
+    assert np.abs(c32 - g["c_bf16"]).max() <= 2e-6
+    assert np.array_equal(c16, onp.f32_to_bf16_bits(c32))
+
+
+@pytest.mark.parametrize("key,heads,causal", [("o_gqa_causal", 4, True), ("o_gqa_full", 4, False),
+                                              ("o_mha_full", 2, False), ("o_mha_causal", 2, True)])
+def test_attention_matches_golden(oracle, key, heads, causal):
+    g = np.load(GOLD / "attention.npz")
+    q = np.ascontiguousarray(g["q"][:, :heads])
+    o = oracle.attention_f32(q, g["k"], g["v"], causal)
+    assert np.abs(o - g[key]).max() <= 2e-6
+
+
+def test_attention_bf16_path_and_row_window(oracle):
+    rng = np.random.default_rng(3)
+    q, k, v = (oracle.f32_to_bf16(rng.standard_normal(s).astype(np.float32)) for s in ((1, 4, 40, 32), (1, 2, 40, 32), (1, 2, 40, 32)))
+    o32, o16 = oracle.attention_bf16(q, k, v, True)
+    ref = onp.attention(*(onp.bf16_bits_to_f32(t) for t in (q, k, v)), True)
+    assert np.abs(o32 - ref).max() <= 2e-6
+    assert np.array_equal(o16, onp.f32_to_bf16_bits(o32))
+    w32, _ = oracle.attention_bf16(q, k, v, True, q_row0=17, q_rows=9)
+    assert np.array_equal(w32, o32[:, :, 17:26])
+
+
+def test_known_answers(oracle):
+    # a constant row is uniform; one dominant entry takes all the mass
+    y = oracle.softmax_f32(np.full((2, 7), 3.25, np.float32))
+    assert np.allclose(y, 1.0 / 7.0, rtol=0, atol=1e-8)
+    x = np.zeros((1, 5), np.float32)
+    x[0, 2] = 200.0
+    assert np.array_equal(oracle.softmax_f32(x), np.array([[0, 0, 1, 0, 0]], np.float32))
+    # identity and zero contraction
+    a = np.arange(12, dtype=np.float32).reshape(3, 4)
+    assert np.array_equal(oracle.gemm_f32(a, np.eye(4, dtype=np.float32)), a)
+    assert np.array_equal(oracle.gemm_f32(np.zeros((3, 0), np.float32), np.zeros((0, 2), np.float32)), np.zeros((3, 2), np.float32))
+    # causal attention: the first query row sees only the first key, so it returns V[0]
+    rng = np.random.default_rng(0)
+    q, k, v = (rng.standard_normal((1, 1, 6, 8)).astype(np.float32) for _ in range(3))
+    o = oracle.attention_f32(q, k, v, True)
+    assert np.array_equal(o[0, 0, 0], v[0, 0, 0])
+    # identical keys: attention is the mean of V
+    k[:] = k[0, 0, 0]
+    o = oracle.attention_f32(q, k, v, False)
+    assert np.abs(o[0, 0] - v[0, 0].mean(axis=0)).max() <= 1e-6
+
+
+def test_bf16_rounding_is_nearest_even(oracle):
+    vals = np.array([1.0, 1.00390625, 1.005859375, 1.01171875, -2.5, 3.0e38, 1e-40, 0.0], np.float32)
+    # 1.00390625 = 1 + 2^-8 is a tie -> rounds to even (1.0); 1.01171875 = 1 + 3*2^-8 is a tie -> 1.015625
+    got = oracle.bf16_to_f32(oracle.f32_to_bf16(vals))
+    assert got[0] == 1.0 and got[1] == 1.0 and got[2] == 1.0078125 and got[3] == 1.015625 and got[4] == -2.5
+    assert np.array_equal(oracle.f32_to_bf16(vals), onp.f32_to_bf16_bits(vals))
+    rng = np.random.default_rng(5)
+    r = rng.standard_normal(10000).astype(np.float32) * 100
+    assert np.array_equal(oracle.f32_to_bf16(r), onp.f32_to_bf16_bits(r))
+    assert np.array_equal(oracle.bf16_to_f32(oracle.f32_to_bf16(r)), onp.bf16_bits_to_f32(onp.f32_to_bf16_bits(r)))
+
+
+def test_softmax_outliers_and_random_against_numpy(oracle, pkg):
+    import util
+    x = util.softmax_input(pkg.capi, 40, 1000)
+    y = oracle.softmax_f32(x)
+    ref = onp.softmax(x)
+    assert np.abs(y / ref - 1).max() <= 1e-5
+    # about 1 % of the positions are +20 and they carry nearly all the mass
+    hot = x == 20.0
+    assert 0.005 < hot.mean() < 0.02
+    assert (y * hot).sum(axis=1).min() > 0.9
+    xb = util.to_bf16(pkg.capi, x)
+    y32, y16 = oracle.softmax_bf16(xb)
+    assert np.abs(y32 - onp.softmax(onp.bf16_bits_to_f32(xb))).max() <= 1e-6
+    assert np.array_equal(y16, onp.f32_to_bf16_bits(y32))
+
+
+def test_compare_metrics(oracle):
+    r = np.array([1.0, -2.0, 4.0, 0.0], np.float32)
+    y = np.array([1.5, -2.0, 4.0, 0.0], np.float32)
+    m = oracle.compare(y, r, floor_r=0.5)
+    assert m["max_abs"] == 0.5 and m["max_ref"] == 4.0 and m["rel_max"] == 0.125
+    assert abs(m["rel_fro"] - 0.5 / np.sqrt(21.0)) < 1e-12 and m["max_elem_rel"] == 0.5

@@ -86,3 +86,20 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
 if __name__ == "__main__":
     path = build_library(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+
+
+def build_module(source: str, out_path: Path) -> Path:
+    """Compiles a translation unit produced by the ``cuda_sm100`` target into a shared
+    library that ``KernelLauncher.load`` / ``tsm100_module_load`` accepts.  This is the
+    step the reference leaves to the host build crate (crates/tile_codegen/src/target.rs:4-10)."""
+    out_path = Path(out_path)
+    out_path.parent.mkdir(parents=True, exist_ok=True)
+    cu = out_path.with_suffix(".cu")
+    cu.write_text(source)
+    cmd = [nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
+           "--expt-relaxed-constexpr", "-shared", "-Xcompiler", "-fPIC", f"-I{CSRC}", f"-I{INCLUDE}",
+           "-cudart", "static", "-o", str(out_path), str(cu)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed on emitted module:\n{r.stdout}\n{r.stderr}")
+    return out_path

@@ -75,6 +75,17 @@ __device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
 }
 
 template <bool kIsBf16>
+__device__ __forceinline__ float unpack16_lo(uint32_t w) {
+  if (kIsBf16) return __uint_as_float(w << 16);
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xffffu)));
+}
+template <bool kIsBf16>
+__device__ __forceinline__ float unpack16_hi(uint32_t w) {
+  if (kIsBf16) return __uint_as_float(w & 0xffff0000u);
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
+}
+
+template <bool kIsBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, uint16_t* __restrict__ o, const Params p) {
@@ -317,18 +328,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           float e = ptx::ex2_approx(fmaf(__uint_as_float(v[i]), sl2, -ms));
           if (masked && (col0 + c * 32 + i > limit)) e = 0.f;
           pr[i] = e;
-          l += e;
         }
         uint8_t* half_base = prow + (c >> 1) * kHalfBytes;
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          uint4 w;
-          w.x = pack16x2<kIsBf16>(pr[8 * t + 0], pr[8 * t + 1]);
-          w.y = pack16x2<kIsBf16>(pr[8 * t + 2], pr[8 * t + 3]);
-          w.z = pack16x2<kIsBf16>(pr[8 * t + 4], pr[8 * t + 5]);
-          w.w = pack16x2<kIsBf16>(pr[8 * t + 6], pr[8 * t + 7]);
+          uint32_t w[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            w[u] = pack16x2<kIsBf16>(pr[8 * t + 2 * u], pr[8 * t + 2 * u + 1]);
+            // The row sum is taken over the ROUNDED probabilities, the ones the PV
+            // product really uses, so that O / l stays a convex combination of V rows.
+            l += unpack16_lo<kIsBf16>(w[u]) + unpack16_hi<kIsBf16>(w[u]);
+          }
           const int i16 = (c & 1) * 4 + t;
-          *reinterpret_cast<uint4*>(half_base + ((i16 ^ sw) << 4)) = w;
+          *reinterpret_cast<uint4*>(half_base + ((i16 ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       ptx::fence_proxy_async_smem();            // P visible to the tensor core's reads

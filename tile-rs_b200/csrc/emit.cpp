@@ -1,7 +1,719 @@
+// The `cuda_sm100` CodegenTarget: merged MLIR text -> one CUDA translation unit.
+//
+// Stands where the reference's NVIDIA emitter stands
+// (crates/rustc_codegen_tile/src/mlir_to_gpu.rs:62-99 behind
+// crates/tile_codegen/src/target.rs:57-65), but does not translate intrinsics
+// into scalar CUDA line by line.  It recognises what an entry kernel computes
+// (row softmax, a matrix product, fused attention, with the casts and masks
+// around them) and emits a launcher that instantiates the hand-written sm_100a
+// kernels of this library for the shapes the module carries.
+//
+// Input contract (crates/rustc_codegen_tile/src/mlir_parse.rs:84-213):
+//   * an entry kernel is an `llvm.func` whose header (pretty form) or closing
+//     line (generic form) carries `hacc.entry`;
+//   * a global-memory pointer argument has a type containing `ptr<1>`;
+//   * tile shapes and other integers are operands defined by
+//     `llvm.mlir.constant`; the first operand of a compute intrinsic is an
+//     ignored destination id.
+// A non-constant SSA name is never read as a number (the reference's
+// parse_const_arg turns `%12` into 12, mlir_parse.rs:1368-1388).
+//
+// Pure and deterministic: reads the text, touches no file, no environment.
+// Anything outside the target's scope is an error, never a TODO comment.
+#include <cmath>
+#include <cstdint>
 #include <cstring>
+#include <map>
+#include <sstream>
+#include <string>
+#include <vector>
+
 #include "../../include/tile_sm100.h"
+
+namespace tsm100 {
+std::string& last_error_ref();
+}
+
+namespace {
+
+struct EmitFailure {
+  std::string msg;
+};
+[[noreturn]] void reject(const std::string& m) { throw EmitFailure{m}; }
+
+std::string trim(const std::string& s) {
+  size_t a = 0, b = s.size();
+  while (a < b && (s[a] == ' ' || s[a] == '\t' || s[a] == '\r' || s[a] == '\n')) ++a;
+  while (b > a && (s[b - 1] == ' ' || s[b - 1] == '\t' || s[b - 1] == '\r' || s[b - 1] == '\n')) --b;
+  return s.substr(a, b - a);
+}
+
+bool starts_with(const std::string& s, const char* p) { return s.compare(0, std::strlen(p), p) == 0; }
+bool contains(const std::string& s, const char* p) { return s.find(p) != std::string::npos; }
+
+int count_char(const std::string& s, char c) {
+  int n = 0;
+  for (char ch : s) n += ch == c;
+  return n;
+}
+
+// Splits on commas that are not nested inside (), <>, [] or {}.
+std::vector<std::string> split_top(const std::string& s) {
+  std::vector<std::string> out;
+  int depth = 0;
+  std::string cur;
+  for (char c : s) {
+    if (c == '(' || c == '<' || c == '[' || c == '{') ++depth;
+    if (c == ')' || c == '>' || c == ']' || c == '}') --depth;
+    if (c == ',' && depth == 0) {
+      out.push_back(trim(cur));
+      cur.clear();
+    } else {
+      cur.push_back(c);
+    }
+  }
+  if (!trim(cur).empty()) out.push_back(trim(cur));
+  return out;
+}
+
+// Text between the '(' at `open` and its matching ')'.
+std::string paren_body(const std::string& s, size_t open) {
+  int depth = 0;
+  for (size_t i = open; i < s.size(); ++i) {
+    if (s[i] == '(') ++depth;
+    if (s[i] == ')' && --depth == 0) return s.substr(open + 1, i - open - 1);
+  }
+  return s.substr(open + 1);
+}
+
+struct Arg {
+  std::string name;
+  bool is_gm = false;
+};
+
+struct Func {
+  std::string name;
+  std::vector<Arg> args;
+  bool is_entry = false;
+  std::vector<std::string> body;
+};
+
+std::vector<Arg> parse_arg_list(const std::string& inside) {
+  std::vector<Arg> out;
+  for (const std::string& item : split_top(inside)) {
+    const size_t colon = item.find(':');
+    if (item.empty() || item[0] != '%' || colon == std::string::npos) continue;
+    Arg a;
+    a.name = trim(item.substr(0, colon));
+    a.is_gm = contains(item.substr(colon + 1), "ptr<1>");
+    out.push_back(a);
+  }
+  return out;
+}
+
+std::vector<Func> parse_module(const std::string& text) {
+  std::vector<std::string> lines;
+  {
+    std::istringstream in(text);
+    std::string l;
+    while (std::getline(in, l)) lines.push_back(trim(l));
+  }
+  std::vector<Func> funcs;
+  for (size_t i = 0; i < lines.size();) {
+    const std::string& line = lines[i];
+    const size_t at = line.find("llvm.func @");
+    if (at != std::string::npos && !starts_with(line, "//")) {
+      Func f;
+      const size_t name0 = at + std::strlen("llvm.func @");
+      const size_t open = line.find('(', name0);
+      if (open == std::string::npos) reject("cannot parse function header: " + line);
+      f.name = trim(line.substr(name0, open - name0));
+      f.args = parse_arg_list(paren_body(line, open));
+      f.is_entry = contains(line, "hacc.entry");
+      int depth = count_char(line, '{') - count_char(line, '}');
+      ++i;
+      while (i < lines.size() && depth > 0) {
+        depth += count_char(lines[i], '{') - count_char(lines[i], '}');
+        if (depth > 0) f.body.push_back(lines[i]);
+        ++i;
+      }
+      funcs.push_back(f);
+    } else if (starts_with(line, "\"llvm.func\"()")) {
+      // generic form: "llvm.func"() <{sym_name = "k", ...}> ({  ^bb0(%arg0: T, ...):  ...  }) {hacc.entry} : () -> ()
+      Func f;
+      const size_t sn = line.find("sym_name = \"");
+      if (sn != std::string::npos) {
+        const size_t b = sn + std::strlen("sym_name = \"");
+        f.name = line.substr(b, line.find('"', b) - b);
+      }
+      int depth = count_char(line, '(') - count_char(line, ')');
+      ++i;
+      while (i < lines.size() && depth > 0) {
+        const std::string& bl = lines[i];
+        depth += count_char(bl, '(') - count_char(bl, ')');
+        if (depth <= 0) {
+          f.is_entry = contains(bl, "hacc.entry");
+        } else if (starts_with(bl, "^bb0(")) {
+          f.args = parse_arg_list(paren_body(bl, bl.find('(')));
+        } else {
+          f.body.push_back(bl);
+        }
+        ++i;
+      }
+      if (!f.name.empty()) funcs.push_back(f);
+    } else {
+      ++i;
+    }
+  }
+  return funcs;
+}
+
+// ---- one body line -----------------------------------------------------------
+struct Call {
+  std::string result;  // may be empty
+  std::string callee;
+  std::vector<std::string> args;
+};
+
+std::string result_of(const std::string& line) {
+  if (line.empty() || line[0] != '%') return "";
+  const size_t eq = line.find('=');
+  return eq == std::string::npos ? "" : trim(line.substr(0, eq));
+}
+
+// Accepts `%r = llvm.call @f(a, b) : ...` and `%r = "llvm.call"(a, b) <{callee = @f, ...}> : ...`.
+bool parse_call(const std::string& line, Call* out) {
+  const size_t pretty = line.find("llvm.call @");
+  if (pretty != std::string::npos && !contains(line, "\"llvm.call\"")) {
+    const size_t n0 = pretty + std::strlen("llvm.call @");
+    const size_t open = line.find('(', n0);
+    if (open == std::string::npos) return false;
+    out->result = result_of(line);
+    out->callee = trim(line.substr(n0, open - n0));
+    out->args = split_top(paren_body(line, open));
+    return true;
+  }
+  const size_t generic = line.find("\"llvm.call\"(");
+  if (generic != std::string::npos) {
+    const size_t open = generic + std::strlen("\"llvm.call\"");
+    const size_t cal = line.find("callee = @");
+    if (cal == std::string::npos) return false;
+    size_t e = cal + std::strlen("callee = @");
+    size_t n1 = e;
+    while (n1 < line.size() && (isalnum(static_cast<unsigned char>(line[n1])) || line[n1] == '_' || line[n1] == '.')) ++n1;
+    out->result = result_of(line);
+    out->callee = line.substr(e, n1 - e);
+    out->args = split_top(paren_body(line, open));
+    return true;
+  }
+  return false;
+}
+
+// `%c = llvm.mlir.constant(128 : i32) : i32` or `%c = "llvm.mlir.constant"() <{value = 128 : i32}> : () -> i32`
+bool parse_constant(const std::string& line, std::string* name, std::string* literal, bool* is_float) {
+  if (!contains(line, "llvm.mlir.constant")) return false;
+  *name = result_of(line);
+  if (name->empty()) return false;
+  std::string lit;
+  const size_t v = line.find("value = ");
+  if (v != std::string::npos) {
+    lit = line.substr(v + std::strlen("value = "));
+  } else {
+    const size_t open = line.find('(', line.find("llvm.mlir.constant"));
+    if (open == std::string::npos) return false;
+    lit = paren_body(line, open);
+  }
+  const size_t colon = lit.find(':');
+  std::string ty = colon == std::string::npos ? "" : trim(lit.substr(colon + 1));
+  lit = trim(colon == std::string::npos ? lit : lit.substr(0, colon));
+  if (lit.empty()) return false;
+  *is_float = starts_with(ty, "f") || lit.find('.') != std::string::npos ||
+              (lit.find('e') != std::string::npos && !starts_with(lit, "0x"));
+  if (lit == "true") lit = "1";
+  if (lit == "false") lit = "0";
+  *literal = lit;
+  return true;
+}
+
+// ---- dataflow over tiles -------------------------------------------------------
+enum class Dt { F32, F16, BF16 };
+const char* dt_enum(Dt d) { return d == Dt::F32 ? "TSM100_F32" : d == Dt::F16 ? "TSM100_F16" : "TSM100_BF16"; }
+const char* dt_name(Dt d) { return d == Dt::F32 ? "f32" : d == Dt::F16 ? "f16" : "bf16"; }
+
+bool suffix_dtype(const std::string& callee, Dt* d) {
+  auto ends = [&](const char* s) {
+    const size_t n = std::strlen(s);
+    return callee.size() >= n && callee.compare(callee.size() - n, n, s) == 0;
+  };
+  if (ends("_bf16")) { *d = Dt::BF16; return true; }
+  if (ends("_f16")) { *d = Dt::F16; return true; }
+  if (ends("_f32")) { *d = Dt::F32; return true; }
+  return false;
+}
+
+enum class Kind { Load, Softmax, Matmul, MatmulT, Transpose, Scale, CausalMask, Attention, AttentionGqa };
+
+struct Tile {
+  Kind kind = Kind::Load;
+  Dt dtype = Dt::F32;      // storage type of the data the tile came from (through casts: the load's)
+  int arg = -1;            // Load: index among the kernel's pointer arguments
+  long rows = 0, cols = 0;
+  std::vector<std::string> in;  // producer tiles
+  long m = 0, k = 0, n = 0;     // Matmul*
+  double scalar = 0;            // Scale
+  long heads = 0, kv_heads = 0, seq = 0, dim = 0;  // Attention*
+};
+
+struct Kernel {
+  std::string name;
+  int nargs = 0;
+  std::string op;        // "softmax" | "gemm" | "attention"
+  std::string summary;   // comment line
+  std::string body;      // statements of the launcher
+  std::string instantiation;  // explicit instantiation(s) of the __global__ kernel(s)
+};
+
+struct FuncCtx {
+  const Func& f;
+  std::map<std::string, long> ints;
+  std::map<std::string, double> floats;
+  std::map<std::string, int> ptr_alias;  // SSA -> pointer-argument index
+  std::map<std::string, Tile> tiles;
+
+  explicit FuncCtx(const Func& fn) : f(fn) {
+    int idx = 0;
+    for (const Arg& a : f.args)
+      if (a.is_gm) ptr_alias[a.name] = idx++;
+  }
+  int nptr() const {
+    int n = 0;
+    for (const Arg& a : f.args) n += a.is_gm;
+    return n;
+  }
+  long int_of(const std::string& ssa, const char* what) const {
+    auto it = ints.find(ssa);
+    if (it == ints.end()) {
+      // a literal operand is accepted; an SSA name that is not a known constant is not
+      if (!ssa.empty() && (isdigit(static_cast<unsigned char>(ssa[0])))) return std::stol(ssa);
+      reject(std::string("kernel ") + f.name + ": " + what + " operand " + ssa + " is not a compile-time integer constant");
+    }
+    return it->second;
+  }
+  int ptr_of(const std::string& ssa) const {
+    auto it = ptr_alias.find(ssa);
+    if (it == ptr_alias.end()) reject("kernel " + f.name + ": " + ssa + " is not a global-memory pointer argument");
+    return it->second;
+  }
+  const Tile& tile_of(const std::string& ssa) const {
+    auto it = tiles.find(ssa);
+    if (it == tiles.end()) reject("kernel " + f.name + ": tile " + ssa + " has no known producer");
+    return it->second;
+  }
+};
+
+const char* cxx_type(Dt d) { return d == Dt::F32 ? "float" : d == Dt::F16 ? "__half" : "__nv_bfloat16"; }
+
+std::string softmax_chunks(Dt d, long cols) {
+  const long per_vec = d == Dt::F32 ? 4 : 8;
+  const long max_chunks = d == Dt::F32 ? 32 : 16;
+  if (cols % per_vec != 0) return "";
+  const long nvec = cols / per_vec;
+  for (long c = 1; c <= max_chunks; c *= 2)
+    if (nvec <= 32 * c) return std::to_string(c);
+  return "";
+}
+
+Kernel lower(const Func& f) {
+  FuncCtx cx(f);
+  Kernel k;
+  k.name = f.name;
+  k.nargs = cx.nptr();
+  std::string stored_tile;
+  int store_arg = -1;
+  Dt store_dt = Dt::F32;
+  long store_rows = 0, store_cols = 0;
+
+  for (const std::string& line : f.body) {
+    if (line.empty() || starts_with(line, "//") || starts_with(line, "^") || contains(line, "llvm.return") ||
+        contains(line, "llvm.mlir.addressof") || line == "}" || line == "{")
+      continue;
+    std::string name, lit;
+    bool is_float = false;
+    if (parse_constant(line, &name, &lit, &is_float)) {
+      try {
+        if (is_float) {
+          if (starts_with(lit, "0x")) {  // bit pattern of an f32
+            uint32_t bits = static_cast<uint32_t>(std::stoul(lit, nullptr, 16));
+            float v;
+            std::memcpy(&v, &bits, 4);
+            cx.floats[name] = v;
+          } else {
+            cx.floats[name] = std::stod(lit);
+          }
+        } else {
+          cx.ints[name] = std::stol(lit, nullptr, 0);
+        }
+      } catch (...) {
+        reject("kernel " + f.name + ": cannot read constant in: " + line);
+      }
+      continue;
+    }
+    Call c;
+    if (parse_call(line, &c)) {
+      const std::string& fn = c.callee;
+      Dt dt = Dt::F32;
+      const bool has_dt = suffix_dtype(fn, &dt);
+      auto need = [&](size_t n) {
+        if (c.args.size() != n)
+          reject("kernel " + f.name + ": " + fn + " expects " + std::to_string(n) + " operands, got " + std::to_string(c.args.size()));
+      };
+      if (fn == "__tile_pipe_barrier" || fn == "__tile_pipelined_for_begin" || fn == "__tile_pipelined_for_end" ||
+          fn == "__tile_get_block_idx" || fn == "__tile_get_block_num" || fn == "get_block_idx" || fn == "get_block_num") {
+        continue;  // scheduling hints and the per-block index: the launcher applies the per-block tile stride
+      }
+      if (starts_with(fn, "__tile_load_") && has_dt) {
+        need(3);
+        Tile t;
+        t.kind = Kind::Load;
+        t.dtype = dt;
+        t.arg = cx.ptr_of(c.args[0]);
+        t.rows = cx.int_of(c.args[1], "rows");
+        t.cols = cx.int_of(c.args[2], "cols");
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_store_") && has_dt) {
+        need(4);
+        if (!stored_tile.empty()) reject("kernel " + f.name + ": more than one tile store; one operator per kernel is supported");
+        store_arg = cx.ptr_of(c.args[0]);
+        stored_tile = c.args[1];
+        store_dt = dt;
+        store_rows = cx.int_of(c.args[2], "rows");
+        store_cols = cx.int_of(c.args[3], "cols");
+      } else if (starts_with(fn, "__tile_cast_")) {
+        need(4);
+        Tile t = cx.tile_of(c.args[1]);  // a cast only relabels: arithmetic is f32 inside every kernel
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_softmax_") && has_dt) {
+        need(4);
+        Tile t;
+        t.kind = Kind::Softmax;
+        t.in = {c.args[1]};
+        t.rows = cx.int_of(c.args[2], "rows");
+        t.cols = cx.int_of(c.args[3], "cols");
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else if ((starts_with(fn, "__tile_matmul_transposed_") || starts_with(fn, "__tile_matmul_")) && has_dt &&
+                 !contains(fn, "dequant") && !contains(fn, "_i8")) {
+        need(6);
+        Tile t;
+        t.kind = starts_with(fn, "__tile_matmul_transposed_") ? Kind::MatmulT : Kind::Matmul;
+        t.in = {c.args[1], c.args[2]};
+        t.m = cx.int_of(c.args[3], "m");
+        t.k = cx.int_of(c.args[4], "k");
+        t.n = cx.int_of(c.args[5], "n");
+        t.rows = t.m;
+        t.cols = t.n;
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_transpose_") && has_dt) {
+        need(4);
+        Tile t;
+        t.kind = Kind::Transpose;
+        t.in = {c.args[1]};
+        t.rows = cx.int_of(c.args[3], "cols");
+        t.cols = cx.int_of(c.args[2], "rows");
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_scale_") && has_dt) {
+        need(5);
+        Tile t;
+        t.kind = Kind::Scale;
+        t.in = {c.args[1]};
+        auto it = cx.floats.find(c.args[2]);
+        if (it == cx.floats.end()) reject("kernel " + f.name + ": scale factor " + c.args[2] + " is not a compile-time float constant");
+        t.scalar = it->second;
+        t.rows = cx.int_of(c.args[3], "rows");
+        t.cols = cx.int_of(c.args[4], "cols");
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_causal_mask_") && has_dt) {
+        need(4);
+        Tile t;
+        t.kind = Kind::CausalMask;
+        t.in = {c.args[1]};
+        t.rows = cx.int_of(c.args[2], "rows");
+        t.cols = cx.int_of(c.args[3], "cols");
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_attention_gqa_") && has_dt) {
+        // operand order of the NVIDIA emitter: (dst, q, k, v, num_heads, num_kv_heads, seq_len, head_dim)
+        need(8);
+        Tile t;
+        t.kind = Kind::AttentionGqa;
+        t.in = {c.args[1], c.args[2], c.args[3]};
+        t.heads = cx.int_of(c.args[4], "num_heads");
+        t.kv_heads = cx.int_of(c.args[5], "num_kv_heads");
+        t.seq = cx.int_of(c.args[6], "seq_len");
+        t.dim = cx.int_of(c.args[7], "head_dim");
+        t.rows = t.heads * t.seq;
+        t.cols = t.dim;
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_attention_") && has_dt) {
+        need(6);
+        Tile t;
+        t.kind = Kind::Attention;
+        t.in = {c.args[1], c.args[2], c.args[3]};
+        t.heads = t.kv_heads = 1;
+        t.seq = cx.int_of(c.args[4], "seq_len");
+        t.dim = cx.int_of(c.args[5], "head_dim");
+        t.rows = t.seq;
+        t.cols = t.dim;
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else {
+        reject("kernel " + f.name + ": intrinsic " + fn + " is outside the cuda_sm100 target (matmul, softmax, attention)");
+      }
+      continue;
+    }
+    // pointer arithmetic of the #[tile_kernel] prelude: the result aliases its base pointer
+    if (contains(line, "llvm.getelementptr")) {
+      const std::string res = result_of(line);
+      const size_t p = line.find('%', line.find("getelementptr"));
+      if (!res.empty() && p != std::string::npos) {
+        size_t e = p + 1;
+        while (e < line.size() && (isalnum(static_cast<unsigned char>(line[e])) || line[e] == '_')) ++e;
+        auto it = cx.ptr_alias.find(line.substr(p, e - p));
+        if (it != cx.ptr_alias.end()) cx.ptr_alias[res] = it->second;
+      }
+      continue;
+    }
+    // integer arithmetic and conversions feeding that pointer arithmetic carry no tile semantics
+    static const char* kScalarOps[] = {"llvm.mul", "llvm.add", "llvm.sub", "llvm.zext", "llvm.sext", "llvm.trunc",
+                                       "llvm.shl", "llvm.ptrtoint", "llvm.inttoptr", "llvm.bitcast", "llvm.and",
+                                       "llvm.or", "llvm.udiv", "llvm.urem", "llvm.icmp", "llvm.select", "llvm.br",
+                                       "llvm.unreachable", "llvm.intr.assume", "llvm.alloca", "llvm.store", "llvm.load"};
+    bool scalar = false;
+    for (const char* op : kScalarOps) scalar = scalar || contains(line, op);
+    if (scalar) continue;
+    reject("kernel " + f.name + ": unrecognised operation: " + line);
+  }
+
+  if (stored_tile.empty()) reject("kernel " + f.name + ": no tile store; nothing to compute");
+  const Tile& root = cx.tile_of(stored_tile);
+  std::ostringstream body, inst, sum;
+  const Dt out_dt = store_dt;
+
+  auto load_of = [&](const std::string& ssa, const char* role) -> const Tile& {
+    const Tile& t = cx.tile_of(ssa);
+    if (t.kind != Kind::Load) reject("kernel " + f.name + ": the " + role + " operand must come straight from a tile load");
+    return t;
+  };
+
+  if (root.kind == Kind::Softmax) {
+    const Tile& x = load_of(root.in[0], "softmax input");
+    if (x.rows != root.rows || x.cols != root.cols || store_rows != root.rows || store_cols != root.cols)
+      reject("kernel " + f.name + ": softmax tile shapes disagree between load, op and store");
+    if (out_dt != x.dtype) reject("kernel " + f.name + ": softmax input and output storage types differ");
+    k.op = "softmax";
+    sum << "__tile_softmax on " << root.rows << " x " << root.cols << " " << dt_name(x.dtype) << " tiles, one per block";
+    body << "  tsm100_softmax_desc d;\n  d.dtype = " << dt_enum(x.dtype) << ";\n  d.rows = static_cast<int64_t>(blocks) * " << root.rows
+         << ";\n  d.cols = " << root.cols << ";\n"
+         << "  st = tsm100::ops::softmax(&msg, &d, args[" << x.arg << "], args[" << store_arg << "], stream);\n";
+    const std::string ch = softmax_chunks(x.dtype, root.cols);
+    if (!ch.empty())
+      inst << "template __global__ void tsm100::softmax::softmax_rows_warp<" << cxx_type(x.dtype) << ", " << ch << ", 4>(const "
+           << cxx_type(x.dtype) << "*, " << cxx_type(x.dtype) << "*, int64_t, int32_t);\n";
+    else
+      inst << "template __global__ void tsm100::softmax::softmax_rows_stream<" << cxx_type(x.dtype) << ", 512>(const "
+           << cxx_type(x.dtype) << "*, " << cxx_type(x.dtype) << "*, int64_t, int64_t);\n";
+  } else if (root.kind == Kind::Matmul || root.kind == Kind::MatmulT) {
+    const Tile* prod = &root;
+    bool causal_chain = false;
+    // softmax(causal_mask(scale(Q K^T))) V : the decomposed causal attention
+    const Tile& lhs = cx.tile_of(root.in[0]);
+    if (root.kind == Kind::Matmul && lhs.kind == Kind::Softmax) {
+      const Tile* t = &cx.tile_of(lhs.in[0]);
+      bool masked = false;
+      double scale = 1.0;
+      bool scaled = false;
+      for (int hop = 0; hop < 2; ++hop) {
+        if (t->kind == Kind::CausalMask) { masked = true; t = &cx.tile_of(t->in[0]); }
+        else if (t->kind == Kind::Scale) { scaled = true; scale = t->scalar; t = &cx.tile_of(t->in[0]); }
+      }
+      const Tile* qk = t;
+      const Tile* qt = nullptr;
+      const Tile* kt = nullptr;
+      if (qk->kind == Kind::MatmulT) {
+        qt = &cx.tile_of(qk->in[0]);
+        kt = &cx.tile_of(qk->in[1]);
+      } else if (qk->kind == Kind::Matmul && cx.tile_of(qk->in[1]).kind == Kind::Transpose) {
+        qt = &cx.tile_of(qk->in[0]);
+        kt = &cx.tile_of(cx.tile_of(qk->in[1]).in[0]);
+      }
+      if (qt && kt) {
+        const Tile& vt = load_of(root.in[1], "attention V");
+        if (qt->kind != Kind::Load || kt->kind != Kind::Load) reject("kernel " + f.name + ": attention Q and K must come straight from tile loads");
+        const long seq = qk->m, dim = qk->k;
+        if (qk->n != seq || vt.rows != seq || vt.cols != dim || root.k != seq || root.n != dim)
+          reject("kernel " + f.name + ": decomposed attention with inconsistent shapes");
+        const double want = 1.0 / std::sqrt(static_cast<double>(dim));
+        if (!scaled || std::fabs(scale - want) > 1e-6 * want)
+          reject("kernel " + f.name + ": decomposed attention must scale the scores by 1/sqrt(head_dim)");
+        causal_chain = true;
+        k.op = "attention";
+        sum << "decomposed attention (matmul, scale" << (masked ? ", causal mask" : "") << ", softmax, matmul) fused: seq " << seq
+            << ", head_dim " << dim << ", " << dt_name(qt->dtype) << ", one head per block";
+        body << "  tsm100_attention_desc d;\n  d.dtype = " << dt_enum(qt->dtype) << ";\n  d.causal = " << (masked ? 1 : 0)
+             << ";\n  d.batch = static_cast<int32_t>(blocks);\n  d.heads_q = 1;\n  d.heads_kv = 1;\n  d.seq = " << seq
+             << ";\n  d.head_dim = " << dim << ";\n"
+             << "  st = tsm100::ops::attention(&msg, &d, args[" << qt->arg << "], args[" << kt->arg << "], args[" << vt.arg
+             << "], args[" << store_arg << "], status, stream);\n";
+        if (out_dt != qt->dtype) reject("kernel " + f.name + ": attention input and output storage types differ");
+        if (qt->dtype != Dt::F32 && dim == 128)
+          inst << "template __global__ void tsm100::attn::attention_fwd_kernel<" << (qt->dtype == Dt::BF16 ? "true" : "false")
+               << ">(const __grid_constant__ CUtensorMap, const __grid_constant__ CUtensorMap, const __grid_constant__ CUtensorMap, uint16_t*, const tsm100::attn::Params);\n";
+        else
+          inst << "template __global__ void tsm100::attn_simt::attention_simt_kernel<" << cxx_type(qt->dtype) << ">(const "
+               << cxx_type(qt->dtype) << "*, const " << cxx_type(qt->dtype) << "*, const " << cxx_type(qt->dtype) << "*, "
+               << cxx_type(qt->dtype) << "*, const tsm100::attn_simt::Params);\n";
+      }
+    }
+    if (!causal_chain) {
+      const Tile& a = load_of(prod->in[0], "matmul A");
+      const Tile& b = load_of(prod->in[1], "matmul B");
+      const bool bt = prod->kind == Kind::MatmulT;
+      if (a.rows != prod->m || a.cols != prod->k || (bt ? (b.rows != prod->n || b.cols != prod->k) : (b.rows != prod->k || b.cols != prod->n)) ||
+          store_rows != prod->m || store_cols != prod->n)
+        reject("kernel " + f.name + ": matmul tile shapes disagree between loads, op and store");
+      if (a.dtype != b.dtype) reject("kernel " + f.name + ": matmul operands have different storage types");
+      if (!(out_dt == a.dtype || out_dt == Dt::F32)) reject("kernel " + f.name + ": matmul output must be the input type or f32");
+      k.op = "gemm";
+      sum << "__tile_matmul" << (bt ? "_transposed" : "") << " " << prod->m << " x " << prod->k << " x " << prod->n << ", "
+          << dt_name(a.dtype) << " in, " << dt_name(out_dt) << " out, one problem per block";
+      body << "  tsm100_gemm_desc d;\n  d.dtype = " << dt_enum(a.dtype) << ";\n  d.out_dtype = " << dt_enum(out_dt)
+           << ";\n  d.b_transposed = " << (bt ? 1 : 0) << ";\n  d.batch = static_cast<int32_t>(blocks);\n  d.m = " << prod->m
+           << ";\n  d.n = " << prod->n << ";\n  d.k = " << prod->k << ";\n"
+           << "  st = tsm100::ops::gemm(&msg, &d, args[" << a.arg << "], args[" << b.arg << "], args[" << store_arg
+           << "], status, stream);\n";
+      const bool tma = a.dtype != Dt::F32 && prod->k % 8 == 0 && (bt || prod->n % 8 == 0) &&
+                       (prod->n * (out_dt == Dt::F32 ? 4 : 2)) % 16 == 0;
+      if (tma)
+        inst << "template __global__ void tsm100::gemm_tc::gemm_tc_kernel<" << cxx_type(out_dt) << ", " << (bt ? "true" : "false")
+             << ", " << (a.dtype == Dt::BF16 ? "true" : "false") << ">(const __grid_constant__ CUtensorMap, const __grid_constant__ CUtensorMap, " << cxx_type(out_dt)
+             << "*, const tsm100::gemm_tc::Params);\n";
+      else
+        inst << "template __global__ void tsm100::gemm_simt::gemm_simt_kernel<" << cxx_type(a.dtype) << ", " << cxx_type(out_dt)
+             << ", 64, 64, 16, 4, 4>(const " << cxx_type(a.dtype) << "*, const " << cxx_type(a.dtype) << "*, " << cxx_type(out_dt)
+             << "*, const tsm100::gemm_simt::Params);\n";
+    }
+  } else if (root.kind == Kind::Attention || root.kind == Kind::AttentionGqa) {
+    const Tile& q = load_of(root.in[0], "attention Q");
+    const Tile& kk = load_of(root.in[1], "attention K");
+    const Tile& v = load_of(root.in[2], "attention V");
+    const bool gqa = root.kind == Kind::AttentionGqa;
+    if (q.dtype != kk.dtype || q.dtype != v.dtype || out_dt != q.dtype)
+      reject("kernel " + f.name + ": attention tensors must share one storage type");
+    if (gqa && (root.kv_heads <= 0 || root.heads % root.kv_heads != 0))
+      reject("kernel " + f.name + ": num_heads must be a positive multiple of num_kv_heads");
+    k.op = "attention";
+    sum << (gqa ? "__tile_attention_gqa (causal)" : "__tile_attention") << ": heads " << root.heads << "/" << root.kv_heads << ", seq "
+        << root.seq << ", head_dim " << root.dim << ", " << dt_name(q.dtype) << ", one " << (gqa ? "batch" : "head") << " per block";
+    body << "  tsm100_attention_desc d;\n  d.dtype = " << dt_enum(q.dtype) << ";\n  d.causal = " << (gqa ? 1 : 0)
+         << ";\n  d.batch = static_cast<int32_t>(blocks);\n  d.heads_q = " << root.heads << ";\n  d.heads_kv = " << root.kv_heads
+         << ";\n  d.seq = " << root.seq << ";\n  d.head_dim = " << root.dim << ";\n"
+         << "  st = tsm100::ops::attention(&msg, &d, args[" << q.arg << "], args[" << kk.arg << "], args[" << v.arg << "], args["
+         << store_arg << "], status, stream);\n";
+    if (q.dtype != Dt::F32 && root.dim == 128)
+      inst << "template __global__ void tsm100::attn::attention_fwd_kernel<" << (q.dtype == Dt::BF16 ? "true" : "false")
+           << ">(const __grid_constant__ CUtensorMap, const __grid_constant__ CUtensorMap, const __grid_constant__ CUtensorMap, uint16_t*, const tsm100::attn::Params);\n";
+    else
+      inst << "template __global__ void tsm100::attn_simt::attention_simt_kernel<" << cxx_type(q.dtype) << ">(const "
+           << cxx_type(q.dtype) << "*, const " << cxx_type(q.dtype) << "*, const " << cxx_type(q.dtype) << "*, " << cxx_type(q.dtype)
+           << "*, const tsm100::attn_simt::Params);\n";
+  } else {
+    reject("kernel " + f.name + ": the stored tile is not produced by matmul, softmax or attention");
+  }
+  k.summary = sum.str();
+  k.body = body.str();
+  k.instantiation = inst.str();
+  return k;
+}
+
+std::string emit_source(const std::string& mlir, std::vector<std::string>* names) {
+  if (trim(mlir).empty()) reject("empty MLIR module");
+  const std::vector<Func> funcs = parse_module(mlir);
+  std::vector<Kernel> kernels;
+  for (const Func& f : funcs)
+    if (f.is_entry) kernels.push_back(lower(f));
+  if (kernels.empty()) reject("no entry kernel (llvm.func with hacc.entry) found in the module");
+
+  std::ostringstream o;
+  o << "// Generated by the tile-rs `cuda_sm100` target. Do not edit.\n"
+       "// Kernels: hand-written sm_100a (tcgen05 / TMEM / TMA) templates of libtile_sm100,\n"
+       "// instantiated here for the shapes the module carries.\n"
+       "// Compile: nvcc -gencode arch=compute_100a,code=sm_100a -std=c++17 -O3 -lineinfo --expt-relaxed-constexpr \\\n"
+       "//          -shared -Xcompiler -fPIC -I<tile_sm100>/csrc -cudart static -o <module>.so <this file>\n"
+       "// Load with tsm100_module_load(); launch <kernel> with tsm100_launch(module, \"<kernel>\", blocks, args, nargs, stream).\n"
+       "#include <cstdint>\n#include <cstdio>\n#include <string>\n\n#include \"ops.cuh\"\n\n";
+  for (const Kernel& k : kernels) {
+    o << "// ---- kernel " << k.name << ": " << k.summary << "\n";
+    o << k.instantiation;
+    o << "extern \"C\" int32_t " << k.name
+      << "_launch(void** args, uint32_t nargs, uint32_t blocks, void* stream, uint32_t* status, char* err, size_t err_cap) {\n"
+         "  std::string msg;\n  int32_t st = TSM100_OK;\n"
+         "  if (nargs != "
+      << k.nargs << "u || args == nullptr) {\n    st = TSM100_ERR_INVALID;\n    msg = \"" << k.name << " takes " << k.nargs
+      << " global-memory pointers\";\n  } else {\n";
+    // indent the body one more level
+    std::istringstream bl(k.body);
+    std::string l;
+    while (std::getline(bl, l)) o << "  " << l << "\n";
+    o << "  }\n  if (st != TSM100_OK && err != nullptr && err_cap > 0) snprintf(err, err_cap, \"%s\", msg.c_str());\n  return st;\n}\n\n";
+    names->push_back(k.name);
+  }
+  return o.str();
+}
+
+int32_t copy_out(const std::string& s, char* buf, size_t cap, size_t* len) {
+  if (len) *len = s.size();
+  if (!buf || cap < s.size() + 1) return TSM100_ERR_BUFFER;
+  std::memcpy(buf, s.data(), s.size());
+  buf[s.size()] = '\0';
+  return TSM100_OK;
+}
+
+}  // namespace
+
 extern "C" {
+
 const char* tsm100_target_name(void) { return "cuda_sm100"; }
 const char* tsm100_target_ext(void) { return "cu"; }
-int32_t tsm100_emit(const char*, size_t, char*, size_t, size_t*, char*, size_t, size_t*) { return TSM100_ERR_EMIT; }
+
+int32_t tsm100_emit(const char* mlir, size_t mlir_len, char* source, size_t source_cap, size_t* source_len,
+                    char* names, size_t names_cap, size_t* names_len) {
+  if (!mlir && mlir_len) {
+    tsm100::last_error_ref() = "null MLIR text";
+    return TSM100_ERR_INVALID;
+  }
+  try {
+    std::vector<std::string> kernel_names;
+    const std::string src = emit_source(std::string(mlir ? mlir : "", mlir_len), &kernel_names);
+    std::string joined;
+    for (size_t i = 0; i < kernel_names.size(); ++i) joined += (i ? "\n" : "") + kernel_names[i];
+    const int32_t a = copy_out(src, source, source_cap, source_len);
+    const int32_t b = copy_out(joined, names, names_cap, names_len);
+    if (a != TSM100_OK || b != TSM100_OK) {
+      tsm100::last_error_ref() = "output buffer too small";
+      return TSM100_ERR_BUFFER;
+    }
+    return TSM100_OK;
+  } catch (const EmitFailure& e) {
+    tsm100::last_error_ref() = e.msg;
+    return TSM100_ERR_EMIT;
+  } catch (const std::exception& e) {
+    tsm100::last_error_ref() = std::string("emit failed: ") + e.what();
+    return TSM100_ERR_EMIT;
+  }
 }
+
+}  // extern "C"
