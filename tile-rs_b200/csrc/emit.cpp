@@ -313,13 +313,22 @@ struct FuncCtx {
 
 const char* cxx_type(Dt d) { return d == Dt::F32 ? "float" : d == Dt::F16 ? "__half" : "__nv_bfloat16"; }
 
-std::string softmax_chunks(Dt d, long cols) {
+// The softmax kernel the library's dispatch picks for a row width (ops.cuh), as an
+// explicit instantiation directive; empty when the row is not 16-byte-vector aligned.
+std::string softmax_instantiation(Dt d, long cols) {
   const long per_vec = d == Dt::F32 ? 4 : 8;
-  const long max_chunks = d == Dt::F32 ? 32 : 16;
   if (cols % per_vec != 0) return "";
   const long nvec = cols / per_vec;
-  for (long c = 1; c <= max_chunks; c *= 2)
-    if (nvec <= 32 * c) return std::to_string(c);
+  const std::string t = cxx_type(d);
+  const std::string sig = "(const " + t + "*, " + t + "*, int64_t, int32_t);\n";
+  if (nvec <= 256) {
+    const long c = nvec <= 32 ? 1 : nvec <= 64 ? 2 : nvec <= 128 ? 4 : 8;
+    return "template __global__ void tsm100::softmax::softmax_rows_warp<" + t + ", " + std::to_string(c) + ", 4>" + sig;
+  }
+  if (nvec <= 2048) {
+    const char* shape = nvec <= 512 ? "4, 128" : nvec <= 1024 ? "8, 128" : "8, 256";
+    return "template __global__ void tsm100::softmax::softmax_rows_cta<" + t + ", " + shape + ">" + sig;
+  }
   return "";
 }
 
@@ -519,10 +528,9 @@ Kernel lower(const Func& f) {
     body << "  tsm100_softmax_desc d;\n  d.dtype = " << dt_enum(x.dtype) << ";\n  d.rows = static_cast<int64_t>(blocks) * " << root.rows
          << ";\n  d.cols = " << root.cols << ";\n"
          << "  st = tsm100::ops::softmax(&msg, &d, args[" << x.arg << "], args[" << store_arg << "], stream);\n";
-    const std::string ch = softmax_chunks(x.dtype, root.cols);
-    if (!ch.empty())
-      inst << "template __global__ void tsm100::softmax::softmax_rows_warp<" << cxx_type(x.dtype) << ", " << ch << ", 4>(const "
-           << cxx_type(x.dtype) << "*, " << cxx_type(x.dtype) << "*, int64_t, int32_t);\n";
+    const std::string direct = softmax_instantiation(x.dtype, root.cols);
+    if (!direct.empty())
+      inst << direct;
     else
       inst << "template __global__ void tsm100::softmax::softmax_rows_stream<" << cxx_type(x.dtype) << ", 512>(const "
            << cxx_type(x.dtype) << "*, " << cxx_type(x.dtype) << "*, int64_t, int64_t);\n";

@@ -122,17 +122,30 @@ inline int32_t softmax_typed(std::string* err, const T* x, T* y, int64_t rows, i
   const bool vec_ok = (cols % PV == 0) && aligned16(x) && aligned16(y);
   const int64_t nvec = cols / PV;
   cudaError_t e;
-  // a lane keeps at most 128 f32 values in registers: 32 vectors of 4, or 16 of 8
-  constexpr int kMaxChunks = PV == 4 ? 32 : 16;
-  if (vec_ok && nvec <= 32 * kMaxChunks && rows <= 4ll * 0x7fffffff) {
+  if (vec_ok && nvec <= 32 * 8 && rows <= 4ll * 0x7fffffff) {  // one warp per row
     const int32_t c = static_cast<int32_t>(cols);
     if (nvec <= 32 * 1) e = launch_softmax_warp<T, 1>(x, y, rows, c, s);
     else if (nvec <= 32 * 2) e = launch_softmax_warp<T, 2>(x, y, rows, c, s);
     else if (nvec <= 32 * 4) e = launch_softmax_warp<T, 4>(x, y, rows, c, s);
-    else if (nvec <= 32 * 8) e = launch_softmax_warp<T, 8>(x, y, rows, c, s);
-    else if (nvec <= 32 * 16) e = launch_softmax_warp<T, 16>(x, y, rows, c, s);
-    else e = launch_softmax_warp<T, kMaxChunks>(x, y, rows, c, s);
+    else e = launch_softmax_warp<T, 8>(x, y, rows, c, s);
     return cuda_ok(err, e, "softmax_rows_warp launch");
+  }
+  if (vec_ok && nvec <= 256 * 8) {  // 128 or 256 threads per row, 32 values each
+    int sms_cta = 0;
+    int32_t st_cta = sm_count(err, &sms_cta);
+    if (st_cta != TSM100_OK) return st_cta;
+    const int32_t c = static_cast<int32_t>(cols);
+    // persistent CTAs: exactly as many as are resident at once, each striding over the rows
+    auto launch = [&](auto kern, int threads) {
+      int per_sm = 1;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+      const unsigned grid = static_cast<unsigned>(std::min<int64_t>(rows, static_cast<int64_t>(sms_cta) * per_sm));
+      kern<<<grid, threads, 0, s>>>(x, y, rows, c);
+    };
+    if (nvec <= 128 * 4) launch(softmax::softmax_rows_cta<T, 4, 128>, 128);
+    else if (nvec <= 128 * 8) launch(softmax::softmax_rows_cta<T, 8, 128>, 128);
+    else launch(softmax::softmax_rows_cta<T, 8, 256>, 256);
+    return cuda_ok(err, cudaGetLastError(), "softmax_rows_cta launch");
   }
   int sms = 0;
   int32_t st = sm_count(err, &sms);

@@ -8,11 +8,14 @@
 // (crates/rustc_codegen_tile/src/mlir_to_gpu.rs:1242-1336); nothing of it is kept.
 //
 // The operator is bound by HBM: 2 * sizeof(T) algorithmic bytes per element.
-// Three kernels, picked by the host from the row width:
+// Four kernels, picked by the host from the row width:
 //   * softmax_rows_warp  : one warp per row, the whole row held in registers,
 //     128-bit coalesced streaming loads, shuffle reductions, one global read and
-//     one global write per element.  Used while the row fits (<= 4096 elements) and
-//     is 16-byte aligned.
+//     one global write per element.  Rows of up to 256 16-byte vectors.
+//   * softmax_rows_cta   : 128 or 256 threads per row, 32 values per thread in
+//     registers, warp shuffles plus one shared-memory exchange per reduction;
+//     persistent CTAs stride over the rows.  Rows of up to 2048 vectors (the
+//     4096-wide configuration runs here with eight resident CTAs per SM).
 //   * softmax_rows_block : one CTA per row, the row staged once in shared memory
 //     as f32 (up to 56 Ki elements); still one read + one write.
 //   * softmax_rows_stream: any width or alignment; online max/sum in a first
@@ -185,6 +188,105 @@ softmax_rows_warp(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int3
       for (int e = 0; e < PV; ++e) v[c][e] *= inv;
       st_stream(yr + i, Elem<T>::pack(v[c]));
     }
+  }
+}
+
+// exp(x - m) as 2^(x*log2e - m*log2e): one FMA and one MUFU op.  For |x - m| up to
+// ~100 the rounding of the FMA argument costs less than 4e-6 relative, inside the
+// 1e-5 bound of the f32 configuration; results below 2^-126 flush to zero.
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float exp_shifted(float x, float m_log2e) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(fmaf(x, kLog2e, -m_log2e)));
+  return y;
+}
+
+// ---------------------------------------------------------------------------
+// THREADS threads per row, VPT 16-byte vectors per thread (vector k*THREADS + tid).
+// Same alignment contract as the warp kernel; cols <= THREADS * VPT * kPerVec.
+// ---------------------------------------------------------------------------
+template <typename T, int VPT, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+softmax_rows_cta(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int32_t cols) {
+  constexpr int PV = Elem<T>::kPerVec;
+  constexpr int NW = THREADS / 32;
+  __shared__ float red_max[NW];
+  __shared__ float red_sum[NW];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nvec = cols / PV;
+  // Software pipeline: the loads of the next row are in flight while this row is
+  // reduced and stored, which doubles the bytes each SM keeps outstanding.
+  Vec16 raw[VPT];
+  if (static_cast<int64_t>(blockIdx.x) < rows) {
+    const Vec16* x0 = reinterpret_cast<const Vec16*>(x + static_cast<int64_t>(blockIdx.x) * cols);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = k * THREADS + tid;
+      if (i < nvec) raw[k] = ld_stream(x0 + i);
+    }
+  }
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    Vec16* yr = reinterpret_cast<Vec16*>(y + row * cols);
+    Vec16 nxt[VPT];
+    const int64_t next_row = row + gridDim.x;
+    if (next_row < rows) {
+      const Vec16* xn = reinterpret_cast<const Vec16*>(x + next_row * cols);
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int i = k * THREADS + tid;
+        if (i < nvec) nxt[k] = ld_stream(xn + i);
+      }
+    }
+    float v[VPT][PV];
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = k * THREADS + tid;
+      if (i < nvec) {
+        Elem<T>::unpack(raw[k], v[k]);
+#pragma unroll
+        for (int e = 0; e < PV; ++e) m = fmaxf(m, v[k][e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < PV; ++e) v[k][e] = -INFINITY;
+      }
+    }
+    m = warp_max(m);
+    if (lane == 0) red_max[warp] = m;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < NW; ++w) m = fmaxf(m, red_max[w]);
+    const float ml = m * kLog2e;
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+#pragma unroll
+      for (int e = 0; e < PV; ++e) {
+        const float t = exp_shifted(v[k][e], ml);  // padding: 2^(-inf) = 0
+        v[k][e] = t;
+        s += t;
+      }
+    }
+    s = warp_sum(s);
+    if (lane == 0) red_sum[warp] = s;
+    __syncthreads();
+    s = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) s += red_sum[w];
+    const float inv = 1.0f / s;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = k * THREADS + tid;
+      if (i < nvec) {
+#pragma unroll
+        for (int e = 0; e < PV; ++e) v[k][e] *= inv;
+        st_stream(yr + i, Elem<T>::pack(v[k]));
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) raw[k] = nxt[k];
+    // red_max is rewritten only after this row's second barrier and red_sum only
+    // after the next row's first one, so neither is overwritten while still read.
   }
 }
 
