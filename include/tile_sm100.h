@@ -156,6 +156,29 @@ typedef struct {
 int32_t tsm100_gemm(tsm100_device_t dev, const tsm100_gemm_desc* desc, const void* a, const void* b,
                     void* c, void* stream);
 
+/* The tensor-core GEMM of tsm100_gemm for callers that must not allocate device
+ * memory; it has no counterpart in the reference.  It takes no device handle
+ * (opening one allocates): it runs on the CUDA device that is current, and the one
+ * word of scratch the kernel needs (where it reports a timed-out wait) lives in a
+ * 256-byte static device array inside the library instead of in cudaMalloc'ed
+ * memory.  Meant for code that runs while a CUDA graph is being captured elsewhere
+ * in the process, for hosts that freeze the device heap after start-up, and for
+ * loops that cannot afford cudaMalloc's implicit synchronisation.  It calls no
+ * cudaMalloc, cudaFree or allocating library routine.
+ *  - Only problems the tensor-core kernel takes are accepted (16-bit inputs,
+ *    16-byte aligned pointers, K and, for row-major B, N multiples of 8, all
+ *    dimensions positive); anything else, or a problem whose scratch need would
+ *    exceed the 256 bytes, is TSM100_ERR_INVALID with a message.
+ *  - The first call on each device looks the array's address up; make that call
+ *    before any stream capture begins.
+ *  - All calls share the array and it keeps the last call's contents; the entry
+ *    point clears the word on `stream` before the kernel.  Two calls whose kernels
+ *    overlap on the GPU (different streams) race on it.
+ *  - status_host may be NULL; otherwise the status word (0, or 0x1000|site) is
+ *    copied there on `stream` after the kernel — read it after synchronising. */
+int32_t tsm100_gemm_static_scratch(const tsm100_gemm_desc* desc, const void* a, const void* b, void* c,
+                                   void* stream, uint32_t* status_host);
+
 /* Fused attention forward, O = softmax(Q K^T / sqrt(d)) V per (batch, head).
  * Q,O: [batch][heads_q][seq][head_dim]; K,V: [batch][heads_kv][seq][head_dim].
  * heads_q == heads_kv, causal = 0: __tile_attention_f32 (tile.rs:218-224,

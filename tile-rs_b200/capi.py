@@ -67,6 +67,7 @@ PROTOTYPES = {
     "tsm100_launch": (c_i32, [c_vp, C.c_char_p, c_u32, P(c_vp), c_u32, c_vp]),
     "tsm100_softmax": (c_i32, [c_vp, P(SoftmaxDesc), c_vp, c_vp, c_vp]),
     "tsm100_gemm": (c_i32, [c_vp, P(GemmDesc), c_vp, c_vp, c_vp, c_vp]),
+    "tsm100_gemm_static_scratch": (c_i32, [P(GemmDesc), c_vp, c_vp, c_vp, c_vp, P(c_u32)]),
     "tsm100_attention": (c_i32, [c_vp, P(AttentionDesc), c_vp, c_vp, c_vp, c_vp, c_vp]),
     "tsm100_softmax_host": (c_i32, [c_vp, P(SoftmaxDesc), c_vp, c_vp]),
     "tsm100_gemm_host": (c_i32, [c_vp, P(GemmDesc), c_vp, c_vp, c_vp]),

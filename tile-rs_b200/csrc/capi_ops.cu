@@ -234,3 +234,84 @@ int32_t tsm100_attention_host(tsm100_device_t dev, const tsm100_attention_desc* 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Tensor-core GEMM for callers that must not allocate device memory.
+//
+// Every other entry point needs a tsm100_device_t, and opening one calls
+// cudaMalloc for the word the kernel reports a timed-out wait in.  Some callers
+// cannot allocate at all: code that runs while a stream is being captured into a
+// CUDA graph (cudaMalloc is refused there), hosts that freeze their device heap
+// after start-up, and latency-critical loops that cannot take the implicit
+// device synchronisation of cudaMalloc / cudaFree.  For them the scratch word
+// lives in the file-scope array below, which every GPU that loads this library
+// holds (256 bytes) until the process exits.
+//
+// In host code `g_static_scratch` is only a stand-in for the symbol, not a device
+// address; the address is asked for once per device with cudaGetSymbolAddress
+// while that device is current, and that pointer is what the kernel receives.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxStaticDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxStaticDevices] = {};
+
+// Device address of g_static_scratch on the current device (looked up on first use).
+int32_t static_scratch_address(void** out) {
+  int dev = -1;
+  TSM_CUDA(cudaGetDevice(&dev), TSM100_ERR_NO_DEVICE);
+  if (dev < 0 || dev >= kMaxStaticDevices) return fail(TSM100_ERR_INVALID, "device ordinal %d is beyond the %d this entry point tracks", dev, kMaxStaticDevices);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    TSM_CUDA(cudaGetSymbolAddress(&p, g_static_scratch), TSM100_ERR_RUNTIME);
+    if (!p) return fail(TSM100_ERR_RUNTIME, "cudaGetSymbolAddress returned a null address for the static scratch");
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return TSM100_OK;
+}
+
+// Scratch the tensor-core GEMM needs for a problem: one status word, whatever the shape.
+size_t gemm_tc_scratch_bytes(const tsm100_gemm_desc*) { return sizeof(uint32_t); }
+
+// The shapes the tensor-core kernel takes (the same conditions under which tsm100_gemm picks it).
+bool gemm_tc_takes(const tsm100_gemm_desc* d, const void* a, const void* b, const void* c) {
+  return d->dtype != TSM100_F32 && ops::aligned16(a) && ops::aligned16(b) && ops::aligned16(c) && d->k % 8 == 0 &&
+         (d->b_transposed || d->n % 8 == 0) && (d->n * ops::dtype_size(d->out_dtype)) % 16 == 0 &&
+         (static_cast<int64_t>((d->m + 127) / 128) * ((d->n + 255) / 256) * d->batch < 0x7fffffff);
+}
+
+}  // namespace
+
+extern "C" int32_t tsm100_gemm_static_scratch(const tsm100_gemm_desc* desc, const void* a, const void* b, void* c,
+                                              void* stream, uint32_t* status_host) {
+  if (!desc || !a || !b || !c) return fail(TSM100_ERR_INVALID, "gemm_static_scratch: null argument");
+  if (!ops::dtype_valid(desc->dtype) || !ops::dtype_valid(desc->out_dtype) || desc->m <= 0 || desc->n <= 0 ||
+      desc->k <= 0 || desc->batch <= 0)
+    return fail(TSM100_ERR_INVALID, "gemm_static_scratch: bad descriptor (every dimension must be positive)");
+  if (!gemm_tc_takes(desc, a, b, c))
+    return fail(TSM100_ERR_INVALID,
+                "gemm_static_scratch: only the tensor-core kernel is offered without allocation: 16-bit inputs, 16-byte "
+                "aligned pointers, K (and N for row-major B) a multiple of 8; use tsm100_gemm for this problem");
+  const size_t need = gemm_tc_scratch_bytes(desc);
+  if (need > kStaticScratchBytes)
+    return fail(TSM100_ERR_INVALID, "gemm_static_scratch: this problem needs %zu bytes of scratch, the static array holds %zu",
+                need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  int32_t st = static_scratch_address(&scratch);
+  if (st != TSM100_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the last call left: the status word must start at zero.
+  TSM_CUDA(cudaMemsetAsync(scratch, 0, need, s), TSM100_ERR_RUNTIME);
+  std::string err;
+  st = ops::gemm(&err, desc, a, b, c, static_cast<uint32_t*>(scratch), stream);
+  if (st != TSM100_OK) return finish(st, err);
+  if (status_host)
+    TSM_CUDA(cudaMemcpyAsync(status_host, scratch, sizeof(uint32_t), cudaMemcpyDeviceToHost, s), TSM100_ERR_RUNTIME);
+  return TSM100_OK;
+}
