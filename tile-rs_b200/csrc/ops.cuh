@@ -20,6 +20,7 @@
 #include "attention_tc.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_tc2.cuh"
 #include "softmax.cuh"
 
 namespace tsm100 {
@@ -245,6 +246,60 @@ inline int32_t gemm_tc_launch(std::string* err, const tsm100_gemm_desc* d, const
   return cuda_ok(err, cudaGetLastError(), "gemm_tc_kernel launch");
 }
 
+// CTA-pair kernel (256 x 256 tile per two SMs), launched as clusters of two.
+template <typename OutT, bool kBT, bool kBf16>
+inline int32_t gemm_tc2_launch(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
+                               uint32_t* status, cudaStream_t s) {
+  namespace g = gemm_tc2;
+  CUtensorMap ta, tb;
+  const uint64_t M = d->m, N = d->n, K = d->k, B = d->batch;
+  int32_t st = make_tmap_16bit_3d(err, &ta, a, K, M, B, K, M * K, g::kBK, g::kCtaM, kBf16);
+  if (st != TSM100_OK) return st;
+  if (kBT)
+    st = make_tmap_16bit_3d(err, &tb, b, K, N, B, K, N * K, g::kBK, g::kCtaN, kBf16);
+  else
+    st = make_tmap_16bit_3d(err, &tb, b, N, K, B, N, K * N, 64, g::kBK, kBf16);
+  if (st != TSM100_OK) return st;
+  gemm_tc::Params p;
+  p.m = static_cast<int32_t>(M);
+  p.n = static_cast<int32_t>(N);
+  p.k = static_cast<int32_t>(K);
+  p.batch = d->batch;
+  p.m_blocks = static_cast<int32_t>((M + g::kPairM - 1) / g::kPairM);
+  p.n_blocks = static_cast<int32_t>((N + g::kBN - 1) / g::kBN);
+  p.c_batch_stride = static_cast<int64_t>(M * N);
+  p.status = status;
+  auto kern = g::gemm_tc2_kernel<OutT, kBT, kBf16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
+  if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(gemm_tc2_kernel)");
+  int sms = 0;
+  st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(g::kThreads);
+  cfg.dynamicSmemBytes = g::kSmemBytes;
+  cfg.stream = s;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1));
+  int max_clusters = 0;
+  e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+  if (e != cudaSuccess || max_clusters < 1) {
+    cudaGetLastError();
+    max_clusters = sms / 2;
+  }
+  const int64_t tiles = static_cast<int64_t>(p.m_blocks) * p.n_blocks * p.batch;
+  const int64_t pairs = std::min<int64_t>(tiles, std::min<int64_t>(max_clusters, sms / 2));
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  e = cudaLaunchKernelEx(&cfg, kern, ta, tb, static_cast<OutT*>(c), p);
+  return cuda_ok(err, e, "gemm_tc2_kernel launch");
+}
+
 // `status` is a device word the tensor-core kernel writes if one of its bounded
 // waits runs out; it must be zero when the launch starts.
 inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
@@ -273,7 +328,10 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
                       (d->b_transposed || d->n % 8 == 0) && (d->n * dtype_size(d->out_dtype)) % 16 == 0 &&
                       (static_cast<int64_t>((d->m + 127) / 128) * ((d->n + 255) / 256) * d->batch < 0x7fffffff);
   if (tma_ok) {
-#define TSM_GEMM_TC(OUT, BT, BF) return gemm_tc_launch<OUT, BT, BF>(err, d, a, b, c, status, s)
+    const bool pair = d->m > 128 && d->n > 128;  // large enough for 256 x 256 tiles on CTA pairs
+#define TSM_GEMM_TC(OUT, BT, BF)                                                     \
+  return pair ? gemm_tc2_launch<OUT, BT, BF>(err, d, a, b, c, status, s) \
+              : gemm_tc_launch<OUT, BT, BF>(err, d, a, b, c, status, s)
     if (bf16) {
       if (out_f32) { if (d->b_transposed) TSM_GEMM_TC(float, true, true); else TSM_GEMM_TC(float, false, true); }
       else { if (d->b_transposed) TSM_GEMM_TC(__nv_bfloat16, true, true); else TSM_GEMM_TC(__nv_bfloat16, false, true); }
