@@ -17,15 +17,19 @@
 // One CTA owns 256 query rows of one (batch, head): two 128-row tiles A and B
 // that take turns on the tensor core while the other is in its softmax.
 //   warp 0      TMA producer: Q once, then K_0,V_0,K_1,V_1,... (128 x 128 tiles,
-//               128-byte swizzle) through a 3-deep ring.  No multicast.
-//   warp 1      MMA issuer (one thread): S_g = Q_g K_j^T and O_g += P_g V_j with
-//               tcgen05.mma, S and O in tensor memory (4 x 128 columns).  V is
+//               128-byte swizzle) through a 5-deep ring.  No multicast.
+//   warp 1      MMA issuer (one thread): S_g = Q_g K_j^T (both operands from shared
+//               memory) and O_g += P_g V_j with P read from TENSOR MEMORY and V
 //               consumed as an MN-major operand straight from its row-major form.
+//               S and O live in tensor memory (4 x 128 columns).
 //   warps 2..5  softmax of tile A, warps 6..9 of tile B: one thread per query
-//               row (TMEM lane), so row max and row sum need no shuffles.  The
-//               running max is only raised when it grows by more than 2^8 (the
-//               accumulator in TMEM is then rescaled); probabilities are written
-//               to shared memory as the 16-bit A operand of the PV product.
+//               row (TMEM lane), so row max and row sum need no shuffles.  A thread
+//               reads its whole 128-wide score row once, and writes the 16-bit
+//               probabilities back over the first 64 columns of the same row, where
+//               the PV product picks them up.  The running max is only raised when
+//               it grows by more than 2^8 (the accumulator in TMEM is then rescaled).
+// Launch order keeps CTAs that share K/V (the query blocks of a head, the heads of
+// a KV group) adjacent so that K/V tiles are served from L2.
 // Roofline: tensor pipe; 4*seq^2*d flop per head (half of it when causal).
 #pragma once
 
@@ -40,7 +44,7 @@ constexpr int kBKV = 128;        // key/value rows per step
 constexpr int kThreads = 320;
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: any 128 x 128 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2; // one 128-row x 64-column swizzled half
-constexpr int kRing = 3;
+constexpr int kRing = 5;
 constexpr int kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
@@ -55,8 +59,8 @@ struct alignas(8) Barriers {
   uint32_t abort_flag;
 };
 
-// Q_A, Q_B, P_A, P_B, ring
-constexpr int kSmemBytes = (4 + kRing) * kTileBytes + sizeof(Barriers) + 1024;
+// Q_A, Q_B, ring
+constexpr int kSmemBytes = (2 + kRing) * kTileBytes + sizeof(Barriers) + 1024;
 
 struct Params {
   int32_t seq;
@@ -73,7 +77,6 @@ __device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-
 template <bool kIsBf16>
 __device__ __forceinline__ float unpack16_lo(uint32_t w) {
   if (kIsBf16) return __uint_as_float(w << 16);
@@ -92,22 +95,22 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_q = smem;                         // 2 tiles
-  uint8_t* smem_p = smem + 2 * kTileBytes;        // 2 tiles
-  uint8_t* smem_kv = smem + 4 * kTileBytes;       // ring
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + (4 + kRing) * kTileBytes);
+  uint8_t* smem_kv = smem + 2 * kTileBytes;       // ring
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + (2 + kRing) * kTileBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   volatile uint32_t* abort_flag = &bars->abort_flag;
 
-  // Heaviest (latest) query blocks first when causal; heads of one KV group adjacent.
-  const int bh_total = p.batch * p.heads_q;
-  const int bh = blockIdx.x % bh_total;
-  const int qb_raw = blockIdx.x / bh_total;
+  // blockIdx -> (head, query block): heads of a KV group vary fastest, then the query
+  // blocks of that group (heaviest first when causal), then the (batch, KV head) groups.
+  const int group = p.heads_q / p.heads_kv;
+  const int hg = blockIdx.x % group;
+  const int t_rest = blockIdx.x / group;
+  const int qb_raw = t_rest % p.q_blocks;
+  const int kvh = t_rest / p.q_blocks;       // flattened (batch, KV head)
+  const int bh = kvh * group + hg;           // flattened (batch, query head)
   const int qb = p.causal ? (p.q_blocks - 1 - qb_raw) : qb_raw;
-  const int b = bh / p.heads_q;
-  const int h = bh - b * p.heads_q;
-  const int kvh = b * p.heads_kv + h / (p.heads_q / p.heads_kv);
   const int q0 = qb * 2 * kBQ;
   const int n_kv_all = (p.seq + kBKV - 1) / kBKV;
   // number of KV steps each tile needs (causal: up to and including its diagonal step)
@@ -136,7 +139,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   __syncthreads();
   ptx::tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  const uint32_t tmem_s = tmem_base;        // S_A at +0,   S_B at +128
+  const uint32_t tmem_s = tmem_base;        // S_A at +0, S_B at +128; P_g overlays columns [0, 64) of S_g
   const uint32_t tmem_o = tmem_base + 256;  // O_A at +256, O_B at +384
 
   if (warp == 0) {
@@ -181,7 +184,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         ptx::tcgen05_fence_after_thread_sync();
         return r;
       };
-      // S_g = Q_g K^T : both operands K-major, K = head_dim in two 64-wide halves
+      // S_g = Q_g K^T : both operands K-major in shared memory, K = head_dim in two 64-wide halves
       auto issue_qk = [&](int g, int idx) {
         const uint32_t qa = ptx::smem_u32(smem_q + g * kTileBytes);
         const uint32_t ka = ptx::smem_u32(smem_kv + (idx % kRing) * kTileBytes);
@@ -193,14 +196,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         ptx::tcgen05_commit(&bars->s_full[g]);
       };
-      // O_g (+)= P_g V : P K-major (K = kv index), V MN-major (N = head_dim)
+      // O_g (+)= P_g V : P from tensor memory (16 K-elements = 8 columns per step), V MN-major
       auto issue_pv = [&](int g, int idx, bool accumulate) {
-        const uint32_t pa = ptx::smem_u32(smem_p + g * kTileBytes);
         const uint32_t va = ptx::smem_u32(smem_kv + (idx % kRing) * kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < kBKV / 16; ++kk) {
-          const uint32_t poff = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-          ptx::tcgen05_mma_f16_ss(tmem_o + g * 128, ptx::smem_desc(kmajor, pa + poff),
+          ptx::tcgen05_mma_f16_ts(tmem_o + g * 128, tmem_s + g * 128 + kk * 8,
                                   ptx::smem_desc(v_mnmajor, va + kk * 2048), idesc_pv,
                                   (accumulate || kk != 0) ? 1u : 0u);
         }
@@ -212,6 +213,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         return r;
       };
 
+      // Issue order per step j: QK_A(j), PV_B(j-1), QK_B(j), PV_A(j).  QK_g(j+1) follows
+      // PV_g(j) in this (in-order) stream, so overwriting S_g never overtakes the read of P_g.
       for (int j = 0; j < n_b && ok; ++j) {
         const int k_idx = 2 * j, v_idx = 2 * j + 1;
         if (j < n_a) {
@@ -252,8 +255,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t ts = tmem_s + g * 128 + lane_base;
     const uint32_t to = tmem_o + g * 128 + lane_base;
-    uint8_t* prow = smem_p + g * kTileBytes + r * 128;
-    const int sw = r & 7;
     const float sl2 = p.scale_log2;
 
     float m_used = -INFINITY;  // running max in raw score units
@@ -269,83 +270,81 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const int col0 = j * kBKV;
       const bool masked = col0 + kBKV - 1 > limit;
 
-      // pass 1: row max of this step
+      // the whole score row of this step, read once
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32b_x32(ts + c * 32, v[c]);
+      ptx::tmem_ld_wait();
+
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(ts + c * 32, v);
-        ptx::tmem_ld_wait();
-        if (masked) {
+      if (masked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            mx = fmaxf(mx, (col0 + c * 32 + i <= limit) ? __uint_as_float(v[i]) : -INFINITY);
-        } else {
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-        }
+          for (int i = 0; i < 32; ++i) {
+            if (col0 + c * 32 + i > limit) v[c][i] = 0xff800000u;  // -inf
+            mx = fmaxf(mx, __uint_as_float(v[c][i]));
+          }
+      } else {
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
       const float m_new = fmaxf(m_used, mx);
-      bool need = false;
       if (j == 0) {
         m_used = m_new;
       } else {
-        need = (m_new - m_used) * sl2 > kRescaleThreshold;
-        // PV of the previous step must have retired: it reads P and updates O.
-        ready = ptx::mbar_wait(&bars->pv_done[g], (j - 1) & 1u, abort_flag, p.status, 18 + g);
-        if (!__all_sync(0xffffffffu, ready)) {
-          alive = false;
-          break;
-        }
-        ptx::tcgen05_fence_after_thread_sync();
+        const bool need = (m_new - m_used) * sl2 > kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {
+          // O_g is rescaled in place; PV of the previous step has retired (S of this
+          // step was produced after it on the in-order tensor pipe), the wait is a formality.
+          ready = ptx::mbar_wait(&bars->pv_done[g], (j - 1) & 1u, abort_flag, p.status, 18 + g);
+          if (!__all_sync(0xffffffffu, ready)) {
+            alive = false;
+            break;
+          }
+          ptx::tcgen05_fence_after_thread_sync();
           const float alpha = need ? ptx::ex2_approx((m_used - m_new) * sl2) : 1.0f;
           if (need) m_used = m_new;
           l *= alpha;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            uint32_t v[32];
-            ptx::tmem_ld_32x32b_x32(to + c * 32, v);
+            uint32_t ov[32];
+            ptx::tmem_ld_32x32b_x32(to + c * 32, ov);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            ptx::tmem_st_32x32b_x32(to + c * 32, v);
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            ptx::tmem_st_32x32b_x32(to + c * 32, ov);
           }
           ptx::tmem_st_wait();
         }
       }
 
-      // pass 2: probabilities -> shared memory (K-major, 128-byte swizzle), row sum
+      // probabilities: exp2, round to 16 bit, two per 32-bit TMEM column over S_g[:, 0:64)
       const float ms = m_used * sl2;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(ts + c * 32, v);
-        ptx::tmem_ld_wait();
-        float pr[32];
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = ptx::ex2_approx(fmaf(__uint_as_float(v[i]), sl2, -ms));
-          if (masked && (col0 + c * 32 + i > limit)) e = 0.f;
-          pr[i] = e;
+          const int c = h2 * 2 + (i >> 4);
+          const int e0 = (i & 15) * 2;
+          const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(v[c][e0]), sl2, -ms));      // 2^(-inf) = 0
+          const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(v[c][e0 + 1]), sl2, -ms));
+          pk[i] = pack16x2<kIsBf16>(p0, p1);
+          // The row sum is taken over the ROUNDED probabilities, the ones the PV product
+          // really uses, so that O / l stays a convex combination of V rows.
+          l4[i & 3] += unpack16_lo<kIsBf16>(pk[i]) + unpack16_hi<kIsBf16>(pk[i]);
         }
-        uint8_t* half_base = prow + (c >> 1) * kHalfBytes;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          uint32_t w[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            w[u] = pack16x2<kIsBf16>(pr[8 * t + 2 * u], pr[8 * t + 2 * u + 1]);
-            // The row sum is taken over the ROUNDED probabilities, the ones the PV
-            // product really uses, so that O / l stays a convex combination of V rows.
-            l += unpack16_lo<kIsBf16>(w[u]) + unpack16_hi<kIsBf16>(w[u]);
-          }
-          const int i16 = (c & 1) * 4 + t;
-          *reinterpret_cast<uint4*>(half_base + ((i16 ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+        ptx::tmem_st_32x32b_x32(ts + h2 * 32, pk);
       }
-      ptx::fence_proxy_async_smem();            // P visible to the tensor core's reads
-      ptx::tcgen05_fence_before_thread_sync();  // S reads and O writes ordered before the arrive
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      ptx::tmem_st_wait();
+      ptx::tcgen05_fence_before_thread_sync();  // P stores (and O rescale) ordered before the arrive
       ptx::mbar_arrive(&bars->p_ready[g]);
     }
 
@@ -357,17 +356,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         uint16_t* orow = o + (static_cast<int64_t>(bh) * p.seq + qrow) * kD;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32b_x32(to + c * 32, v);
+          uint32_t ov[32];
+          ptx::tmem_ld_32x32b_x32(to + c * 32, ov);
           ptx::tmem_ld_wait();
           if (qrow < p.seq) {
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
               uint4 w;
-              w.x = pack16x2<kIsBf16>(__uint_as_float(v[8 * t + 0]) * inv, __uint_as_float(v[8 * t + 1]) * inv);
-              w.y = pack16x2<kIsBf16>(__uint_as_float(v[8 * t + 2]) * inv, __uint_as_float(v[8 * t + 3]) * inv);
-              w.z = pack16x2<kIsBf16>(__uint_as_float(v[8 * t + 4]) * inv, __uint_as_float(v[8 * t + 5]) * inv);
-              w.w = pack16x2<kIsBf16>(__uint_as_float(v[8 * t + 6]) * inv, __uint_as_float(v[8 * t + 7]) * inv);
+              w.x = pack16x2<kIsBf16>(__uint_as_float(ov[8 * t + 0]) * inv, __uint_as_float(ov[8 * t + 1]) * inv);
+              w.y = pack16x2<kIsBf16>(__uint_as_float(ov[8 * t + 2]) * inv, __uint_as_float(ov[8 * t + 3]) * inv);
+              w.z = pack16x2<kIsBf16>(__uint_as_float(ov[8 * t + 4]) * inv, __uint_as_float(ov[8 * t + 5]) * inv);
+              w.w = pack16x2<kIsBf16>(__uint_as_float(ov[8 * t + 6]) * inv, __uint_as_float(ov[8 * t + 7]) * inv);
               reinterpret_cast<uint4*>(orow + c * 32)[t] = w;
             }
           }

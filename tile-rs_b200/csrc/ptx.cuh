@@ -318,6 +318,21 @@ __device__ __forceinline__ void tcgen05_mma_f16_ss(uint32_t d_tmem, uint64_t a_d
       : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (M = 128 rows = TMEM lanes, K-major)
+// is read from tensor memory, where 16-bit elements are packed two per 32-bit column
+// (element 2c in the low half of column c).  Issued by ONE thread.
+__device__ __forceinline__ void tcgen05_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // ---------------------------------------------------------------------------
 // tcgen05.ld: tensor memory -> registers.  Shape 32x32b: lane i of the warp
 // reads TMEM lane (32 * (warp_id % 4) + i); register j holds column base + j.
