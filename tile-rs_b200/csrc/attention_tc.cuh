@@ -16,13 +16,13 @@
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row tiles A and B
 // that take turns on the tensor core while the other is in its softmax.
-//   warp 0      TMA producer: Q once, then K_0,V_0,K_1,V_1,... (128 x 128 tiles,
+//   warp 8      TMA producer: Q once, then K_0,V_0,K_1,V_1,... (128 x 128 tiles,
 //               128-byte swizzle) through a 5-deep ring.  No multicast.
-//   warp 1      MMA issuer (one thread): S_g = Q_g K_j^T (both operands from shared
+//   warp 9      MMA issuer (one thread): S_g = Q_g K_j^T (both operands from shared
 //               memory) and O_g += P_g V_j with P read from TENSOR MEMORY and V
 //               consumed as an MN-major operand straight from its row-major form.
 //               S and O live in tensor memory (4 x 128 columns).
-//   warps 2..5  softmax of tile A, warps 6..9 of tile B: one thread per query
+//   warps 0..3  softmax of tile A, warps 4..7 of tile B: one thread per query
 //               row (TMEM lane), so row max and row sum need no shuffles.  A thread
 //               reads its whole 128-wide score row once, and writes the 16-bit
 //               probabilities back over the first 64 columns of the same row, where
@@ -41,7 +41,9 @@ namespace attn {
 constexpr int kD = 128;          // head_dim
 constexpr int kBQ = 128;         // query rows per tile (two tiles per CTA)
 constexpr int kBKV = 128;        // key/value rows per step
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;         // warps 0..3 softmax A, 4..7 softmax B, 8 TMA, 9 MMA, 10..11 idle
+constexpr int kRegsSoftmax = 224;      // register budget after setmaxnreg (launch: 168 per thread)
+constexpr int kRegsOther = 56;
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: any 128 x 128 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2; // one 128-row x 64-column swizzled half
 constexpr int kRing = 5;
@@ -131,7 +133,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == 9) {
     ptx::tmem_alloc(&bars->tmem_base, kTmemCols);
     ptx::tmem_relinquish_alloc_permit();
   }
@@ -142,8 +144,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t tmem_s = tmem_base;        // S_A at +0, S_B at +128; P_g overlays columns [0, 64) of S_g
   const uint32_t tmem_o = tmem_base + 256;  // O_A at +256, O_B at +384
 
-  if (warp == 0) {
+  // The non-softmax warpgroup (warps 8..11) gives most of its registers to the softmax
+  // warpgroups; each role branch starts with its own setmaxnreg so that the register
+  // budget is unambiguous inside it.
+  if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
+    ptx::setmaxnreg_dec<kRegsOther>();
     if (lane == 0) {
       ptx::prefetch_tensormap(&tmap_q);
       ptx::prefetch_tensormap(&tmap_k);
@@ -169,8 +175,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                            row0, kvh);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 9) {
     // ------------------------------ MMA issuer --------------------------------
+    ptx::setmaxnreg_dec<kRegsOther>();
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBQ, kBKV, false, false, kIsBf16);
       constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBQ, kD, false, true, kIsBf16);
@@ -244,9 +251,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
     }
+  } else if (warp >= 10) {
+    ptx::setmaxnreg_dec<kRegsOther>();
   } else {
     // ------------------------------ softmax / output ---------------------------
-    const int g = (warp - 2) >> 2;          // 0: tile A, 1: tile B
+    ptx::setmaxnreg_inc<kRegsSoftmax>();
+    const int g = warp >> 2;          // 0: tile A, 1: tile B
     const int quad = warp & 3;              // TMEM lanes this warp may touch
     const int r = quad * 32 + lane;         // row inside the tile == TMEM lane
     const int n_g = g == 0 ? n_a : n_b;
@@ -290,7 +300,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
+          for (int i = 0; i < 32; i += 2)  // three-input max: 64 instructions for 128 values
+            mx4[(i >> 1) & 3] = ptx::fmax3(mx4[(i >> 1) & 3], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
       const float m_new = fmaxf(m_used, mx);
@@ -383,7 +394,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   }
   ptx::tcgen05_fence_before_thread_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 9) {
     ptx::tcgen05_fence_after_thread_sync();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
