@@ -183,39 +183,49 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBQ, kD, false, true, kIsBf16);
       constexpr uint64_t kmajor = ptx::make_smem_desc_base(16, 1024);
       constexpr uint64_t v_mnmajor = ptx::make_smem_desc_base(kHalfBytes, 1024);
-      bool ok = ptx::mbar_wait(&bars->q_full, 0, abort_flag, p.status, 12);
+      bool ok = ptx::mbar_wait_relaxed(&bars->q_full, 0, abort_flag, p.status, 12);
       ptx::tcgen05_fence_after_thread_sync();
 
+      // The issuing thread's waits are relaxed: it only hands TMA-written shared memory to
+      // the tensor core (same async proxy), and tensor memory behind the tcgen05 fence; an
+      // acquiring wait costs this thread (and so the tensor pipe) about twice as long.
       auto wait_kv = [&](int idx) -> bool {
-        const bool r = ptx::mbar_wait(&bars->kv_full[idx % kRing], (idx / kRing) & 1u, abort_flag, p.status, 13);
-        ptx::tcgen05_fence_after_thread_sync();
-        return r;
+        return ptx::mbar_wait_relaxed(&bars->kv_full[idx % kRing], (idx / kRing) & 1u, abort_flag, p.status, 13);
       };
+      // Issuing one 128 x 128 x 16 MMA costs this thread nearly as long as the tensor core
+      // needs to execute it, so everything per MMA is reduced to one add on the low word
+      // of each descriptor (the start-address field; the high words are constants).
+      constexpr uint32_t k_hi = static_cast<uint32_t>(kmajor >> 32), v_hi = static_cast<uint32_t>(v_mnmajor >> 32);
+      constexpr uint32_t k_lo_base = static_cast<uint32_t>(kmajor), v_lo_base = static_cast<uint32_t>(v_mnmajor);
+      const uint32_t q_lo = k_lo_base | (ptx::smem_u32(smem_q) >> 4);       // + g * (kTileBytes >> 4)
+      const uint32_t ring_k_lo = k_lo_base | (ptx::smem_u32(smem_kv) >> 4);  // + slot * (kTileBytes >> 4)
+      const uint32_t ring_v_lo = v_lo_base | (ptx::smem_u32(smem_kv) >> 4);
+      auto desc64 = [](uint32_t hi, uint32_t lo) -> uint64_t { return (static_cast<uint64_t>(hi) << 32) | lo; };
       // S_g = Q_g K^T : both operands K-major in shared memory, K = head_dim in two 64-wide halves
       auto issue_qk = [&](int g, int idx) {
-        const uint32_t qa = ptx::smem_u32(smem_q + g * kTileBytes);
-        const uint32_t ka = ptx::smem_u32(smem_kv + (idx % kRing) * kTileBytes);
+        const uint32_t a_lo = q_lo + g * (kTileBytes >> 4);
+        const uint32_t b_lo = ring_k_lo + (idx % kRing) * (kTileBytes >> 4);
+        const uint32_t d = tmem_s + g * 128;
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-          ptx::tcgen05_mma_f16_ss(tmem_s + g * 128, ptx::smem_desc(kmajor, qa + off),
-                                  ptx::smem_desc(kmajor, ka + off), idesc_qk, kk != 0 ? 1u : 0u);
+          constexpr int kHalf16 = kHalfBytes >> 4;
+          const uint32_t off = (kk >> 2) * kHalf16 + (kk & 3) * 2;  // in 16-byte units
+          ptx::tcgen05_mma_f16_ss(d, desc64(k_hi, a_lo + off), desc64(k_hi, b_lo + off), idesc_qk, kk != 0 ? 1u : 0u);
         }
         ptx::tcgen05_commit(&bars->s_full[g]);
       };
       // O_g (+)= P_g V : P from tensor memory (16 K-elements = 8 columns per step), V MN-major
       auto issue_pv = [&](int g, int idx, bool accumulate) {
-        const uint32_t va = ptx::smem_u32(smem_kv + (idx % kRing) * kTileBytes);
+        const uint32_t b_lo = ring_v_lo + (idx % kRing) * (kTileBytes >> 4);
+        const uint32_t d = tmem_o + g * 128, a = tmem_s + g * 128;
+        ptx::tcgen05_mma_f16_ts(d, a, desc64(v_hi, b_lo), idesc_pv, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < kBKV / 16; ++kk) {
-          ptx::tcgen05_mma_f16_ts(tmem_o + g * 128, tmem_s + g * 128 + kk * 8,
-                                  ptx::smem_desc(v_mnmajor, va + kk * 2048), idesc_pv,
-                                  (accumulate || kk != 0) ? 1u : 0u);
-        }
+        for (int kk = 1; kk < kBKV / 16; ++kk)
+          ptx::tcgen05_mma_f16_ts(d, a + kk * 8, desc64(v_hi, b_lo + kk * (2048 >> 4)), idesc_pv, 1u);
         ptx::tcgen05_commit(&bars->pv_done[g]);
       };
       auto wait_p = [&](int g, int j) -> bool {
-        const bool r = ptx::mbar_wait(&bars->p_ready[g], j & 1u, abort_flag, p.status, 14 + g);
+        const bool r = ptx::mbar_wait_relaxed(&bars->p_ready[g], j & 1u, abort_flag, p.status, 14 + g);
         ptx::tcgen05_fence_after_thread_sync();
         return r;
       };
@@ -234,7 +244,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           issue_pv(1, v_idx - 2, j - 1 > 0);
           ptx::tcgen05_commit(&bars->kv_empty[(v_idx - 2) % kRing]);
         }
-        if (!(ok = wait_kv(k_idx))) break;
+        if (j >= n_a && !(ok = wait_kv(k_idx))) break;  // otherwise already waited for before QK_A
         issue_qk(1, k_idx);  // last reader of K_j
         ptx::tcgen05_commit(&bars->kv_empty[k_idx % kRing]);
         if (j < n_a) {

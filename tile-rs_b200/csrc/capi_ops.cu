@@ -315,3 +315,9 @@ extern "C" int32_t tsm100_gemm_static_scratch(const tsm100_gemm_desc* desc, cons
     TSM_CUDA(cudaMemcpyAsync(status_host, scratch, sizeof(uint32_t), cudaMemcpyDeviceToHost, s), TSM100_ERR_RUNTIME);
   return TSM100_OK;
 }
+
+#ifdef TSM100_TRACE
+extern "C" int32_t tsm100_debug_read_attn_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, tsm100::attn::g_attn_trace, sizeof(tsm100::attn::g_attn_trace)) == cudaSuccess ? 0 : 6;
+}
+#endif

@@ -157,7 +157,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         ptx::tcgen05_fence_after_thread_sync();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(&bars->full[stage], phase, abort_flag, p.status, 33)) {
+          if (!ptx::mbar_wait_relaxed(&bars->full[stage], phase, abort_flag, p.status, 33)) {  // relaxed: the data goes straight to the async proxy
             ok = false;
             break;
           }

@@ -110,6 +110,41 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// The same bounded wait without acquire semantics.  For threads that only hand the
+// data on to the async proxy (a tcgen05.mma issuer reading TMA-written shared memory,
+// or tensor memory behind tcgen05.fence::after_thread_sync): the relaxed test costs
+// the issuing thread well under half of the acquiring one.
+__device__ __forceinline__ bool mbar_try_wait_relaxed(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.relaxed.cta.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t* status, uint32_t site) {
+  if (mbar_try_wait_relaxed(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_relaxed(bar, parity)) return true;
+    if ((++spins & 0x3ffu) == 0u) {
+      if (*abort_flag != 0u) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1u;
+        atomicCAS(status, kStatusOk, kStatusWaitTimeout | site);
+        return false;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // TMA: tiled bulk tensor copies.  No form here carries a cluster-multicast
 // qualifier; every CTA fetches its own tiles.
@@ -392,6 +427,56 @@ template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
+// Packed pairs of f32 (one 64-bit register pair): the FMA pipe takes one such
+// instruction per two lanes-worth of work, halving the issue slots of scalar code.
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pack_f32x2(float lo, float hi) {
+  f32x2_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(f32x2_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2_t fma_f32x2(f32x2_t a, f32x2_t b, f32x2_t c) {
+  f32x2_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2_t add_f32x2(f32x2_t a, f32x2_t b) {
+  f32x2_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// 2^t for a pair of t <= 0 on the FMA pipe (no MUFU): round t to the nearest integer n
+// with the 1.5*2^23 trick, evaluate a cubic for 2^(t-n) on [-0.5, 0.5] (relative error
+// 7.5e-5, far below the 16-bit rounding that follows) and add n to the exponent field.
+// t is clamped at -125 so the exponent cannot wrap; 2^-125 stands in for zero.
+__device__ __forceinline__ void exp2_poly_x2(f32x2_t t2, float& out_lo, float& out_hi) {
+  float lo, hi;
+  unpack_f32x2(t2, lo, hi);
+  t2 = pack_f32x2(fmaxf(lo, -125.0f), fmaxf(hi, -125.0f));
+  const f32x2_t magic = pack_f32x2(12582912.0f, 12582912.0f);
+  const f32x2_t neg_magic = pack_f32x2(-12582912.0f, -12582912.0f);
+  const f32x2_t neg_one = pack_f32x2(-1.0f, -1.0f);
+  const f32x2_t c0 = pack_f32x2(0.9999281168f, 0.9999281168f);
+  const f32x2_t c1 = pack_f32x2(0.6932609677f, 0.6932609677f);
+  const f32x2_t c2 = pack_f32x2(0.2426108569f, 0.2426108569f);
+  const f32x2_t c3 = pack_f32x2(0.0551714599f, 0.0551714599f);
+  const f32x2_t r2 = add_f32x2(t2, magic);           // low mantissa bits = round(t)
+  const f32x2_t n2 = add_f32x2(r2, neg_magic);       // round(t) as a float
+  const f32x2_t f2 = fma_f32x2(n2, neg_one, t2);     // t - round(t)
+  f32x2_t p2 = fma_f32x2(c3, f2, c2);
+  p2 = fma_f32x2(p2, f2, c1);
+  p2 = fma_f32x2(p2, f2, c0);
+  float rl, rh, pl, ph;
+  unpack_f32x2(r2, rl, rh);
+  unpack_f32x2(p2, pl, ph);
+  out_lo = __uint_as_float(__float_as_uint(pl) + (__float_as_uint(rl) << 23));
+  out_hi = __uint_as_float(__float_as_uint(ph) + (__float_as_uint(rh) << 23));
+}
+
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
