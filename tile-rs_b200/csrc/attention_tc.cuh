@@ -49,6 +49,10 @@ constexpr int kHalfBytes = kTileBytes / 2; // one 128-row x 64-column swizzled h
 constexpr int kRing = 5;
 constexpr int kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef TSM100_POLY_PAIRS
+#define TSM100_POLY_PAIRS 2
+#endif
+constexpr int kPolyPairs = TSM100_POLY_PAIRS;  // of every 8 pairs of exponentials, how many avoid MUFU
 
 struct alignas(8) Barriers {
   uint64_t q_full;
@@ -72,6 +76,19 @@ struct Params {
   float scale_log2;        // (1/sqrt(d)) * log2(e)
   uint32_t* status;
 };
+
+#ifdef TSM100_TRACE
+// Development aid (never compiled into the library): per-step clock stamps of CTA 0.
+__device__ long long g_attn_trace[3 * 64 * 8];
+#define TSM_TRACE(role, j, slot)                                                                  \
+  do {                                                                                            \
+    if (blockIdx.x == 0 && (j) < 64) g_attn_trace[((role) * 64 + (j)) * 8 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define TSM_TRACE(role, j, slot) \
+  do {                           \
+  } while (0)
+#endif
 
 template <bool kIsBf16>
 __device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
@@ -234,23 +251,31 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       // PV_g(j) in this (in-order) stream, so overwriting S_g never overtakes the read of P_g.
       for (int j = 0; j < n_b && ok; ++j) {
         const int k_idx = 2 * j, v_idx = 2 * j + 1;
+        TSM_TRACE(1, j, 0);
         if (j < n_a) {
           if (!(ok = wait_kv(k_idx))) break;
+          TSM_TRACE(1, j, 1);
           issue_qk(0, k_idx);
         }
         if (j >= 1) {  // PV_B(j-1): last reader of V_{j-1}
           if (!(ok = wait_kv(v_idx - 2))) break;
+          TSM_TRACE(1, j, 2);
           if (!(ok = wait_p(1, j - 1))) break;
+          TSM_TRACE(1, j, 3);
           issue_pv(1, v_idx - 2, j - 1 > 0);
           ptx::tcgen05_commit(&bars->kv_empty[(v_idx - 2) % kRing]);
         }
         if (j >= n_a && !(ok = wait_kv(k_idx))) break;  // otherwise already waited for before QK_A
+        TSM_TRACE(1, j, 4);
         issue_qk(1, k_idx);  // last reader of K_j
         ptx::tcgen05_commit(&bars->kv_empty[k_idx % kRing]);
         if (j < n_a) {
           if (!(ok = wait_kv(v_idx))) break;
+          TSM_TRACE(1, j, 5);
           if (!(ok = wait_p(0, j))) break;
+          TSM_TRACE(1, j, 6);
           issue_pv(0, v_idx, j > 0);
+          TSM_TRACE(1, j, 7);
         }
       }
       if (ok) {
@@ -280,13 +305,23 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     float m_used = -INFINITY;  // running max in raw score units
     float l = 0.f;
     bool alive = true;
+    const bool tracer = (threadIdx.x & 127) == 0;
     for (int j = 0; j < n_g; ++j) {
+      if (tracer) TSM_TRACE(g * 2, j, 0);
       bool ready = ptx::mbar_wait(&bars->s_full[g], j & 1u, abort_flag, p.status, 16 + g);
       if (!__all_sync(0xffffffffu, ready)) {
         alive = false;
         break;
       }
       ptx::tcgen05_fence_after_thread_sync();
+      if (tracer) TSM_TRACE(g * 2, j, 1);
+#ifdef TSM100_DEBUG_SKIP_SOFTMAX
+      if (j >= 0) {  // development aid: hand the tile straight back, to time the MMA pipeline alone
+        ptx::tcgen05_fence_before_thread_sync();
+        ptx::mbar_arrive(&bars->p_ready[g]);
+        continue;
+      }
+#endif
       const int col0 = j * kBKV;
       const bool masked = col0 + kBKV - 1 > limit;
 
@@ -295,6 +330,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
       for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32b_x32(ts + c * 32, v[c]);
       ptx::tmem_ld_wait();
+      if (tracer) TSM_TRACE(g * 2, j, 2);
 
       float mx = -INFINITY;
       if (masked) {
@@ -315,6 +351,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
       const float m_new = fmaxf(m_used, mx);
+      if (tracer) TSM_TRACE(g * 2, j, 3);
       if (j == 0) {
         m_used = m_new;
       } else {
@@ -345,8 +382,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
 
       // probabilities: exp2, round to 16 bit, two per 32-bit TMEM column over S_g[:, 0:64)
+      // Of every 8 pairs, kPolyPairs go through the FMA-pipe polynomial and the rest through
+      // MUFU ex2, so that neither pipe alone bounds the exponentials.  The row sum adds the
+      // f32 probabilities before they are rounded (packed adds, two per instruction).
       const float ms = m_used * sl2;
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      const ptx::f32x2_t sl2x2 = ptx::pack_f32x2(sl2, sl2);
+      const ptx::f32x2_t nmsx2 = ptx::pack_f32x2(-ms, -ms);
+      ptx::f32x2_t lsum[2] = {0ull, 0ull};  // (+0.0f, +0.0f)
 #pragma unroll
       for (int h2 = 0; h2 < 2; ++h2) {
         uint32_t pk[32];
@@ -354,19 +396,31 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         for (int i = 0; i < 32; ++i) {
           const int c = h2 * 2 + (i >> 4);
           const int e0 = (i & 15) * 2;
-          const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(v[c][e0]), sl2, -ms));      // 2^(-inf) = 0
-          const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(v[c][e0 + 1]), sl2, -ms));
+          const ptx::f32x2_t t2 = ptx::fma_f32x2(
+              ptx::pack_f32x2(__uint_as_float(v[c][e0]), __uint_as_float(v[c][e0 + 1])), sl2x2, nmsx2);
+          float p0, p1;
+          if ((i & 7) < kPolyPairs) {
+            ptx::exp2_poly_x2(t2, p0, p1);
+          } else {
+            float t0, t1;
+            ptx::unpack_f32x2(t2, t0, t1);
+            p0 = ptx::ex2_approx(t0);  // 2^(-inf) = 0
+            p1 = ptx::ex2_approx(t1);
+          }
           pk[i] = pack16x2<kIsBf16>(p0, p1);
-          // The row sum is taken over the ROUNDED probabilities, the ones the PV product
-          // really uses, so that O / l stays a convex combination of V rows.
-          l4[i & 3] += unpack16_lo<kIsBf16>(pk[i]) + unpack16_hi<kIsBf16>(pk[i]);
+          lsum[i & 1] = ptx::add_f32x2(lsum[i & 1], ptx::pack_f32x2(p0, p1));
         }
         ptx::tmem_st_32x32b_x32(ts + h2 * 32, pk);
       }
+      float l4[4];
+      ptx::unpack_f32x2(lsum[0], l4[0], l4[1]);
+      ptx::unpack_f32x2(lsum[1], l4[2], l4[3]);
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      if (tracer) TSM_TRACE(g * 2, j, 4);
       ptx::tmem_st_wait();
       ptx::tcgen05_fence_before_thread_sync();  // P stores (and O rescale) ordered before the arrive
       ptx::mbar_arrive(&bars->p_ready[g]);
+      if (tracer) TSM_TRACE(g * 2, j, 5);
     }
 
     if (alive && n_g > 0) {
