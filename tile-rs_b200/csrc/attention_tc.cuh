@@ -195,19 +195,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   } else if (warp == 9) {
     // ------------------------------ MMA issuer --------------------------------
     ptx::setmaxnreg_dec<kRegsOther>();
-    if (lane == 0) {
+    {  // the whole warp runs the loop (uniform control flow, uniform operands); one elected lane issues
       constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBQ, kBKV, false, false, kIsBf16);
       constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBQ, kD, false, true, kIsBf16);
       constexpr uint64_t kmajor = ptx::make_smem_desc_base(16, 1024);
       constexpr uint64_t v_mnmajor = ptx::make_smem_desc_base(kHalfBytes, 1024);
-      bool ok = ptx::mbar_wait_relaxed(&bars->q_full, 0, abort_flag, p.status, 12);
+      bool ok = __all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&bars->q_full, 0, abort_flag, p.status, 12));
       ptx::tcgen05_fence_after_thread_sync();
 
       // The issuing thread's waits are relaxed: it only hands TMA-written shared memory to
       // the tensor core (same async proxy), and tensor memory behind the tcgen05 fence; an
       // acquiring wait costs this thread (and so the tensor pipe) about twice as long.
       auto wait_kv = [&](int idx) -> bool {
-        return ptx::mbar_wait_relaxed(&bars->kv_full[idx % kRing], (idx / kRing) & 1u, abort_flag, p.status, 13);
+        const bool r = ptx::mbar_wait_relaxed(&bars->kv_full[idx % kRing], (idx / kRing) & 1u, abort_flag, p.status, 13);
+        return __all_sync(0xffffffffu, r);  // the warp stays converged, also when a wait gives up
       };
       // Issuing one 128 x 128 x 16 MMA costs this thread nearly as long as the tensor core
       // needs to execute it, so everything per MMA is reduced to one add on the low word
@@ -223,6 +224,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const uint32_t a_lo = q_lo + g * (kTileBytes >> 4);
         const uint32_t b_lo = ring_k_lo + (idx % kRing) * (kTileBytes >> 4);
         const uint32_t d = tmem_s + g * 128;
+        if (ptx::elect_one_sync()) {
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
           constexpr int kHalf16 = kHalfBytes >> 4;
@@ -230,21 +232,26 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           ptx::tcgen05_mma_f16_ss(d, desc64(k_hi, a_lo + off), desc64(k_hi, b_lo + off), idesc_qk, kk != 0 ? 1u : 0u);
         }
         ptx::tcgen05_commit(&bars->s_full[g]);
+        }
+        __syncwarp();
       };
       // O_g (+)= P_g V : P from tensor memory (16 K-elements = 8 columns per step), V MN-major
       auto issue_pv = [&](int g, int idx, bool accumulate) {
         const uint32_t b_lo = ring_v_lo + (idx % kRing) * (kTileBytes >> 4);
         const uint32_t d = tmem_o + g * 128, a = tmem_s + g * 128;
+        if (ptx::elect_one_sync()) {
         ptx::tcgen05_mma_f16_ts(d, a, desc64(v_hi, b_lo), idesc_pv, accumulate ? 1u : 0u);
 #pragma unroll
         for (int kk = 1; kk < kBKV / 16; ++kk)
           ptx::tcgen05_mma_f16_ts(d, a + kk * 8, desc64(v_hi, b_lo + kk * (2048 >> 4)), idesc_pv, 1u);
         ptx::tcgen05_commit(&bars->pv_done[g]);
+        }
+        __syncwarp();
       };
       auto wait_p = [&](int g, int j) -> bool {
         const bool r = ptx::mbar_wait_relaxed(&bars->p_ready[g], j & 1u, abort_flag, p.status, 14 + g);
         ptx::tcgen05_fence_after_thread_sync();
-        return r;
+        return __all_sync(0xffffffffu, r);
       };
 
       // Issue order per step j: QK_A(j), PV_B(j-1), QK_B(j), PV_A(j).  QK_g(j+1) follows
@@ -263,12 +270,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           if (!(ok = wait_p(1, j - 1))) break;
           TSM_TRACE(1, j, 3);
           issue_pv(1, v_idx - 2, j - 1 > 0);
-          ptx::tcgen05_commit(&bars->kv_empty[(v_idx - 2) % kRing]);
+          if (ptx::elect_one_sync()) ptx::tcgen05_commit(&bars->kv_empty[(v_idx - 2) % kRing]);
         }
         if (j >= n_a && !(ok = wait_kv(k_idx))) break;  // otherwise already waited for before QK_A
         TSM_TRACE(1, j, 4);
         issue_qk(1, k_idx);  // last reader of K_j
-        ptx::tcgen05_commit(&bars->kv_empty[k_idx % kRing]);
+        if (ptx::elect_one_sync()) ptx::tcgen05_commit(&bars->kv_empty[k_idx % kRing]);
         if (j < n_a) {
           if (!(ok = wait_kv(v_idx))) break;
           TSM_TRACE(1, j, 5);
@@ -282,7 +289,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const int v_idx = 2 * (n_b - 1) + 1;
         if (wait_kv(v_idx) && wait_p(1, n_b - 1)) {
           issue_pv(1, v_idx, n_b - 1 > 0);
-          ptx::tcgen05_commit(&bars->kv_empty[v_idx % kRing]);
+          if (ptx::elect_one_sync()) ptx::tcgen05_commit(&bars->kv_empty[v_idx % kRing]);
         }
       }
     }
