@@ -318,6 +318,8 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU baseline)")
     torch.cuda.set_device(local)
+    if world > 1:  # torchrun pins OMP_NUM_THREADS=1; the host input generator may use this rank's share of the cores
+        os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or world) // world))
     ctx = Ctx()
     ctx.pkg = entry.load_package()
     ctx.hal = ctx.pkg.hal
@@ -388,6 +390,8 @@ def run_ours(args):
             if u == 0:
                 continue
             w2 = fac(ctx, u, f)
+            torch.cuda.synchronize()
+            time.sleep(0.5)  # let the power/clock state settle after the previous workload and the input set-up
             steps2 = max(3, min(args.steps, 10))
             tot, per2 = time_steps(ctx, w2, steps2, 3)
             ms = tot / steps2
@@ -395,7 +399,7 @@ def run_ours(args):
             sc = 1e9 if w2.bound == "hbm" else 1e12
             r2 = roofline_for(w2, statistics.mean(per2), peaks)
             extras[name] = {"value": round(gu * w2.work_per_unit / (ms * 1e-3) / sc, 2), "unit": "GB/s" if w2.bound == "hbm" else "TFLOP/s",
-                            "ms_per_step": round(ms, 4), "dtype": w2.dtype, "roofline_frac": r2["frac"], "roofline_peak": r2["peak"],
+                            "ms_per_step": round(ms, 4), "ms_per_step_min": round(min(per2), 4), "ms_per_step_max": round(max(per2), 4), "dtype": w2.dtype, "roofline_frac": r2["frac"], "roofline_peak": r2["peak"],
                             "config": w2.describe()}
             del w2
             torch.cuda.empty_cache()
