@@ -302,8 +302,9 @@ def roofline_for(wl, ms_per_launch, peaks):
 NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per full-size launch (profiles/*.md)
     "softmax_f32": 4 * (268.5e6 + 215.7e6),       # captured on a quarter of the rows, scaled by rows
     "softmax_bf16": 4 * (134.2e6 + 79.0e6),
-    "gemm_bf16_8192": 943.9e6 + 125.8e6,
-    "attention_causal": 4 * (538.8e6 + 45.1e6),   # captured on 64 of 256 heads, scaled by heads
+    "gemm_bf16_8192": 1064.7e6 + 127.0e6,
+    "attention_causal": 4 * (201.4e6 + 48.2e6),   # captured on 64 of 256 heads, scaled by heads
+    "attention_noncausal": 4 * (201.4e6 + 48.0e6),
 }
 
 
