@@ -45,9 +45,9 @@ constexpr int kD = 128;          // head_dim
 constexpr int kBQ = 128;         // query rows per tile (two tiles per CTA)
 constexpr int kBKV = 128;        // key/value rows per K/V tile in shared memory
 constexpr int kHalfKV = 64;      // key/value rows per half-step (one score buffer)
-constexpr int kThreads = 384;         // warps 0..3 softmax A, 4..7 softmax B, 8 TMA, 9 MMA, 10..11 idle
-constexpr int kRegsSoftmax = 224;      // register budget after setmaxnreg (launch: 168 per thread)
-constexpr int kRegsOther = 56;
+constexpr int kSoftmaxWarps = 16;     // per tile 8: two threads per query row, 32 of a half-step's 64 keys each
+constexpr int kWarpTma = 16, kWarpMmaA = 17, kWarpMmaB = 18;
+constexpr int kThreads = 640;         // warps 0..7 softmax A, 8..15 softmax B, 16 TMA, 17/18 MMA issuers, 19 idle
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: any 128 x 128 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2; // one 128-row x 64-column swizzled half
 constexpr int kRing = 5;
@@ -68,10 +68,14 @@ struct alignas(8) Barriers {
   uint64_t pv_done[2][2];  // [tile][half-step parity]: the PV product of that half-step has retired
   uint32_t tmem_base;
   uint32_t abort_flag;
+  int16_t row_max[2][2][2][kBQ];  // [half-step parity][tile][column half][row]: that half's maximum, whole log2 units
 };
 
 // Q_A, Q_B, ring
-constexpr int kSmemBytes = (2 + kRing) * kTileBytes + sizeof(Barriers) + 1024;
+// No slack for aligning the base: the kernel checks that the dynamic shared memory window
+// starts on a 1024-byte boundary (the 128-byte swizzle needs it) and reports kStatusSmemLayout if not.
+constexpr int kSmemBytes = (2 + kRing) * kTileBytes + sizeof(Barriers);
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
 struct Params {
   int32_t seq;
@@ -163,8 +167,11 @@ template <bool kIsBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, uint16_t* __restrict__ o, const Params p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((ptx::smem_u32(smem) & 1023u) != 0u) {  // uniform over the CTA: nothing has been set up yet
+    if (threadIdx.x == 0) atomicCAS(p.status, ptx::kStatusOk, ptx::kStatusSmemLayout);
+    return;
+  }
   uint8_t* smem_q = smem;                         // 2 tiles
   uint8_t* smem_kv = smem + 2 * kTileBytes;       // ring
   Barriers* bars = reinterpret_cast<Barriers*>(smem + (2 + kRing) * kTileBytes);
@@ -187,14 +194,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     for (int g = 0; g < 2; ++g) {
       for (int b = 0; b < 2; ++b) {
         ptx::mbar_init(&bars->s_full[g][b], 1);
-        ptx::mbar_init(&bars->p_ready[g][b], 128);
+        ptx::mbar_init(&bars->p_ready[g][b], 256);
         ptx::mbar_init(&bars->pv_done[g][b], 1);
       }
     }
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  if (warp == 9) {
+  if (warp == kWarpMmaA) {
     ptx::tmem_alloc(&bars->tmem_base, kTmemCols);
     ptx::tmem_relinquish_alloc_permit();
   }
@@ -210,7 +217,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   // The non-softmax warpgroup (warps 8..11) gives most of its registers to the softmax
   // warpgroups; each role branch starts with its own setmaxnreg so that the register
   // budget is unambiguous inside it.
-  if (warp == 8) {
+  if (warp == kWarpTma) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       ptx::prefetch_tensormap(&tmap_q);
@@ -241,11 +248,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             const uint32_t pos = ring_pos + idx;
             const uint32_t slot = pos % kRing;
             const uint32_t phase = (pos / kRing) & 1u;
+            TSM_TRACE(3, idx, 0);
             if (!ptx::mbar_wait(&bars->kv_empty[0][slot], phase ^ 1u, abort_flag, p.status, 11) ||
                 !ptx::mbar_wait(&bars->kv_empty[1][slot], phase ^ 1u, abort_flag, p.status, 11)) {
               ok = false;
               break;
             }
+            TSM_TRACE(3, idx, 1);
             ptx::mbar_arrive_expect_tx(&bars->kv_full[slot], kTileBytes);
             const CUtensorMap* tm = (idx & 1) ? &tmap_v : &tmap_k;
             const int row0 = (idx >> 1) * kBKV;
@@ -253,19 +262,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             for (int c = 0; c < 2; ++c)
               ptx::tma_load_3d(smem_kv + slot * kTileBytes + c * kHalfBytes, tm, &bars->kv_full[slot], c * 64,
                                row0, wk.kvh);
+            TSM_TRACE(3, idx, 2);
           }
           ring_pos += total;
           ++blocks;
         }
       }
     }
-  } else if (warp == 9 || warp == 10) {
+  } else if (warp == kWarpMmaA || warp == kWarpMmaB) {
     // ------------------------------ MMA issuers -------------------------------
     // One warp per tile (warp 9: A, warp 10: B).  Issuing an MMA costs a thread about 40
     // cycles and every barrier test 70 to 300, which for 64-key half-steps is more than
     // one thread can do in the time the tensor core needs for both tiles.  The whole warp
     // runs the loop (uniform control flow, uniform operands); one elected lane issues.
-    const int g = warp - 9;
+    const int g = warp - kWarpMmaA;
     {
       constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBQ, kHalfKV, false, false, kIsBf16);
       constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBQ, kD, false, true, kIsBf16);
@@ -282,6 +292,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       int kv_seen = 0;  // K/V tiles of this block (K_0, V_0, K_1, ...) known to have landed
       auto need_kv = [&](int idx) -> bool {
         bool r = true;
+#ifdef TSM100_DEBUG_NO_KV_WAIT
+        if (idx > 0) return true;  // development aid (results may be wrong): what do these waits cost the issuer?
+#endif
         while (kv_seen <= idx && r) {  // tiles land in ring order
           const uint32_t pos = ring_base + kv_seen;
           r = ptx::mbar_wait_relaxed(&bars->kv_full[pos % kRing], (pos / kRing) & 1u, abort_flag, p.status, 13);
@@ -400,16 +413,24 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
     }
-  } else if (warp < 8) {
+  } else if (warp < kSoftmaxWarps) {
     // ------------------------------ softmax / output ---------------------------
-    const int g = warp >> 2;          // 0: tile A, 1: tile B
-    const int quad = warp & 3;              // TMEM lanes this warp may touch
-    const int r = quad * 32 + lane;         // row inside the tile == TMEM lane
+    // Two threads per query row: thread (row, h) owns keys [32 h, 32 h + 32) of every
+    // half-step and output columns [64 h, 64 h + 64).  Four such warps share a scheduler,
+    // which hides the latencies of tensor-memory loads, barriers and the exp pipeline.
+    const int g = warp >> 3;          // 0: tile A, 1: tile B
+    const int h = (warp >> 2) & 1;    // column half
+    const int quad = warp & 3;        // TMEM lanes this warp may touch
+    const int r = quad * 32 + lane;   // row inside the tile == TMEM lane
+    const uint32_t pair_bar = 1 + g * 4 + quad;  // named barrier of the two warps that share these rows
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t ts = tmem_s + g * 128 + lane_base;
-    const uint32_t to = tmem_o + g * 128 + lane_base;
+    const uint32_t to = tmem_o + g * 128 + lane_base + h * 64;
     const float sl2 = p.scale_log2;
-    const bool tracer = (threadIdx.x & 127) == 0;
+    const bool tracer = (threadIdx.x & 255) == 0;
+    // row_max[parity][g][h][r]; the other parity's entry is kBQ * 4 further on
+    int16_t* my_max = &bars->row_max[0][g][h][r];
+    const int16_t* other_max = &bars->row_max[0][g][h ^ 1][r];
     bool alive = true;
     uint32_t done = 0;   // half-steps this tile has been through (barrier phases run on across query blocks)
     int blk = 0;         // query blocks so far (trace builds only)
@@ -422,8 +443,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int bh = wk.bh;
     const int qrow = wk.q0 + g * kBQ + r;
     const int limit = p.causal ? min(qrow, p.seq - 1) : (p.seq - 1);  // last visible column
-    float m_used = -INFINITY;  // running max in raw score units
-    float l = 0.f;
+    // The running maximum is kept in whole log2 units (rounded up), so that the two threads
+    // of a row agree on it exactly after exchanging 16-bit values; being up to one unit above
+    // the true maximum only scales P and l by the same factor.
+    float ms = -INFINITY;
+    float l = 0.f;  // this thread's share of the row sum
     if (tracer) TSM_TRACE_BLOCK(g * 2, blk, 0);
     for (int i = 0; i < n_g; ++i) {
       const int buf = i & 1;
@@ -437,47 +461,43 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       ptx::tcgen05_fence_after_thread_sync();
       if (tracer) TSM_TRACE(g * 2, i, 1);
       if (tracer && i == 0) TSM_TRACE_BLOCK(g * 2, blk, 1);
-#ifdef TSM100_DEBUG_SKIP_SOFTMAX
-      if (i >= 0) {  // development aid: hand the tile straight back, to time the MMA pipeline alone
-        ptx::tcgen05_fence_before_thread_sync();
-        ptx::mbar_arrive(&bars->p_ready[g][buf]);
-        continue;
-      }
-#endif
-      const int col0 = i * kHalfKV;
-      const bool masked = col0 + kHalfKV - 1 > limit;
+      const int col0 = i * kHalfKV + h * 32;
+      const bool masked = col0 + 31 > limit;
 
-      // this thread's 64 scores of the half-step, read once
-      uint32_t v[2][32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) ptx::tmem_ld_32x32b_x32(tsb + c * 32, v[c]);
+      // this thread's 32 scores of the half-step, read once
+      uint32_t v[32];
+      ptx::tmem_ld_32x32b_x32(tsb + h * 32, v);
       ptx::tmem_ld_wait();
       if (tracer) TSM_TRACE(g * 2, i, 2);
 
       float mx = -INFINITY;
       if (masked) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            if (col0 + c * 32 + e > limit) v[c][e] = 0xff800000u;  // -inf
-            mx = fmaxf(mx, __uint_as_float(v[c][e]));
-          }
+        for (int e = 0; e < 32; ++e) {
+          if (col0 + e > limit) v[e] = 0xff800000u;  // -inf
+          mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
       } else {
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; e += 2)  // three-input max: 32 instructions for 64 values
-            mx4[(e >> 1) & 3] = ptx::fmax3(mx4[(e >> 1) & 3], __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
+        for (int e = 0; e < 32; e += 2)  // three-input max: 16 instructions for 32 values
+          mx4[(e >> 1) & 3] = ptx::fmax3(mx4[(e >> 1) & 3], __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
-      const float m_new = fmaxf(m_used, mx);
+      // exchange with the thread that owns the other 32 keys of this row (also orders its
+      // tensor-memory reads of this buffer before this thread's P stores below)
+      const int mine = max(-32768, min(32767, __float2int_ru(mx * sl2)));  // -inf -> -32768
+      // (two sets of slots alternate: the value of half-step i is read before its reader
+      // arrives at the pair barrier of half-step i+1, the slot is rewritten after that barrier)
+      my_max[buf * (4 * kBQ)] = static_cast<int16_t>(mine);
+      ptx::named_bar_sync(pair_bar, 64);
+      const int both = max(mine, static_cast<int>(other_max[buf * (4 * kBQ)]));
+      const float m_new = fmaxf(ms, both == -32768 ? -INFINITY : static_cast<float>(both));
       if (tracer) TSM_TRACE(g * 2, i, 3);
       if (i == 0) {
-        m_used = m_new;
+        ms = m_new;
       } else {
-        const bool need = (m_new - m_used) * sl2 > kRescaleThreshold;
+        const bool need = m_new - ms > kRescaleThreshold;  // identical in both threads of the row
         if (__any_sync(0xffffffffu, need)) {
           // O_g is rescaled in place once the PV product of the previous half-step has retired
           // (the one of this half-step cannot start before this thread reports its probabilities).
@@ -489,11 +509,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             break;
           }
           ptx::tcgen05_fence_after_thread_sync();
-          const float alpha = need ? ptx::ex2_approx((m_used - m_new) * sl2) : 1.0f;
-          if (need) m_used = m_new;
+          const float alpha = need ? ptx::ex2_approx(ms - m_new) : 1.0f;
+          if (need) ms = m_new;
           l *= alpha;
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {  // this thread's 64 output columns
             uint32_t ov[32];
             ptx::tmem_ld_32x32b_x32(to + c * 32, ov);
             ptx::tmem_ld_wait();
@@ -505,22 +525,19 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
 
-      // probabilities: exp2, round to 16 bit, two per 32-bit TMEM column over the first 32
-      // columns of this score buffer.  Of every 8 pairs, kPolyPairs go through the FMA-pipe
-      // polynomial and the rest through MUFU ex2, so that neither pipe alone bounds the
-      // exponentials.  The row sum adds the f32 probabilities before they are rounded
-      // (packed adds, two per instruction).
-      const float ms = m_used * sl2;
+      // probabilities: exp2, round to 16 bit, two per 32-bit TMEM column; the 32 packed
+      // columns of a half-step overlay the first 32 columns of its score buffer (this thread:
+      // 16 of them).  Of every 8 pairs, kPolyPairs go through the FMA-pipe polynomial and the
+      // rest through MUFU ex2, so that neither pipe alone bounds the exponentials.  The row
+      // sum adds the f32 probabilities before they are rounded (packed adds).
       const ptx::f32x2_t sl2x2 = ptx::pack_f32x2(sl2, sl2);
       const ptx::f32x2_t nmsx2 = ptx::pack_f32x2(-ms, -ms);
       ptx::f32x2_t lsum[2] = {0ull, 0ull};  // (+0.0f, +0.0f)
-      uint32_t pk[32];
+      uint32_t pk[16];
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const int c = e >> 4;
-        const int e0 = (e & 15) * 2;
+      for (int e = 0; e < 16; ++e) {
         const ptx::f32x2_t t2 = ptx::fma_f32x2(
-            ptx::pack_f32x2(__uint_as_float(v[c][e0]), __uint_as_float(v[c][e0 + 1])), sl2x2, nmsx2);
+            ptx::pack_f32x2(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1])), sl2x2, nmsx2);
         float p0, p1;
         if ((e & 7) < kPolyPairs) {
           ptx::exp2_poly_x2(t2, p0, p1);
@@ -533,7 +550,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         pk[e] = pack16x2<kIsBf16>(p0, p1);
         lsum[e & 1] = ptx::add_f32x2(lsum[e & 1], ptx::pack_f32x2(p0, p1));
       }
-      ptx::tmem_st_32x32b_x32(tsb, pk);
+      ptx::tmem_st_32x32b_x16(tsb + h * 16, pk);
       float l4[4];
       ptx::unpack_f32x2(lsum[0], l4[0], l4[1]);
       ptx::unpack_f32x2(lsum[1], l4[2], l4[3]);
@@ -554,24 +571,33 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       } else {
         ptx::tcgen05_fence_after_thread_sync();
         if (tracer) TSM_TRACE_BLOCK(g * 2, blk, 3);
-        const float inv = 1.0f / l;
-        uint16_t* orow = o + (static_cast<int64_t>(bh) * p.seq + qrow) * kD;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t ov[32];
-          ptx::tmem_ld_32x32b_x32(to + c * 32, ov);
-          ptx::tmem_ld_wait();
-          if (qrow < p.seq) {
+        // this thread's 64 output columns; then the two row-sum shares change hands through
+        // the first column of each thread's (already read) part of O
+        uint32_t ov[2][32];
+        ptx::tmem_ld_32x32b_x32(to, ov[0]);
+        ptx::tmem_ld_32x32b_x32(to + 32, ov[1]);
+        ptx::tmem_ld_wait();
+        ptx::tmem_st_32x32b_x1(to, __float_as_uint(l));
+        ptx::tmem_st_wait();
+        ptx::tcgen05_fence_before_thread_sync();
+        ptx::named_bar_sync(pair_bar, 64);
+        ptx::tcgen05_fence_after_thread_sync();
+        const float l_other = __uint_as_float(ptx::tmem_ld_32x32b_x1(to + 64 - 2 * h * 64));
+        ptx::tmem_ld_wait();
+        const float inv = 1.0f / (l + l_other);
+        if (qrow < p.seq) {
+          uint16_t* orow = o + (static_cast<int64_t>(bh) * p.seq + qrow) * kD + h * 64;
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
-              uint4 w;
-              w.x = pack16x2<kIsBf16>(__uint_as_float(ov[8 * t + 0]) * inv, __uint_as_float(ov[8 * t + 1]) * inv);
-              w.y = pack16x2<kIsBf16>(__uint_as_float(ov[8 * t + 2]) * inv, __uint_as_float(ov[8 * t + 3]) * inv);
-              w.z = pack16x2<kIsBf16>(__uint_as_float(ov[8 * t + 4]) * inv, __uint_as_float(ov[8 * t + 5]) * inv);
-              w.w = pack16x2<kIsBf16>(__uint_as_float(ov[8 * t + 6]) * inv, __uint_as_float(ov[8 * t + 7]) * inv);
-              reinterpret_cast<uint4*>(orow + c * 32)[t] = w;
+              uint4 w4;
+              w4.x = pack16x2<kIsBf16>(__uint_as_float(ov[c][8 * t + 0]) * inv, __uint_as_float(ov[c][8 * t + 1]) * inv);
+              w4.y = pack16x2<kIsBf16>(__uint_as_float(ov[c][8 * t + 2]) * inv, __uint_as_float(ov[c][8 * t + 3]) * inv);
+              w4.z = pack16x2<kIsBf16>(__uint_as_float(ov[c][8 * t + 4]) * inv, __uint_as_float(ov[c][8 * t + 5]) * inv);
+              w4.w = pack16x2<kIsBf16>(__uint_as_float(ov[c][8 * t + 6]) * inv, __uint_as_float(ov[c][8 * t + 7]) * inv);
+              reinterpret_cast<uint4*>(orow + c * 32)[t] = w4;
             }
-          }
         }
       }
     }
@@ -590,7 +616,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   }
   ptx::tcgen05_fence_before_thread_sync();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kWarpMmaA) {
     ptx::tcgen05_fence_after_thread_sync();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
