@@ -10,7 +10,6 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
-#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -386,14 +385,8 @@ inline int32_t attention_tc_launch(std::string* err, const tsm100_attention_desc
   p.q_blocks = (d->seq + 2 * at::kBQ - 1) / (2 * at::kBQ);
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
   p.status = status;
-  p.slots = p.causal ? (p.q_blocks + 1) / 2 : p.q_blocks;
-  const int64_t items = static_cast<int64_t>(p.slots) * nq;
-  if (items > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many tiles for one launch");
-  p.work_items = static_cast<int32_t>(items);
-  int sms = 0;
-  st = sm_count(err, &sms);
-  if (st != TSM100_OK) return st;
-  const int64_t grid = std::min<int64_t>(items, sms);  // persistent: one CTA per SM walks the item list
+  const int64_t grid = static_cast<int64_t>(p.q_blocks) * nq;
+  if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many tiles for one launch");
   auto kern = at::attention_fwd_kernel<kBf16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, at::kSmemBytes);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_fwd_kernel)");
