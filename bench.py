@@ -189,6 +189,41 @@ class SoftmaxWL(Workload):
         return done * self.work_per_unit / dt / 1e9, f"{rows} rows x {self.cols} cols f32, {done // rows} passes in {dt:.1f} s"
 
 
+class RowOpWL(Workload):
+    """rms_norm / row sum / silu * mul on the softmax configuration's shape (rows x 4096)."""
+    unit_name = "rows"
+
+    def __init__(self, ctx, units, op, dtype="f32"):
+        super().__init__(ctx, units)
+        torch, capi = _torch(), ctx.pkg.capi
+        self.op, self.dtype, self.cols = op, dtype, SOFTMAX_COLS
+        self.name = f"{op}_{dtype}"
+        es = 4 if dtype == "f32" else 2
+        self.code = capi.F32 if dtype == "f32" else capi.BF16
+        tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+        g = torch.Generator(device=ctx.tdev).manual_seed(601)
+        self.x = (torch.randn(units, self.cols, device=ctx.tdev, generator=g) * 3).to(tdt)
+        streams = {"rms_norm": 2, "reduce_sum": 1, "silu_mul": 3}[op]
+        self.work_per_unit = streams * self.cols * es + (es if op == "reduce_sum" else 0)
+        if op == "reduce_sum":
+            self.y = torch.empty(units, device=ctx.tdev, dtype=tdt)
+        else:
+            self.y = torch.empty_like(self.x)
+        self.up = torch.randn(units, self.cols, device=ctx.tdev, generator=g).to(tdt) if op == "silu_mul" else None
+
+    def step(self):
+        d, capi = self.ctx.dev, self.ctx.pkg.capi
+        if self.op == "rms_norm":
+            d.rms_norm(self.code, self.units, self.cols, 1e-5, self.x.data_ptr(), self.y.data_ptr(), stream=self.ctx.stream)
+        elif self.op == "reduce_sum":
+            d.reduce(self.code, capi.REDUCE_SUM, self.units, self.cols, self.x.data_ptr(), self.y.data_ptr(), stream=self.ctx.stream)
+        else:
+            d.silu_mul(self.code, self.units, self.cols, self.x.data_ptr(), self.up.data_ptr(), self.y.data_ptr(), stream=self.ctx.stream)
+
+    def describe(self):
+        return {"cols": self.cols, "rows_per_gpu": self.units}
+
+
 class GemmWL(Workload):
     bound, unit_name = "tensor", "problems"
 
@@ -253,6 +288,10 @@ def catalogue():
         "attention_noncausal": (256, lambda c, u, f: AttentionWL(c, u, 1, 4096, False, "attention_noncausal")),
         "attention_causal": (256, lambda c, u, f: AttentionWL(c, u, 1, 4096, True, "attention_causal")),
         "attention_gqa_causal": (16, lambda c, u, f: AttentionWL(c, u, 8, 16384, True, "attention_gqa_causal")),
+        "rms_norm_f32": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "rms_norm")),
+        "reduce_sum_f32": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "reduce_sum")),
+        "silu_mul_f32": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "silu_mul")),
+        "silu_mul_bf16": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "silu_mul", "bf16")),
     }
 
 

@@ -136,6 +136,47 @@ typedef struct {
 int32_t tsm100_softmax(tsm100_device_t dev, const tsm100_softmax_desc* desc, const void* x, void* y,
                        void* stream);
 
+/* RMS normalisation, y[r,c] = x[r,c] * rsqrt(mean_c(x[r,:]^2) + eps), no weight.
+ * __tile_rms_norm_f32 (crates/tile_std/src/tile.rs:2063; wrapper :2731-2738);
+ * semantics linalg.mul + linalg.reduce addf + rsqrt(sum / cols + eps) + multiply
+ * (crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1666-1767).  Replaces the lowering at
+ * crates/rustc_codegen_tile/src/mlir_to_gpu.rs:920-977. */
+typedef struct {
+  int32_t dtype; /* storage type; math is f32 */
+  int64_t rows;
+  int64_t cols;
+  float eps;
+} tsm100_rms_norm_desc;
+int32_t tsm100_rms_norm(tsm100_device_t dev, const tsm100_rms_norm_desc* desc, const void* x, void* y,
+                        void* stream);
+
+/* Row reduction to a ROWS x 1 tile, y[r] = sum_c x[r,c] or max_c x[r,c] (an empty row gives 0
+ * or -inf).  __tile_reduce_sum_f32 / __tile_reduce_max_f32 (tile.rs:206-209; wrappers
+ * :2352-2367); semantics linalg.fill + linalg.reduce (mlir_to_linalg.rs:545-550).  Replaces
+ * the warp-only lowering at mlir_to_gpu.rs:2059-2092. */
+#define TSM100_REDUCE_SUM 0
+#define TSM100_REDUCE_MAX 1
+typedef struct {
+  int32_t dtype; /* storage type of x and y; accumulation is f32 */
+  int32_t kind;  /* TSM100_REDUCE_SUM | TSM100_REDUCE_MAX */
+  int64_t rows;
+  int64_t cols;
+} tsm100_reduce_desc;
+int32_t tsm100_reduce(tsm100_device_t dev, const tsm100_reduce_desc* desc, const void* x, void* y,
+                      void* stream);
+
+/* y = silu(gate) * up element-wise, silu(x) = x / (1 + exp(-x)); up == NULL gives silu(gate).
+ * __tile_silu_f32 / _f16 and __tile_mul_f32 / _f16 (tile.rs:229, :1135, :184, :2160; wrappers
+ * :2416-2422, :2272-2282); semantics mlir_to_linalg.rs:774-782 and :425.  Replaces the fused
+ * lowering at mlir_to_gpu.rs:542-641. */
+typedef struct {
+  int32_t dtype;
+  int64_t rows;
+  int64_t cols;
+} tsm100_silu_mul_desc;
+int32_t tsm100_silu_mul(tsm100_device_t dev, const tsm100_silu_mul_desc* desc, const void* gate,
+                        const void* up, void* y, void* stream);
+
 /* GEMM, C[M,N] = A[M,K] * B, all row-major, C overwritten (zero-initialised
  * accumulator).  __tile_matmul_f32 (tile.rs:192-193, :2307-2319),
  * __tile_matmul_f16 (tile.rs:1982-1986, :2593-2601, :2666-2674) and, with

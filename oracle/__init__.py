@@ -44,12 +44,18 @@ def lib() -> C.CDLL:
         h.orc_softmax_bf16.argtypes = [_vp, _vp, _vp, _i64, _i64]
         h.orc_attention_f32.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, C.c_int]
         h.orc_attention_bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, C.c_int, _i64, _i64]
+        h.orc_rms_norm_f32.argtypes = [_vp, _vp, _i64, _i64, C.c_float, C.c_int]
+        h.orc_rms_norm_bf16.argtypes = [_vp, _vp, _vp, _i64, _i64, C.c_float]
+        h.orc_reduce_f32.argtypes = [_vp, _vp, _i64, _i64, C.c_int, C.c_int]
+        h.orc_silu_mul_f32.argtypes = [_vp, _vp, _vp, _i64, C.c_int]
+        h.orc_silu_mul_bf16.argtypes = [_vp, _vp, _vp, _vp, _i64]
         h.orc_compare_f32.argtypes = [_vp, _vp, _i64, C.c_double, _vp]
         h.orc_bf16_to_f32.argtypes = [_vp, _vp, _i64]
         h.orc_f32_to_bf16.argtypes = [_vp, _vp, _i64]
         for name in ("orc_gemm_f32", "orc_gemm_f64acc", "orc_gemm_bf16", "orc_softmax_f32", "orc_softmax_f64acc",
                      "orc_softmax_bf16", "orc_attention_f32", "orc_attention_bf16", "orc_compare_f32",
-                     "orc_bf16_to_f32", "orc_f32_to_bf16"):
+                     "orc_bf16_to_f32", "orc_f32_to_bf16", "orc_rms_norm_f32", "orc_rms_norm_bf16", "orc_reduce_f32",
+                     "orc_silu_mul_f32", "orc_silu_mul_bf16"):
             getattr(h, name).restype = None
         _LIB = h
     return _LIB
@@ -115,6 +121,48 @@ def softmax_bf16(x: np.ndarray):
     y32 = np.empty(x.shape, np.float32)
     y16 = np.empty(x.shape, np.uint16)
     lib().orc_softmax_bf16(_p(x), _p(y32), _p(y16), x.shape[0], x.shape[1])
+    return y32, y16
+
+
+def rms_norm_f32(x: np.ndarray, eps: float, f64_acc: bool = False) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.empty_like(x)
+    lib().orc_rms_norm_f32(_p(x), _p(y), x.shape[0], x.shape[1], eps, int(f64_acc))
+    return y
+
+
+def rms_norm_bf16(x: np.ndarray, eps: float):
+    """Returns (unrounded f32 result, RNE bf16 bit patterns)."""
+    x = np.ascontiguousarray(x, np.uint16)
+    y32 = np.empty(x.shape, np.float32)
+    y16 = np.empty(x.shape, np.uint16)
+    lib().orc_rms_norm_bf16(_p(x), _p(y32), _p(y16), x.shape[0], x.shape[1], eps)
+    return y32, y16
+
+
+def reduce_f32(x: np.ndarray, kind: str, f64_acc: bool = False) -> np.ndarray:
+    """Row sums ('sum') or row maxima ('max') of a [rows, cols] f32 matrix -> [rows]."""
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.empty(x.shape[0], np.float32)
+    lib().orc_reduce_f32(_p(x), _p(y), x.shape[0], x.shape[1], int(kind == "max"), int(f64_acc))
+    return y
+
+
+def silu_mul_f32(gate: np.ndarray, up, f64_acc: bool = False) -> np.ndarray:
+    gate = np.ascontiguousarray(gate, np.float32)
+    y = np.empty_like(gate)
+    upc = None if up is None else np.ascontiguousarray(up, np.float32)
+    lib().orc_silu_mul_f32(_p(gate), None if upc is None else _p(upc), _p(y), gate.size, int(f64_acc))
+    return y
+
+
+def silu_mul_bf16(gate: np.ndarray, up):
+    """Returns (unrounded f32 result, RNE bf16 bit patterns)."""
+    gate = np.ascontiguousarray(gate, np.uint16)
+    upc = None if up is None else np.ascontiguousarray(up, np.uint16)
+    y32 = np.empty(gate.shape, np.float32)
+    y16 = np.empty(gate.shape, np.uint16)
+    lib().orc_silu_mul_bf16(_p(gate), None if upc is None else _p(upc), _p(y32), _p(y16), gate.size)
     return y32, y16
 
 

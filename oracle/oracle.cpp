@@ -110,6 +110,44 @@ void attention_slice(const float* q, const float* k, const float* v, float* o,
   }
 }
 
+// One rms_norm row (crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1666-1767):
+//   sq = x * x (linalg.mul) ; s = 0 + sum_j sq_j (linalg.fill 0 + linalg.reduce addf, in
+//   index order) ; rs = rsqrt(s / cols + eps) (arith.divf, arith.addf, math.rsqrt) ;
+//   y_j = x_j * rs.  Acc = float follows the bridge's f32 arithmetic, Acc = double is the
+//   truth the error bound is taken against.
+template <typename Acc>
+inline void rms_norm_row(const float* x, float* y, int64_t n, float eps) {
+  Acc s = 0;
+  for (int64_t j = 0; j < n; ++j) {
+    const Acc sq = static_cast<Acc>(x[j]) * static_cast<Acc>(x[j]);
+    s += sq;
+  }
+  const Acc var = s / static_cast<Acc>(static_cast<float>(n)) + static_cast<Acc>(eps);
+  const Acc rs = static_cast<Acc>(1) / std::sqrt(var);
+  for (int64_t j = 0; j < n; ++j) y[j] = static_cast<float>(static_cast<Acc>(x[j]) * rs);
+}
+
+// Row reduction (mlir_to_linalg.rs:545-550: linalg.fill(0 | -inf) + linalg.reduce addf |
+// maximumf over dimension 1, in index order).
+template <typename Acc>
+inline float reduce_row(const float* x, int64_t n, bool is_max) {
+  if (is_max) {
+    float m = -std::numeric_limits<float>::infinity();
+    for (int64_t j = 0; j < n; ++j) m = x[j] > m ? x[j] : m;
+    return m;
+  }
+  Acc s = 0;
+  for (int64_t j = 0; j < n; ++j) s += static_cast<Acc>(x[j]);
+  return static_cast<float>(s);
+}
+
+// silu(x) = x / (1 + exp(-x)) (mlir_to_linalg.rs:774-782: negf, math.exp, addf 1, divf).
+template <typename Acc>
+inline float silu_one(float x) {
+  if (sizeof(Acc) == 4) return x / (expf(-x) + 1.0f);
+  return static_cast<float>(static_cast<double>(x) / (std::exp(-static_cast<double>(x)) + 1.0));
+}
+
 }  // namespace
 
 extern "C" {
@@ -254,6 +292,66 @@ void orc_softmax_bf16(const uint16_t* x, float* y_f32, uint16_t* y_bf16, int64_t
       if (y_bf16)
         for (int64_t j = 0; j < cols; ++j) y_bf16[r * cols + j] = f32_to_bf16(yr[j]);
     }
+  }
+}
+
+// __tile_rms_norm_f32 on an f32 tile; f64acc != 0 selects the truth variant.
+void orc_rms_norm_f32(const float* x, float* y, int64_t rows, int64_t cols, float eps, int f64acc) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    if (f64acc) rms_norm_row<double>(x + r * cols, y + r * cols, cols, eps);
+    else rms_norm_row<float>(x + r * cols, y + r * cols, cols, eps);
+  }
+}
+
+// bf16-I/O rms_norm: widen, f32 math, unrounded f32 to y_f32 (may be NULL) and RNE bf16 to
+// y_bf16 (may be NULL).
+void orc_rms_norm_bf16(const uint16_t* x, float* y_f32, uint16_t* y_bf16, int64_t rows, int64_t cols, float eps) {
+#pragma omp parallel
+  {
+    std::vector<float> xr(cols), yr(cols);
+#pragma omp for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+      for (int64_t j = 0; j < cols; ++j) xr[j] = bf16_to_f32(x[r * cols + j]);
+      rms_norm_row<float>(xr.data(), yr.data(), cols, eps);
+      if (y_f32) std::memcpy(y_f32 + r * cols, yr.data(), sizeof(float) * cols);
+      if (y_bf16)
+        for (int64_t j = 0; j < cols; ++j) y_bf16[r * cols + j] = f32_to_bf16(yr[j]);
+    }
+  }
+}
+
+// __tile_reduce_sum_f32 / __tile_reduce_max_f32: y[rows].
+void orc_reduce_f32(const float* x, float* y, int64_t rows, int64_t cols, int is_max, int f64acc) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r)
+    y[r] = f64acc ? reduce_row<double>(x + r * cols, cols, is_max != 0) : reduce_row<float>(x + r * cols, cols, is_max != 0);
+}
+
+// __tile_silu_f32 followed by __tile_mul_f32 (linalg.mul, mlir_to_linalg.rs:425); up == NULL
+// gives silu alone.
+void orc_silu_mul_f32(const float* gate, const float* up, float* y, int64_t n, int f64acc) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    if (f64acc) {
+      const double g = gate[i];
+      const double s = g / (std::exp(-g) + 1.0);
+      y[i] = static_cast<float>(up ? s * static_cast<double>(up[i]) : s);
+    } else {
+      const float s = silu_one<float>(gate[i]);
+      y[i] = up ? s * up[i] : s;
+    }
+  }
+}
+
+// bf16-I/O: widen, f32 math, unrounded f32 and RNE bf16 results (either may be NULL).
+void orc_silu_mul_bf16(const uint16_t* gate, const uint16_t* up, float* y_f32, uint16_t* y_bf16, int64_t n) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    const float s = silu_one<float>(bf16_to_f32(gate[i]));
+    const float r = up ? s * bf16_to_f32(up[i]) : s;
+    if (y_f32) y_f32[i] = r;
+    if (y_bf16) y_bf16[i] = f32_to_bf16(r);
   }
 }
 

@@ -34,6 +34,26 @@ def softmax(x: np.ndarray) -> np.ndarray:
     return e / e.sum(axis=-1, keepdims=True)
 
 
+def rms_norm(x: np.ndarray, eps: float) -> np.ndarray:
+    """x * rsqrt(mean(x^2) + eps) per row (mlir_to_linalg.rs:1666-1767), in float64."""
+    x = x.astype(np.float64)
+    return x / np.sqrt((x * x).sum(axis=1, keepdims=True) / x.shape[1] + np.float64(np.float32(eps)))
+
+
+def reduce(x: np.ndarray, kind: str) -> np.ndarray:
+    """Row sums or row maxima (mlir_to_linalg.rs:545-550), in float64."""
+    x = x.astype(np.float64)
+    return x.max(axis=1) if kind == "max" else x.sum(axis=1)
+
+
+def silu_mul(gate: np.ndarray, up=None) -> np.ndarray:
+    """silu(gate) [* up], silu(x) = x / (1 + exp(-x)) (mlir_to_linalg.rs:774-782, :425), in float64."""
+    g = gate.astype(np.float64)
+    with np.errstate(over="ignore"):
+        s = g / (1.0 + np.exp(-g))
+    return s if up is None else s * up.astype(np.float64)
+
+
 def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, causal: bool) -> np.ndarray:
     """transpose, matmul, scale 1/sqrt(D), [causal mask col > row -> -inf], softmax, matmul
     (mlir_to_linalg.rs:1781-1902, :1191-1244); grouped KV heads with

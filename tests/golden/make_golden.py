@@ -1,6 +1,6 @@
 """Writes tests/golden/*.npz: small seeded cases with float64 numpy results.
 
-The reference ships no numeric vectors for matmul / softmax / attention (its tests
+The reference ships no numeric vectors for matmul / softmax / attention / the row operators (its tests
 assert emitted text), and none of its code can run here, so these vectors pin the
 C++ oracle against an independent float64 statement of the same linalg semantics
 (oracle/oracle_np.py) and against drift of the input generator.  Regenerate with
@@ -44,6 +44,11 @@ def main() -> None:
     np.savez(out / "attention.npz", q=q, k=k, v=v, o_gqa_causal=onp.attention(q, k, v, True),
              o_gqa_full=onp.attention(q, k, v, False),
              o_mha_full=onp.attention(q[:, :2], k, v, False), o_mha_causal=onp.attention(q[:, :2], k, v, True))
+    # the other row operators: rms_norm, row sum / max, silu * mul
+    xr = util.gen_normal(capi, (6, 96), 601, 3.0)
+    gate, up = util.gen_normal(capi, (6, 96), 602, 4.0), util.gen_normal(capi, (6, 96), 603)
+    np.savez(out / "rowops.npz", x=xr, eps=np.float32(1e-5), rms=onp.rms_norm(xr, 1e-5), row_sum=onp.reduce(xr, "sum"),
+             row_max=onp.reduce(xr, "max"), gate=gate, up=up, silu=onp.silu_mul(gate), silu_mul=onp.silu_mul(gate, up))
     print("wrote", sorted(p.name for p in out.glob("*.npz")))
 
 

@@ -6,7 +6,10 @@ modules restate the reference's own parser/emitter fixtures
 crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1941-1955, :2088-2102,
 crates/rustc_codegen_tile/src/mlir_to_gpu.rs:2939-2955, :2974-2992) with other
 kernel names and shapes; the bf16, causal-chain and generic-form modules are
-this project's additions.
+this project's additions.  The rms_norm, reduce_sum / reduce_max and silu modules
+restate crates/rustc_codegen_tile/src/mlir_to_linalg.rs:2629-2641, :2030-2056 and
+:2143-2155; silu followed by mul is the pair the reference's NVIDIA emitter fuses
+(crates/rustc_codegen_tile/src/mlir_to_gpu.rs:542-641).
 """
 
 
@@ -107,3 +110,35 @@ ADD_OUT_OF_SCOPE = module("add_test", 3, consts(r=1, c=256) + [
     "%b = llvm.call @__tile_load_f32(%arg1, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
     "%s = llvm.call @__tile_add_f32(%a, %a, %b, %r, %c) : (i32, i32, i32, i32, i32) -> i32",
     "llvm.call @__tile_store_f32(%arg2, %s, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+
+
+def rms_norm(name="tile_rms", rows=1, cols=256, dt="f32", eps="1.0e-5"):
+    return module(name, 2, consts(r=rows, c=cols) + [
+        f"%eps = llvm.mlir.constant({eps} : f32) : f32",
+        f"%x = llvm.call @__tile_load_{dt}(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%y = llvm.call @__tile_rms_norm_{dt}(%x, %x, %eps, %r, %c) : (i32, i32, f32, i32, i32) -> i32",
+        f"llvm.call @__tile_store_{dt}(%arg1, %y, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+
+
+def reduce(kind="sum", name=None, rows=1, cols=1024, dt="f32"):
+    return module(name or f"tile_reduce_{kind}", 2, consts(r=rows, c=cols, one=1) + [
+        f"%x = llvm.call @__tile_load_{dt}(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%y = llvm.call @__tile_reduce_{kind}_{dt}(%x, %x, %r, %c) : (i32, i32, i32, i32) -> i32",
+        f"llvm.call @__tile_store_{dt}(%arg1, %y, %r, %one) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+
+
+def silu(name="tile_silu", rows=1, cols=1024, dt="f32"):
+    return module(name, 2, consts(r=rows, c=cols) + [
+        f"%x = llvm.call @__tile_load_{dt}(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%y = llvm.call @__tile_silu_{dt}(%x, %x, %r, %c) : (i32, i32, i32, i32) -> i32",
+        f"llvm.call @__tile_store_{dt}(%arg1, %y, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+
+
+def silu_mul(name="tile_swiglu", rows=1, cols=1024, dt="f32", up_first=False):
+    ops = "%u, %s" if up_first else "%s, %u"
+    return module(name, 3, consts(c0=0, r=rows, c=cols) + [
+        f"%g = llvm.call @__tile_load_{dt}(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%u = llvm.call @__tile_load_{dt}(%arg1, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%s = llvm.call @__tile_silu_{dt}(%c0, %g, %r, %c) : (i32, i32, i32, i32) -> i32",
+        f"%y = llvm.call @__tile_mul_{dt}(%c0, {ops}, %r, %c) : (i32, i32, i32, i32, i32) -> i32",
+        f"llvm.call @__tile_store_{dt}(%arg2, %y, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])

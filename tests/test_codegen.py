@@ -68,6 +68,15 @@ CASES = {
     "causal_chain": (F.causal_chain(), ["d.causal = 1", "d.seq = 128", "d.head_dim = 64", "fused"]),
     "plain_chain": (F.causal_chain(mask=False), ["d.causal = 0"]),
     "generic_form": (F.GENERIC_SOFTMAX, ["softmax_generic_launch", "* 2;", "d.cols = 512"]),
+    "rms_norm": (F.rms_norm(), ["row_op_kernel<float, tsm100::rowops::kRmsNorm, 2, 32, 128>", "d.eps = 9.99999975e-06f", "tsm100::ops::rms_norm"]),
+    "rms_norm_bf16_wide": (F.rms_norm(rows=4, cols=4096, dt="bf16", eps="1.0e-6"),
+                           ["row_op_kernel<__nv_bfloat16, tsm100::rowops::kRmsNorm, 4, 128, 128>", "blocks) * 4;", "TSM100_BF16"]),
+    "reduce_sum": (F.reduce("sum"), ["row_op_kernel<float, tsm100::rowops::kReduceSum, 8, 32, 128>", "TSM100_REDUCE_SUM", "d.cols = 1024"]),
+    "reduce_max": (F.reduce("max", cols=5000), ["row_op_kernel<float, tsm100::rowops::kReduceMax, 8, 256, 256>", "TSM100_REDUCE_MAX"]),
+    "reduce_odd_width": (F.reduce("sum", cols=1001), ["row_op_stream_kernel<float, tsm100::rowops::kReduceSum, 512>"]),
+    "silu": (F.silu(), ["silu_mul_kernel<float, false, 4, 256>", "nullptr, args[1]", "tsm100::ops::silu_mul"]),
+    "silu_mul": (F.silu_mul(), ["silu_mul_kernel<float, true, 4, 256>", "args[0], args[1], args[2]", "fused"]),
+    "silu_mul_up_first_f16": (F.silu_mul(dt="f16", up_first=True, cols=4096), ["silu_mul_kernel<__half, true, 4, 256>", "args[0], args[1], args[2]"]),
 }
 
 
@@ -102,6 +111,9 @@ def test_non_entry_functions_are_ignored(target):
     (F.softmax().replace(" attributes {hacc.entry}", ""), "no entry kernel"),
     (F.ADD_OUT_OF_SCOPE, "__tile_add_f32 is outside the cuda_sm100 target"),
     (F.causal_chain(scale=0.5), "1/sqrt(head_dim)"),
+    (F.reduce("sum").replace("%y, %r, %one)", "%y, %r, %c)"), "rows x 1 tile"),
+    (F.silu_mul().replace("__tile_silu_f32(%c0, %g", "__tile_softmax_f32(%c0, %g"), "silu(gate) * up"),
+    (F.rms_norm().replace("%eps, %r, %c) : (i32, i32, f32", "%eps, %r) : (i32, i32, f32"), "expects 5 operands"),
     (F.softmax().replace("%t0, %r, %c) : (i32", "%t0, %r) : (i32"), "expects 4 operands"),
     (F.softmax().replace("(%c0, %t0, %r, %c)", "(%c0, %t0, %r, %7)"), "not a compile-time integer constant"),
     (F.softmax().replace("(%arg0, %r, %c)", "(%c0, %r, %c)"), "not a global-memory pointer"),

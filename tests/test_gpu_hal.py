@@ -108,3 +108,32 @@ def test_emitted_gemm_and_attention_modules(dev, pkg, oracle, tmp_path):
     assert dev.status(s) == 0
     ref32, _ = oracle.attention_bf16(q, k, v, True)
     util.assert_16bit_close(oracle, oracle.bf16_to_f32(o), ref32)
+
+
+def test_emitted_row_operator_modules(dev, pkg, oracle, tmp_path):
+    """rms_norm, reduce_max and the fused silu * mul pair through emit -> nvcc -> load -> launch."""
+    capi = pkg.capi
+    rows_per_block, cols, blocks = 2, 2048, 19
+    parts = [F.rms_norm("rms_tiles", rows_per_block, cols, eps="1.0e-6"), F.reduce("max", "max_tiles", rows_per_block, cols),
+             F.silu_mul("swiglu_tiles", rows_per_block, cols)]
+    mlir = parts[0].rsplit("}", 1)[0] + "".join(p.split("module {", 1)[1].rsplit("}", 1)[0] for p in parts[1:]) + "}\n"
+    out, so = _module(pkg, tmp_path, mlir, "rowops")
+    assert out.meta.kernel_names == ["rms_tiles", "max_tiles", "swiglu_tiles"]
+    launcher = dev.create_launcher()
+    launcher.load(so, pkg.hal.KernelMode.Vector)
+    s = dev.create_stream()
+    grid = pkg.hal.LaunchGrid.blocks_(blocks)
+    rows = blocks * rows_per_block
+    x = util.gen_normal(capi, (rows, cols), 601, 3.0)
+    u = util.gen_normal(capi, (rows, cols), 603)
+    xb, ub = dev.alloc_from_slice(x, s), dev.alloc_from_slice(u, s)
+    yb, rb = dev.alloc(x.size, np.float32), dev.alloc(rows, np.float32)
+    launcher.launch("rms_tiles", grid, [xb.as_raw_ptr(), yb.as_raw_mut_ptr()], s)
+    m = oracle.compare(yb.copy_to_host(s).reshape(x.shape), oracle.rms_norm_f32(x, 1e-6, f64_acc=True))
+    assert m["rel_max"] <= util.F32_REL, m
+    launcher.launch("max_tiles", grid, [xb.as_raw_ptr(), rb.as_raw_mut_ptr()], s)
+    assert np.array_equal(rb.copy_to_host(s), oracle.reduce_f32(x, "max"))
+    launcher.launch("swiglu_tiles", grid, [xb.as_raw_ptr(), ub.as_raw_ptr(), yb.as_raw_mut_ptr()], s)
+    m = oracle.compare(yb.copy_to_host(s).reshape(x.shape), oracle.silu_mul_f32(x, u, f64_acc=True))
+    assert m["rel_max"] <= util.F32_REL, m
+    assert dev.status(s) == 0

@@ -103,3 +103,45 @@ def test_compare_metrics(oracle):
     m = oracle.compare(y, r, floor_r=0.5)
     assert m["max_abs"] == 0.5 and m["max_ref"] == 4.0 and m["rel_max"] == 0.125
     assert abs(m["rel_fro"] - 0.5 / np.sqrt(21.0)) < 1e-12 and m["max_elem_rel"] == 0.5
+
+
+def test_row_operators_match_golden(oracle):
+    g = np.load(GOLD / "rowops.npz")
+    x, eps = g["x"], float(g["eps"])
+    assert np.abs(oracle.rms_norm_f32(x, eps) / g["rms"] - 1).max() <= 2e-6
+    assert np.abs(oracle.rms_norm_f32(x, eps, f64_acc=True) / g["rms"] - 1).max() <= 6.1e-8
+    assert np.abs(oracle.reduce_f32(x, "sum") - g["row_sum"]).max() <= 2e-4   # 96 terms of size ~3 in f32
+    assert np.abs(oracle.reduce_f32(x, "sum", f64_acc=True) - g["row_sum"]).max() <= 2e-6
+    assert np.array_equal(oracle.reduce_f32(x, "max"), g["row_max"].astype(np.float32))
+    def rel(a, ref):  # error relative to the largest magnitude (values reach ~15 and ~40 here)
+        return np.abs(a - ref).max() / np.abs(ref).max()
+    assert rel(oracle.silu_mul_f32(g["gate"], None), g["silu"]) <= 2e-7       # f32 exp and divide against float64
+    assert rel(oracle.silu_mul_f32(g["gate"], g["up"]), g["silu_mul"]) <= 2e-7
+    assert rel(oracle.silu_mul_f32(g["gate"], g["up"], f64_acc=True), g["silu_mul"]) <= 6.1e-8  # one f32 rounding
+
+
+def test_row_operators_known_answers_and_bf16(oracle):
+    # a row of equal magnitudes normalises to +-1 (eps = 0); scaling the input leaves rms_norm unchanged
+    x = np.array([[2.0, -2.0, 2.0, -2.0], [0.5, 0.5, 0.5, 0.5]], np.float32)
+    assert np.array_equal(oracle.rms_norm_f32(x, 0.0), np.sign(x))
+    rng = np.random.default_rng(11)
+    r = rng.standard_normal((5, 64)).astype(np.float32)
+    assert np.abs(oracle.rms_norm_f32(r, 0.0) - oracle.rms_norm_f32(4.0 * r, 0.0)).max() <= 1e-6
+    # an all-zero row: rsqrt(eps) * 0 = 0
+    assert np.array_equal(oracle.rms_norm_f32(np.zeros((1, 8), np.float32), 1e-6), np.zeros((1, 8), np.float32))
+    # empty rows: the fill values of the reductions
+    e = np.zeros((3, 0), np.float32)
+    assert np.array_equal(oracle.reduce_f32(e, "sum"), np.zeros(3, np.float32))
+    assert np.all(np.isneginf(oracle.reduce_f32(e, "max")))
+    # silu: 0 -> 0, large positive -> x, large negative -> -0
+    s = oracle.silu_mul_f32(np.array([0.0, 50.0, -200.0], np.float32), None)
+    assert s[0] == 0.0 and s[1] == 50.0 and s[2] == 0.0
+    # bf16 I/O: widen, f32 math, one RNE rounding
+    xb = oracle.f32_to_bf16(r)
+    y32, y16 = oracle.rms_norm_bf16(xb, 1e-5)
+    assert np.abs(y32 - onp.rms_norm(onp.bf16_bits_to_f32(xb), 1e-5)).max() <= 2e-6
+    assert np.array_equal(y16, onp.f32_to_bf16_bits(y32))
+    gb, ub = oracle.f32_to_bf16(3 * r), oracle.f32_to_bf16(r[::-1].copy())
+    s32, s16 = oracle.silu_mul_bf16(gb, ub)
+    assert np.abs(s32 - onp.silu_mul(onp.bf16_bits_to_f32(gb), onp.bf16_bits_to_f32(ub))).max() <= 2e-6
+    assert np.array_equal(s16, onp.f32_to_bf16_bits(s32))

@@ -28,6 +28,21 @@ class GemmDesc(C.Structure):
                 ("m", c_i64), ("n", c_i64), ("k", c_i64)]
 
 
+class RmsNormDesc(C.Structure):
+    _fields_ = [("dtype", c_i32), ("rows", c_i64), ("cols", c_i64), ("eps", C.c_float)]
+
+
+class ReduceDesc(C.Structure):
+    _fields_ = [("dtype", c_i32), ("kind", c_i32), ("rows", c_i64), ("cols", c_i64)]
+
+
+class SiluMulDesc(C.Structure):
+    _fields_ = [("dtype", c_i32), ("rows", c_i64), ("cols", c_i64)]
+
+
+REDUCE_SUM, REDUCE_MAX = 0, 1
+
+
 class AttentionDesc(C.Structure):
     _fields_ = [("dtype", c_i32), ("causal", c_i32), ("batch", c_i32), ("heads_q", c_i32),
                 ("heads_kv", c_i32), ("seq", c_i32), ("head_dim", c_i32)]
@@ -66,6 +81,9 @@ PROTOTYPES = {
     "tsm100_module_unload": (c_i32, [c_vp]),
     "tsm100_launch": (c_i32, [c_vp, C.c_char_p, c_u32, P(c_vp), c_u32, c_vp]),
     "tsm100_softmax": (c_i32, [c_vp, P(SoftmaxDesc), c_vp, c_vp, c_vp]),
+    "tsm100_rms_norm": (c_i32, [c_vp, P(RmsNormDesc), c_vp, c_vp, c_vp]),
+    "tsm100_reduce": (c_i32, [c_vp, P(ReduceDesc), c_vp, c_vp, c_vp]),
+    "tsm100_silu_mul": (c_i32, [c_vp, P(SiluMulDesc), c_vp, c_vp, c_vp, c_vp]),
     "tsm100_gemm": (c_i32, [c_vp, P(GemmDesc), c_vp, c_vp, c_vp, c_vp]),
     "tsm100_gemm_static_scratch": (c_i32, [P(GemmDesc), c_vp, c_vp, c_vp, c_vp, P(c_u32)]),
     "tsm100_attention": (c_i32, [c_vp, P(AttentionDesc), c_vp, c_vp, c_vp, c_vp, c_vp]),

@@ -63,6 +63,28 @@ int32_t tsm100_softmax(tsm100_device_t dev, const tsm100_softmax_desc* desc, con
   return finish(ops::softmax(&err, desc, x, y, stream), err);
 }
 
+int32_t tsm100_rms_norm(tsm100_device_t dev, const tsm100_rms_norm_desc* desc, const void* x, void* y, void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::rms_norm(&err, desc, x, y, stream), err);
+}
+
+int32_t tsm100_reduce(tsm100_device_t dev, const tsm100_reduce_desc* desc, const void* x, void* y, void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::reduce(&err, desc, x, y, stream), err);
+}
+
+int32_t tsm100_silu_mul(tsm100_device_t dev, const tsm100_silu_mul_desc* desc, const void* gate, const void* up, void* y,
+                        void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::silu_mul(&err, desc, gate, up, y, stream), err);
+}
+
 int32_t tsm100_gemm(tsm100_device_t dev, const tsm100_gemm_desc* desc, const void* a, const void* b, void* c,
                     void* stream) {
   int32_t st = use_device(dev);

@@ -22,6 +22,7 @@
 // Anything outside the target's scope is an error, never a TODO comment.
 #include <cmath>
 #include <cstdint>
+#include <cstdio>
 #include <cstring>
 #include <map>
 #include <sstream>
@@ -251,7 +252,8 @@ bool suffix_dtype(const std::string& callee, Dt* d) {
   return false;
 }
 
-enum class Kind { Load, Softmax, Matmul, MatmulT, Transpose, Scale, CausalMask, Attention, AttentionGqa };
+enum class Kind { Load, Softmax, Matmul, MatmulT, Transpose, Scale, CausalMask, Attention, AttentionGqa,
+                  RmsNorm, ReduceSum, ReduceMax, Silu, Mul };
 
 struct Tile {
   Kind kind = Kind::Load;
@@ -260,14 +262,14 @@ struct Tile {
   long rows = 0, cols = 0;
   std::vector<std::string> in;  // producer tiles
   long m = 0, k = 0, n = 0;     // Matmul*
-  double scalar = 0;            // Scale
+  double scalar = 0;            // Scale: factor; RmsNorm: eps
   long heads = 0, kv_heads = 0, seq = 0, dim = 0;  // Attention*
 };
 
 struct Kernel {
   std::string name;
   int nargs = 0;
-  std::string op;        // "softmax" | "gemm" | "attention"
+  std::string op;        // "softmax" | "gemm" | "attention" | "rms_norm" | "reduce" | "silu_mul"
   std::string summary;   // comment line
   std::string body;      // statements of the launcher
   std::string instantiation;  // explicit instantiation(s) of the __global__ kernel(s)
@@ -330,6 +332,20 @@ std::string softmax_instantiation(Dt d, long cols) {
     return "template __global__ void tsm100::softmax::softmax_rows_cta<" + t + ", " + shape + ">" + sig;
   }
   return "";
+}
+
+// The same for the rms_norm / reduce kernels (ops.cuh: row_op_typed).
+std::string row_op_instantiation(Dt d, const char* op, long cols) {
+  const long per_vec = d == Dt::F32 ? 4 : 8;
+  const std::string t = cxx_type(d);
+  const long nvec = cols / per_vec;
+  if (cols % per_vec != 0 || nvec > 2048)
+    return "template __global__ void tsm100::rowops::row_op_stream_kernel<" + t + ", tsm100::rowops::" + op + ", 512>(const " + t +
+           "*, " + t + "*, int64_t, int64_t, float);\n";
+  const char* shape = nvec <= 32 ? "1, 32, 128" : nvec <= 64 ? "2, 32, 128" : nvec <= 128 ? "4, 32, 128" : nvec <= 256 ? "8, 32, 128"
+                    : nvec <= 512 ? "4, 128, 128" : nvec <= 1024 ? "8, 128, 128" : "8, 256, 256";
+  return "template __global__ void tsm100::rowops::row_op_kernel<" + t + ", tsm100::rowops::" + op + ", " + shape + ">(const " + t + "*, " +
+         t + "*, int64_t, int32_t, float);\n";
 }
 
 Kernel lower(const Func& f) {
@@ -410,6 +426,48 @@ Kernel lower(const Func& f) {
         t.cols = cx.int_of(c.args[3], "cols");
         t.dtype = cx.tile_of(c.args[1]).dtype;
         cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_rms_norm_") && has_dt && !contains(fn, "_mul_") && fn.back() != '4') {
+        need(5);  // (dst, src, eps, rows, cols)
+        Tile t;
+        t.kind = Kind::RmsNorm;
+        t.in = {c.args[1]};
+        auto it = cx.floats.find(c.args[2]);
+        t.scalar = it == cx.floats.end() ? 1e-5 : it->second;  // the reference's NVIDIA emitter falls back to 1e-5
+        t.rows = cx.int_of(c.args[3], "rows");
+        t.cols = cx.int_of(c.args[4], "cols");
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else if ((starts_with(fn, "__tile_reduce_sum_") || starts_with(fn, "__tile_reduce_max_")) && has_dt) {
+        need(4);  // (dst, src, rows, cols) -> a rows x 1 tile
+        Tile t;
+        t.kind = starts_with(fn, "__tile_reduce_sum_") ? Kind::ReduceSum : Kind::ReduceMax;
+        t.in = {c.args[1]};
+        t.rows = cx.int_of(c.args[2], "rows");
+        t.cols = cx.int_of(c.args[3], "cols");  // width of the reduced tile; the result has one column
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_silu_") && has_dt && fn.back() != '4' && !contains(fn, "scalar")) {
+        need(4);
+        Tile t;
+        t.kind = Kind::Silu;
+        t.in = {c.args[1]};
+        t.rows = cx.int_of(c.args[2], "rows");
+        t.cols = cx.int_of(c.args[3], "cols");
+        t.dtype = cx.tile_of(c.args[1]).dtype;
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_mul_") && has_dt) {
+        // (dst, a, b, rows, cols), or the four-operand form (a, b, rows, cols) the reference's
+        // SiLU*Mul fusion also accepts
+        if (c.args.size() != 5 && c.args.size() != 4)
+          reject("kernel " + f.name + ": " + fn + " expects 4 or 5 operands, got " + std::to_string(c.args.size()));
+        const size_t o = c.args.size() == 5 ? 1 : 0;
+        Tile t;
+        t.kind = Kind::Mul;
+        t.in = {c.args[o], c.args[o + 1]};
+        t.rows = cx.int_of(c.args[o + 2], "rows");
+        t.cols = cx.int_of(c.args[o + 3], "cols");
+        t.dtype = cx.tile_of(c.args[o]).dtype;
+        cx.tiles[c.result] = t;
       } else if ((starts_with(fn, "__tile_matmul_transposed_") || starts_with(fn, "__tile_matmul_")) && has_dt &&
                  !contains(fn, "dequant") && !contains(fn, "_i8")) {
         need(6);
@@ -480,7 +538,7 @@ Kernel lower(const Func& f) {
         t.dtype = cx.tile_of(c.args[1]).dtype;
         cx.tiles[c.result] = t;
       } else {
-        reject("kernel " + f.name + ": intrinsic " + fn + " is outside the cuda_sm100 target (matmul, softmax, attention)");
+        reject("kernel " + f.name + ": intrinsic " + fn + " is outside the cuda_sm100 target (matmul, softmax, attention, rms_norm, reduce_sum/max, silu, silu*mul)");
       }
       continue;
     }
@@ -534,6 +592,67 @@ Kernel lower(const Func& f) {
     else
       inst << "template __global__ void tsm100::softmax::softmax_rows_stream<" << cxx_type(x.dtype) << ", 512>(const "
            << cxx_type(x.dtype) << "*, " << cxx_type(x.dtype) << "*, int64_t, int64_t);\n";
+  } else if (root.kind == Kind::RmsNorm) {
+    const Tile& x = load_of(root.in[0], "rms_norm input");
+    if (x.rows != root.rows || x.cols != root.cols || store_rows != root.rows || store_cols != root.cols)
+      reject("kernel " + f.name + ": rms_norm tile shapes disagree between load, op and store");
+    if (out_dt != x.dtype) reject("kernel " + f.name + ": rms_norm input and output storage types differ");
+    k.op = "rms_norm";
+    sum << "__tile_rms_norm on " << root.rows << " x " << root.cols << " " << dt_name(x.dtype) << " tiles, one per block";
+    char eps_lit[48];
+    snprintf(eps_lit, sizeof eps_lit, "%.9gf", static_cast<double>(static_cast<float>(root.scalar)));
+    std::string eps_s = eps_lit;
+    if (eps_s.find('.') == std::string::npos && eps_s.find('e') == std::string::npos) eps_s.insert(eps_s.size() - 1, ".0");
+    body << "  tsm100_rms_norm_desc d;\n  d.dtype = " << dt_enum(x.dtype) << ";\n  d.rows = static_cast<int64_t>(blocks) * " << root.rows
+         << ";\n  d.cols = " << root.cols << ";\n  d.eps = " << eps_s << ";\n"
+         << "  st = tsm100::ops::rms_norm(&msg, &d, args[" << x.arg << "], args[" << store_arg << "], stream);\n";
+    inst << row_op_instantiation(x.dtype, "kRmsNorm", root.cols);
+  } else if (root.kind == Kind::ReduceSum || root.kind == Kind::ReduceMax) {
+    const Tile& x = load_of(root.in[0], "reduce input");
+    if (x.rows != root.rows || x.cols != root.cols || store_rows != root.rows || store_cols != 1)
+      reject("kernel " + f.name + ": a row reduction stores a rows x 1 tile of the loaded tile's rows");
+    if (out_dt != x.dtype) reject("kernel " + f.name + ": reduce input and output storage types differ");
+    const bool is_max = root.kind == Kind::ReduceMax;
+    k.op = "reduce";
+    sum << "__tile_reduce_" << (is_max ? "max" : "sum") << " on " << root.rows << " x " << root.cols << " " << dt_name(x.dtype)
+        << " tiles, one per block";
+    body << "  tsm100_reduce_desc d;\n  d.dtype = " << dt_enum(x.dtype) << ";\n  d.kind = "
+         << (is_max ? "TSM100_REDUCE_MAX" : "TSM100_REDUCE_SUM") << ";\n  d.rows = static_cast<int64_t>(blocks) * " << root.rows
+         << ";\n  d.cols = " << root.cols << ";\n"
+         << "  st = tsm100::ops::reduce(&msg, &d, args[" << x.arg << "], args[" << store_arg << "], stream);\n";
+    inst << row_op_instantiation(x.dtype, is_max ? "kReduceMax" : "kReduceSum", root.cols);
+  } else if (root.kind == Kind::Silu || root.kind == Kind::Mul) {
+    // silu(gate), or silu(gate) * up with the pair fused as the reference's NVIDIA emitter does
+    const Tile* silu = &root;
+    const Tile* up = nullptr;
+    if (root.kind == Kind::Mul) {
+      const Tile& a = cx.tile_of(root.in[0]);
+      const Tile& b = cx.tile_of(root.in[1]);
+      if (a.kind == Kind::Silu && b.kind == Kind::Load) { silu = &a; up = &b; }
+      else if (b.kind == Kind::Silu && a.kind == Kind::Load) { silu = &b; up = &a; }
+      else reject("kernel " + f.name + ": an element-wise product is supported as silu(gate) * up of two loaded tiles");
+    }
+    const Tile& gate = load_of(silu->in[0], "silu input");
+    if (gate.rows != root.rows || gate.cols != root.cols || store_rows != root.rows || store_cols != root.cols ||
+        (up && (up->rows != root.rows || up->cols != root.cols)))
+      reject("kernel " + f.name + ": silu / mul tile shapes disagree between loads, ops and store");
+    if (out_dt != gate.dtype || (up && up->dtype != gate.dtype))
+      reject("kernel " + f.name + ": silu / mul operands and output must share one storage type");
+    k.op = "silu_mul";
+    sum << (up ? "__tile_silu * __tile_mul fused" : "__tile_silu") << " on " << root.rows << " x " << root.cols << " "
+        << dt_name(gate.dtype) << " tiles, one per block";
+    body << "  tsm100_silu_mul_desc d;\n  d.dtype = " << dt_enum(gate.dtype) << ";\n  d.rows = static_cast<int64_t>(blocks) * " << root.rows
+         << ";\n  d.cols = " << root.cols << ";\n"
+         << "  st = tsm100::ops::silu_mul(&msg, &d, args[" << gate.arg << "], " << (up ? "args[" + std::to_string(up->arg) + "]" : std::string("nullptr"))
+         << ", args[" << store_arg << "], stream);\n";
+    const std::string t = cxx_type(gate.dtype);
+    const long per_vec = gate.dtype == Dt::F32 ? 4 : 8;
+    if ((root.rows * root.cols) % per_vec == 0)
+      inst << "template __global__ void tsm100::rowops::silu_mul_kernel<" << t << ", " << (up ? "true" : "false") << ", 4, 256>(const " << t
+           << "*, const " << t << "*, " << t << "*, int64_t);\n";
+    else
+      inst << "template __global__ void tsm100::rowops::silu_mul_scalar_kernel<" << t << ", " << (up ? "true" : "false") << ", 256>(const " << t
+           << "*, const " << t << "*, " << t << "*, int64_t);\n";
   } else if (root.kind == Kind::Matmul || root.kind == Kind::MatmulT) {
     const Tile* prod = &root;
     bool causal_chain = false;
@@ -639,7 +758,7 @@ Kernel lower(const Func& f) {
            << cxx_type(q.dtype) << "*, const " << cxx_type(q.dtype) << "*, const " << cxx_type(q.dtype) << "*, " << cxx_type(q.dtype)
            << "*, const tsm100::attn_simt::Params);\n";
   } else {
-    reject("kernel " + f.name + ": the stored tile is not produced by matmul, softmax or attention");
+    reject("kernel " + f.name + ": the stored tile is not produced by an operator of the cuda_sm100 target");
   }
   k.summary = sum.str();
   k.body = body.str();

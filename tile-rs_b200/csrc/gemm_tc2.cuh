@@ -34,7 +34,10 @@ constexpr int kABytes = kCtaM * kBK * 2;  // 16 KiB
 constexpr int kBBytes = kCtaN * kBK * 2;  // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 512;
-constexpr int kGroupM = 8;
+#ifndef TSM100_GEMM_GROUP_M
+#define TSM100_GEMM_GROUP_M 8
+#endif
+constexpr int kGroupM = TSM100_GEMM_GROUP_M;  // pair tiles per band: the band's rows of A stay in L2 while B streams
 
 struct alignas(8) Barriers {
   uint64_t full[kStages];      // used in the leader: both CTAs' bytes of a stage have landed

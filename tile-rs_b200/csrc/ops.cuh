@@ -21,6 +21,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_tc2.cuh"
+#include "rowops.cuh"
 #include "softmax.cuh"
 
 namespace tsm100 {
@@ -183,6 +184,123 @@ inline int32_t softmax(std::string* err, const tsm100_softmax_desc* d, const voi
                                           static_cast<__nv_bfloat16*>(y), d->rows, d->cols, s);
     default:
       return softmax_typed<__half>(err, static_cast<const __half*>(x), static_cast<__half*>(y), d->rows, d->cols, s);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// rms_norm / row reductions / SiLU * Mul
+// ---------------------------------------------------------------------------
+template <typename T, int OP>
+inline int32_t row_op_typed(std::string* err, const T* x, T* y, int64_t rows, int64_t cols, float eps, cudaStream_t s) {
+  namespace ro = rowops;
+  constexpr int PV = softmax::Elem<T>::kPerVec;
+  const bool vec_ok = (cols % PV == 0) && aligned16(x) && (OP != ro::kRmsNorm || aligned16(y));
+  const int64_t nvec = cols / PV;
+  int sms = 0;
+  int32_t st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  // persistent CTAs: exactly as many as are resident at once, each striding over the rows
+  auto launch = [&](auto kern, int threads, int rows_per_cta) {
+    int per_sm = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    const int64_t want = (rows + rows_per_cta - 1) / rows_per_cta;
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(want, static_cast<int64_t>(sms) * per_sm));
+    kern<<<grid, threads, 0, s>>>(x, y, rows, static_cast<int32_t>(cols), eps);
+  };
+  if (vec_ok && nvec <= 32 * 8) {  // one warp per row, four rows per CTA
+    if (nvec <= 32 * 1) launch(ro::row_op_kernel<T, OP, 1, 32, 128>, 128, 4);
+    else if (nvec <= 32 * 2) launch(ro::row_op_kernel<T, OP, 2, 32, 128>, 128, 4);
+    else if (nvec <= 32 * 4) launch(ro::row_op_kernel<T, OP, 4, 32, 128>, 128, 4);
+    else launch(ro::row_op_kernel<T, OP, 8, 32, 128>, 128, 4);
+    return cuda_ok(err, cudaGetLastError(), "row_op_kernel (warp per row) launch");
+  }
+  if (vec_ok && nvec <= 256 * 8) {  // 128 or 256 threads per row, 32 values each
+    if (nvec <= 128 * 4) launch(ro::row_op_kernel<T, OP, 4, 128, 128>, 128, 1);
+    else if (nvec <= 128 * 8) launch(ro::row_op_kernel<T, OP, 8, 128, 128>, 128, 1);
+    else launch(ro::row_op_kernel<T, OP, 8, 256, 256>, 256, 1);
+    return cuda_ok(err, cudaGetLastError(), "row_op_kernel (CTA per row) launch");
+  }
+  constexpr int THREADS = 512;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(rows, static_cast<int64_t>(sms) * 4));
+  ro::row_op_stream_kernel<T, OP, THREADS><<<grid, THREADS, 0, s>>>(x, y, rows, cols, eps);
+  return cuda_ok(err, cudaGetLastError(), "row_op_stream_kernel launch");
+}
+
+template <int OP>
+inline int32_t row_op(std::string* err, int32_t dtype, int64_t rows, int64_t cols, float eps, const void* x, void* y,
+                      void* stream, const char* what) {
+  if (!x || !y) return op_fail(err, TSM100_ERR_INVALID, std::string(what) + ": null argument");
+  if (!dtype_valid(dtype)) return op_fail(err, TSM100_ERR_INVALID, std::string(what) + ": unknown dtype");
+  if (rows < 0 || cols < 0) return op_fail(err, TSM100_ERR_INVALID, std::string(what) + ": negative shape");
+  if (rows == 0) return TSM100_OK;
+  if (cols == 0 && OP == rowops::kRmsNorm) return TSM100_OK;  // empty tile: nothing to write
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case TSM100_F32:
+      return row_op_typed<float, OP>(err, static_cast<const float*>(x), static_cast<float*>(y), rows, cols, eps, s);
+    case TSM100_BF16:
+      return row_op_typed<__nv_bfloat16, OP>(err, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
+                                              rows, cols, eps, s);
+    default:
+      return row_op_typed<__half, OP>(err, static_cast<const __half*>(x), static_cast<__half*>(y), rows, cols, eps, s);
+  }
+}
+
+inline int32_t rms_norm(std::string* err, const tsm100_rms_norm_desc* d, const void* x, void* y, void* stream) {
+  if (!d) return op_fail(err, TSM100_ERR_INVALID, "rms_norm: null descriptor");
+  return row_op<rowops::kRmsNorm>(err, d->dtype, d->rows, d->cols, d->eps, x, y, stream, "rms_norm");
+}
+
+inline int32_t reduce(std::string* err, const tsm100_reduce_desc* d, const void* x, void* y, void* stream) {
+  if (!d) return op_fail(err, TSM100_ERR_INVALID, "reduce: null descriptor");
+  if (d->kind == TSM100_REDUCE_SUM)
+    return row_op<rowops::kReduceSum>(err, d->dtype, d->rows, d->cols, 0.f, x, y, stream, "reduce");
+  if (d->kind == TSM100_REDUCE_MAX)
+    return row_op<rowops::kReduceMax>(err, d->dtype, d->rows, d->cols, 0.f, x, y, stream, "reduce");
+  return op_fail(err, TSM100_ERR_INVALID, "reduce: unknown kind");
+}
+
+template <typename T>
+inline int32_t silu_mul_typed(std::string* err, const T* gate, const T* up, T* y, int64_t n, cudaStream_t s) {
+  namespace ro = rowops;
+  constexpr int PV = softmax::Elem<T>::kPerVec;
+  constexpr int THREADS = 256, UNROLL = 4;
+  int sms = 0;
+  int32_t st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  const bool vec_ok = (n % PV == 0) && aligned16(gate) && aligned16(y) && (!up || aligned16(up));
+  if (vec_ok) {
+    const int64_t nvec = n / PV;
+    const int64_t want = (nvec + THREADS * UNROLL - 1) / (THREADS * UNROLL);
+    const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, static_cast<int64_t>(sms) * 8)));
+    if (up) ro::silu_mul_kernel<T, true, UNROLL, THREADS><<<grid, THREADS, 0, s>>>(gate, up, y, nvec);
+    else ro::silu_mul_kernel<T, false, UNROLL, THREADS><<<grid, THREADS, 0, s>>>(gate, up, y, nvec);
+    return cuda_ok(err, cudaGetLastError(), "silu_mul_kernel launch");
+  }
+  const int64_t want = (n + THREADS - 1) / THREADS;
+  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, static_cast<int64_t>(sms) * 8)));
+  if (up) ro::silu_mul_scalar_kernel<T, true, THREADS><<<grid, THREADS, 0, s>>>(gate, up, y, n);
+  else ro::silu_mul_scalar_kernel<T, false, THREADS><<<grid, THREADS, 0, s>>>(gate, up, y, n);
+  return cuda_ok(err, cudaGetLastError(), "silu_mul_scalar_kernel launch");
+}
+
+inline int32_t silu_mul(std::string* err, const tsm100_silu_mul_desc* d, const void* gate, const void* up, void* y,
+                        void* stream) {
+  if (!d || !gate || !y) return op_fail(err, TSM100_ERR_INVALID, "silu_mul: null argument");
+  if (!dtype_valid(d->dtype)) return op_fail(err, TSM100_ERR_INVALID, "silu_mul: unknown dtype");
+  if (d->rows < 0 || d->cols < 0) return op_fail(err, TSM100_ERR_INVALID, "silu_mul: negative shape");
+  if (d->rows == 0 || d->cols == 0) return TSM100_OK;
+  const int64_t n = d->rows * d->cols;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (d->dtype) {
+    case TSM100_F32:
+      return silu_mul_typed<float>(err, static_cast<const float*>(gate), static_cast<const float*>(up), static_cast<float*>(y), n, s);
+    case TSM100_BF16:
+      return silu_mul_typed<__nv_bfloat16>(err, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up),
+                                           static_cast<__nv_bfloat16*>(y), n, s);
+    default:
+      return silu_mul_typed<__half>(err, static_cast<const __half*>(gate), static_cast<const __half*>(up),
+                                    static_cast<__half*>(y), n, s);
   }
 }
 

@@ -367,6 +367,20 @@ class CudaSm100Device:
         d = capi.SoftmaxDesc(dtype, rows, cols)
         check(capi.lib().tsm100_softmax(self._h, C.byref(d), x, y, stream or None))
 
+    def rms_norm(self, dtype: int, rows: int, cols: int, eps: float, x: int, y: int, stream: int = 0) -> None:
+        d = capi.RmsNormDesc(dtype, rows, cols, eps)
+        check(capi.lib().tsm100_rms_norm(self._h, C.byref(d), x, y, stream or None))
+
+    def reduce(self, dtype: int, kind: int, rows: int, cols: int, x: int, y: int, stream: int = 0) -> None:
+        """Row sums (capi.REDUCE_SUM) or maxima (capi.REDUCE_MAX) of a rows x cols tile into y[rows]."""
+        d = capi.ReduceDesc(dtype, kind, rows, cols)
+        check(capi.lib().tsm100_reduce(self._h, C.byref(d), x, y, stream or None))
+
+    def silu_mul(self, dtype: int, rows: int, cols: int, gate: int, up: Optional[int], y: int, stream: int = 0) -> None:
+        """y = silu(gate) * up; up=None gives silu(gate)."""
+        d = capi.SiluMulDesc(dtype, rows, cols)
+        check(capi.lib().tsm100_silu_mul(self._h, C.byref(d), gate, up or None, y, stream or None))
+
     def gemm(self, dtype: int, m: int, n: int, k: int, a: int, b: int, c: int, *, out_dtype: Optional[int] = None,
              b_transposed: bool = False, batch: int = 1, stream: int = 0) -> None:
         d = capi.GemmDesc(dtype, dtype if out_dtype is None else out_dtype, int(b_transposed), batch, m, n, k)
