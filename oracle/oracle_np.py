@@ -54,6 +54,19 @@ def silu_mul(gate: np.ndarray, up=None) -> np.ndarray:
     return s if up is None else s * up.astype(np.float64)
 
 
+# Element-wise operators in float64, as the linalg bridge defines them (mlir_to_linalg.rs:422-470 named
+# linalg ops; :756-790 rsqrt / sigmoid / silu / relu; :805-905 scale; :907-982 clamp = min(max(x, lo), hi)).
+EWISE = {
+    "add": lambda a, b: a + b, "sub": lambda a, b: a - b, "mul": lambda a, b: a * b, "div": lambda a, b: a / b,
+    "max": np.maximum, "min": np.minimum,
+    "exp": np.exp, "log": np.log, "neg": lambda a: -a, "tanh": np.tanh, "abs": np.abs, "sqrt": np.sqrt,
+    "rsqrt": lambda a: 1.0 / np.sqrt(a), "sigmoid": lambda a: 1.0 / (1.0 + np.exp(-a)),
+    "silu": lambda a: a / (1.0 + np.exp(-a)), "relu": lambda a: np.maximum(a, 0.0),
+    "scale": lambda a, c: a * np.float64(np.float32(c)),
+    "clamp": lambda a, lo, hi: np.minimum(np.maximum(a, np.float64(np.float32(lo))), np.float64(np.float32(hi))),
+}
+
+
 def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, causal: bool) -> np.ndarray:
     """transpose, matmul, scale 1/sqrt(D), [causal mask col > row -> -inf], softmax, matmul
     (mlir_to_linalg.rs:1781-1902, :1191-1244); grouped KV heads with

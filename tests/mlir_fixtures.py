@@ -105,11 +105,67 @@ GENERIC_SOFTMAX = '''"builtin.module"() ({
 }) : () -> ()
 '''
 
-ADD_OUT_OF_SCOPE = module("add_test", 3, consts(r=1, c=256) + [
+OUT_OF_SCOPE = module("rope_test", 2, consts(r=1, c=256, pos=7) + [
     "%a = llvm.call @__tile_load_f32(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
-    "%b = llvm.call @__tile_load_f32(%arg1, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
-    "%s = llvm.call @__tile_add_f32(%a, %a, %b, %r, %c) : (i32, i32, i32, i32, i32) -> i32",
-    "llvm.call @__tile_store_f32(%arg2, %s, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+    "%s = llvm.call @__tile_rope_f32(%a, %a, %pos, %r, %c) : (i32, i32, i32, i32, i32) -> i32",
+    "llvm.call @__tile_store_f32(%arg1, %s, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+
+
+def ewise_add(name="add_test", rows=1, cols=256, dt="f32"):
+    return module(name, 3, consts(r=rows, c=cols) + [
+        f"%a = llvm.call @__tile_load_{dt}(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%b = llvm.call @__tile_load_{dt}(%arg1, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%s = llvm.call @__tile_add_{dt}(%a, %a, %b, %r, %c) : (i32, i32, i32, i32, i32) -> i32",
+        f"llvm.call @__tile_store_{dt}(%arg2, %s, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+
+
+def ewise_chain(name="gelu_like", rows=2, cols=512, dt="f32", out_dt=None):
+    """out = clamp(tanh(scale(x, 0.5)) * y + exp(neg(abs(x))), -0.75, 2.5) / max(sqrt(abs(y)), sigmoid(x)): thirteen
+    operators, two inputs (x is used four times), one pass."""
+    out_dt = out_dt or dt
+    u = "(i32, i32, i32, i32) -> i32"
+    b = "(i32, i32, i32, i32, i32) -> i32"
+    return module(name, 3, consts(c0=0, r=rows, c=cols) + [
+        "%half = llvm.mlir.constant(5.000000e-01 : f32) : f32",
+        "%lo = llvm.mlir.constant(-7.500000e-01 : f32) : f32",
+        "%hi = llvm.mlir.constant(2.500000e+00 : f32) : f32",
+        f"%x = llvm.call @__tile_load_{dt}(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%y = llvm.call @__tile_load_{dt}(%arg1, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%t1 = llvm.call @__tile_scale_f32(%c0, %x, %half, %r, %c) : (i32, i32, f32, i32, i32) -> i32",
+        f"%t2 = llvm.call @__tile_tanh_f32(%c0, %t1, %r, %c) : {u}",
+        f"%t3 = llvm.call @__tile_mul_f32(%c0, %t2, %y, %r, %c) : {b}",
+        f"%t4 = llvm.call @__tile_abs_f32(%c0, %x, %r, %c) : {u}",
+        f"%t5 = llvm.call @__tile_neg_f32(%c0, %t4, %r, %c) : {u}",
+        f"%t6 = llvm.call @__tile_exp_f32(%c0, %t5, %r, %c) : {u}",
+        f"%t7 = llvm.call @__tile_add_f32(%c0, %t3, %t6, %r, %c) : {b}",
+        f"%t8 = llvm.call @__tile_clamp_f32(%c0, %t7, %lo, %hi, %r, %c) : (i32, i32, f32, f32, i32, i32) -> i32",
+        f"%t9 = llvm.call @__tile_abs_f32(%c0, %y, %r, %c) : {u}",
+        f"%t10 = llvm.call @__tile_sqrt_f32(%c0, %t9, %r, %c) : {u}",
+        f"%t11 = llvm.call @__tile_sigmoid_f32(%c0, %x, %r, %c) : {u}",
+        f"%t12 = llvm.call @__tile_max_f32(%c0, %t10, %t11, %r, %c) : {b}",
+        f"%t13 = llvm.call @__tile_div_f32(%c0, %t8, %t12, %r, %c) : {b}",
+        f"llvm.call @__tile_store_{out_dt}(%arg2, %t13, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+
+
+def ewise_misc(name="misc_ops", rows=3, cols=333, dt="f32"):
+    """out = min(relu(x) - rsqrt(fill(4.0)), log(silu(x) * silu(x) + fill(1.0))): the remaining operators, odd width."""
+    u = "(i32, i32, i32, i32) -> i32"
+    b = "(i32, i32, i32, i32, i32) -> i32"
+    return module(name, 2, consts(c0=0, r=rows, c=cols) + [
+        "%four = llvm.mlir.constant(4.000000e+00 : f32) : f32",
+        "%one = llvm.mlir.constant(1.000000e+00 : f32) : f32",
+        f"%x = llvm.call @__tile_load_{dt}(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%f4 = llvm.call @__tile_fill_f32(%c0, %four, %r, %c) : (i32, f32, i32, i32) -> i32",
+        f"%f1 = llvm.call @__tile_fill_f32(%c0, %one, %r, %c) : (i32, f32, i32, i32) -> i32",
+        f"%t1 = llvm.call @__tile_relu_f32(%c0, %x, %r, %c) : {u}",
+        f"%t2 = llvm.call @__tile_rsqrt_f32(%c0, %f4, %r, %c) : {u}",
+        f"%t3 = llvm.call @__tile_sub_f32(%c0, %t1, %t2, %r, %c) : {b}",
+        f"%t4 = llvm.call @__tile_silu_f32(%c0, %x, %r, %c) : {u}",
+        f"%t5 = llvm.call @__tile_mul_f32(%c0, %t4, %t4, %r, %c) : {b}",
+        f"%t6 = llvm.call @__tile_add_f32(%c0, %t5, %f1, %r, %c) : {b}",
+        f"%t7 = llvm.call @__tile_log_f32(%c0, %t6, %r, %c) : {u}",
+        f"%t8 = llvm.call @__tile_min_f32(%c0, %t3, %t7, %r, %c) : {b}",
+        f"llvm.call @__tile_store_{dt}(%arg1, %t8, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
 
 
 def rms_norm(name="tile_rms", rows=1, cols=256, dt="f32", eps="1.0e-5"):

@@ -74,6 +74,11 @@ CASES = {
     "reduce_sum": (F.reduce("sum"), ["row_op_kernel<float, tsm100::rowops::kReduceSum, 8, 32, 128>", "TSM100_REDUCE_SUM", "d.cols = 1024"]),
     "reduce_max": (F.reduce("max", cols=5000), ["row_op_kernel<float, tsm100::rowops::kReduceMax, 8, 256, 256>", "TSM100_REDUCE_MAX"]),
     "reduce_odd_width": (F.reduce("sum", cols=1001), ["row_op_stream_kernel<float, tsm100::rowops::kReduceSum, 512>"]),
+    "ewise_add": (F.ewise_add(), ["add_test_ewise_vec", "a0[e] + a1[e]".replace("a0[e] + a1[e]", "v0 + v1"), "out = add(in0, in1)", "one pass"]),
+    "ewise_chain": (F.ewise_chain(), ["gelu_like_ewise_vec(const float* __restrict__ p0, const float* __restrict__ p1, float* __restrict__ out",
+                                      "tanhf(", "op_clamp(", "-0.75f, 2.5f", "op_sigmoid(", "fmaxf(", "* 0.5f", "blocks) * 2 * 512"]),
+    "ewise_chain_bf16_to_f32": (F.ewise_chain(dt="bf16", out_dt="f32"), ["const __nv_bfloat16* __restrict__ p0", "float* __restrict__ out"]),
+    "ewise_misc": (F.ewise_misc(), ["op_relu(", "op_rsqrt(", "op_silu(", "logf(", "fminf(", "4.0f", "misc_ops_ewise_scalar"]),
     "silu": (F.silu(), ["silu_mul_kernel<float, false, 4, 256>", "nullptr, args[1]", "tsm100::ops::silu_mul"]),
     "silu_mul": (F.silu_mul(), ["silu_mul_kernel<float, true, 4, 256>", "args[0], args[1], args[2]", "fused"]),
     "silu_mul_up_first_f16": (F.silu_mul(dt="f16", up_first=True, cols=4096), ["silu_mul_kernel<__half, true, 4, 256>", "args[0], args[1], args[2]"]),
@@ -109,10 +114,12 @@ def test_non_entry_functions_are_ignored(target):
     ("", "empty MLIR module"), ("  \n\t ", "empty MLIR module"),
     ("module {\n}\n", "no entry kernel"),
     (F.softmax().replace(" attributes {hacc.entry}", ""), "no entry kernel"),
-    (F.ADD_OUT_OF_SCOPE, "__tile_add_f32 is outside the cuda_sm100 target"),
+    (F.OUT_OF_SCOPE, "__tile_rope_f32 is outside the cuda_sm100 target"),
+    (F.ewise_add().replace("(%arg1, %r, %c)", "(%arg1, %c, %r)"), "share the stored tile's shape"),
+    (F.ewise_chain().replace("__tile_tanh_f32(%c0, %t1", "__tile_softmax_f32(%c0, %t1"), "may only consume loaded tiles"),
     (F.causal_chain(scale=0.5), "1/sqrt(head_dim)"),
     (F.reduce("sum").replace("%y, %r, %one)", "%y, %r, %c)"), "rows x 1 tile"),
-    (F.silu_mul().replace("__tile_silu_f32(%c0, %g", "__tile_softmax_f32(%c0, %g"), "silu(gate) * up"),
+    (F.silu_mul().replace("__tile_silu_f32(%c0, %g", "__tile_softmax_f32(%c0, %g"), "may only consume loaded tiles"),
     (F.rms_norm().replace("%eps, %r, %c) : (i32, i32, f32", "%eps, %r) : (i32, i32, f32"), "expects 5 operands"),
     (F.softmax().replace("%t0, %r, %c) : (i32", "%t0, %r) : (i32"), "expects 4 operands"),
     (F.softmax().replace("(%c0, %t0, %r, %c)", "(%c0, %t0, %r, %7)"), "not a compile-time integer constant"),
@@ -128,7 +135,12 @@ def test_emit_rejects(target, cg, mlir, fragment):
 
 
 def test_emitted_module_compiles(target, pkg, tmp_path):
-    """nvcc accepts what emit produces (cross-compiled for sm_100a; no GPU needed)."""
-    out = target.emit(F.softmax("sm_compile_check", rows=2, cols=512))
+    """nvcc accepts what emit produces (cross-compiled for sm_100a; no GPU needed): a library operator and
+    two generated element-wise kernels in one module."""
+    parts = [F.softmax("sm_compile_check", rows=2, cols=512), F.ewise_chain("chain_compile_check", dt="bf16", out_dt="f32"),
+             F.ewise_misc("misc_compile_check")]
+    mlir = parts[0].rsplit("}", 1)[0] + "".join(p.split("module {", 1)[1].rsplit("}", 1)[0] for p in parts[1:]) + "}\n"
+    out = target.emit(mlir)
+    assert out.meta.kernel_names == ["sm_compile_check", "chain_compile_check", "misc_compile_check"]
     so = pkg.build.build_module(out.source, tmp_path / "mod.so")
     assert so.exists() and so.stat().st_size > 0

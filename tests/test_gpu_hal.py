@@ -137,3 +137,63 @@ def test_emitted_row_operator_modules(dev, pkg, oracle, tmp_path):
     m = oracle.compare(yb.copy_to_host(s).reshape(x.shape), oracle.silu_mul_f32(x, u, f64_acc=True))
     assert m["rel_max"] <= util.F32_REL, m
     assert dev.status(s) == 0
+
+
+def test_generated_elementwise_kernels(dev, pkg, oracle, tmp_path):
+    """Chains of element-wise intrinsics are emitted as one generated kernel each; results against the
+    float64 statement of the same operators (oracle_np.EWISE)."""
+    from oracle import oracle_np as onp
+    E = onp.EWISE
+    capi = pkg.capi
+    parts = [F.ewise_chain("chain_f32", 2, 512), F.ewise_chain("chain_bf16", 2, 512, dt="bf16", out_dt="f32"),
+             F.ewise_misc("misc_f32", 3, 333), F.ewise_add("add_f16", 1, 4096, dt="f16")]
+    mlir = parts[0].rsplit("}", 1)[0] + "".join(p.split("module {", 1)[1].rsplit("}", 1)[0] for p in parts[1:]) + "}\n"
+    out, so = _module(pkg, tmp_path, mlir, "ewise")
+    assert out.meta.kernel_names == ["chain_f32", "chain_bf16", "misc_f32", "add_f16"]
+    launcher = dev.create_launcher()
+    launcher.load(so, pkg.hal.KernelMode.Vector)
+    s = dev.create_stream()
+
+    def chain(x, y):
+        x, y = x.astype(np.float64), y.astype(np.float64)
+        num = E["clamp"](E["add"](E["mul"](E["tanh"](E["scale"](x, 0.5)), y), E["exp"](E["neg"](E["abs"](x)))), -0.75, 2.5)
+        return E["div"](num, E["max"](E["sqrt"](E["abs"](y)), E["sigmoid"](x)))
+
+    blocks = 41
+    x = util.gen_normal(capi, (blocks * 2, 512), 701, 2.0)
+    y = util.gen_normal(capi, (blocks * 2, 512), 702, 1.5)
+    xb, yb = dev.alloc_from_slice(x, s), dev.alloc_from_slice(y, s)
+    ob = dev.alloc(x.size, np.float32)
+    launcher.launch("chain_f32", pkg.hal.LaunchGrid.blocks_(blocks), [xb.as_raw_ptr(), yb.as_raw_ptr(), ob.as_raw_mut_ptr()], s)
+    got = ob.copy_to_host(s).reshape(x.shape)
+    ref = chain(x, y)
+    assert np.abs(got - ref).max() / np.abs(ref).max() <= util.F32_REL
+    assert np.abs(got - ref).max() <= 1e-5 * (1.0 + np.abs(ref).max())
+
+    x16, y16 = util.to_bf16(capi, x), util.to_bf16(capi, y)
+    xb16, yb16 = dev.alloc_from_slice(x16, s), dev.alloc_from_slice(y16, s)
+    launcher.launch("chain_bf16", pkg.hal.LaunchGrid.blocks_(blocks), [xb16.as_raw_ptr(), yb16.as_raw_ptr(), ob.as_raw_mut_ptr()], s)
+    got = ob.copy_to_host(s).reshape(x.shape)
+    ref = chain(onp.bf16_bits_to_f32(x16), onp.bf16_bits_to_f32(y16))  # bf16 inputs widen exactly; the store is f32
+    assert np.abs(got - ref).max() / np.abs(ref).max() <= util.F32_REL
+
+    blocks = 7  # 7 * 3 * 333 elements: not a multiple of eight -> the scalar kernel
+    z = util.gen_normal(capi, (blocks * 3, 333), 703, 2.0)
+    zb = dev.alloc_from_slice(z, s)
+    mb = dev.alloc(z.size, np.float32)
+    launcher.launch("misc_f32", pkg.hal.LaunchGrid.blocks_(blocks), [zb.as_raw_ptr(), mb.as_raw_mut_ptr()], s)
+    got = mb.copy_to_host(s).reshape(z.shape)
+    z64 = z.astype(np.float64)
+    sl = E["silu"](z64)
+    ref = E["min"](E["sub"](E["relu"](z64), E["rsqrt"](np.full_like(z64, 4.0))), E["log"](E["add"](E["mul"](sl, sl), 1.0)))
+    assert np.abs(got - ref).max() <= 1e-5 * (1.0 + np.abs(ref).max())
+
+    a = util.f32_to_f16_bits(util.gen_normal(capi, (5, 4096), 704))
+    b = util.f32_to_f16_bits(util.gen_normal(capi, (5, 4096), 705))
+    ab, bb = dev.alloc_from_slice(a, s), dev.alloc_from_slice(b, s)
+    cb = dev.alloc(a.size, np.uint16)
+    launcher.launch("add_f16", pkg.hal.LaunchGrid.blocks_(5), [ab.as_raw_ptr(), bb.as_raw_ptr(), cb.as_raw_mut_ptr()], s)
+    got = cb.copy_to_host(s).reshape(a.shape).view(np.float16)
+    want = (a.view(np.float16).astype(np.float32) + b.view(np.float16).astype(np.float32)).astype(np.float16)
+    assert np.array_equal(got, want)  # one exact f32 sum, one RNE rounding
+    assert dev.status(s) == 0

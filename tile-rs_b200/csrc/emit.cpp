@@ -24,6 +24,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <functional>
 #include <map>
 #include <sstream>
 #include <string>
@@ -253,7 +254,7 @@ bool suffix_dtype(const std::string& callee, Dt* d) {
 }
 
 enum class Kind { Load, Softmax, Matmul, MatmulT, Transpose, Scale, CausalMask, Attention, AttentionGqa,
-                  RmsNorm, ReduceSum, ReduceMax, Silu, Mul };
+                  RmsNorm, ReduceSum, ReduceMax, Ewise };
 
 struct Tile {
   Kind kind = Kind::Load;
@@ -262,14 +263,16 @@ struct Tile {
   long rows = 0, cols = 0;
   std::vector<std::string> in;  // producer tiles
   long m = 0, k = 0, n = 0;     // Matmul*
-  double scalar = 0;            // Scale: factor; RmsNorm: eps
+  double scalar = 0;            // Scale: factor; RmsNorm: eps; Ewise scale / fill: the constant; clamp: lo
+  double scalar2 = 0;           // Ewise clamp: hi
+  std::string ew;               // Ewise: operator name ("add", "exp", "clamp", ...)
   long heads = 0, kv_heads = 0, seq = 0, dim = 0;  // Attention*
 };
 
 struct Kernel {
   std::string name;
   int nargs = 0;
-  std::string op;        // "softmax" | "gemm" | "attention" | "rms_norm" | "reduce" | "silu_mul"
+  std::string op;        // "softmax" | "gemm" | "attention" | "rms_norm" | "reduce" | "silu_mul" | "ewise"
   std::string summary;   // comment line
   std::string body;      // statements of the launcher
   std::string instantiation;  // explicit instantiation(s) of the __global__ kernel(s)
@@ -332,6 +335,35 @@ std::string softmax_instantiation(Dt d, long cols) {
     return "template __global__ void tsm100::softmax::softmax_rows_cta<" + t + ", " + shape + ">" + sig;
   }
   return "";
+}
+
+// Element-wise intrinsics `__tile_<op>_<dtype>`: 1 = unary, 2 = binary, 0 = not one of them.
+// The packed `_4` and `_scalar` variants of the ggml family are other intrinsics.
+std::string ewise_name(const std::string& callee) {
+  const size_t b = std::strlen("__tile_"), e = callee.rfind('_');
+  return (callee.size() > b && e != std::string::npos && e > b) ? callee.substr(b, e - b) : std::string();
+}
+int ewise_arity(const std::string& callee) {
+  if (!starts_with(callee, "__tile_")) return 0;
+  const std::string n = ewise_name(callee);
+  static const char* kBinary[] = {"add", "sub", "mul", "div", "max", "min"};
+  static const char* kUnary[] = {"exp", "log", "neg", "tanh", "abs", "sqrt", "rsqrt", "sigmoid", "silu", "relu"};
+  for (const char* k : kBinary)
+    if (n == k) return 2;
+  for (const char* k : kUnary)
+    if (n == k) return 1;
+  return 0;
+}
+
+std::string float_literal(double v) {
+  const float f = static_cast<float>(v);
+  if (std::isinf(f)) return f > 0 ? "INFINITY" : "(-INFINITY)";
+  if (std::isnan(f)) return "NAN";
+  char buf[48];
+  snprintf(buf, sizeof buf, "%.9g", static_cast<double>(f));
+  std::string s = buf;
+  if (s.find('.') == std::string::npos && s.find('e') == std::string::npos) s += ".0";
+  return s + "f";
 }
 
 // The same for the rms_norm / reduce kernels (ops.cuh: row_op_typed).
@@ -446,27 +478,53 @@ Kernel lower(const Func& f) {
         t.cols = cx.int_of(c.args[3], "cols");  // width of the reduced tile; the result has one column
         t.dtype = cx.tile_of(c.args[1]).dtype;
         cx.tiles[c.result] = t;
-      } else if (starts_with(fn, "__tile_silu_") && has_dt && fn.back() != '4' && !contains(fn, "scalar")) {
-        need(4);
+      } else if (has_dt && ewise_arity(fn) != 0) {
+        // element-wise intrinsics: (dst, a, b, rows, cols) / (dst, src, rows, cols); the reference's
+        // SiLU*Mul fusion also accepts the four-operand product (a, b, rows, cols)
+        const int arity = ewise_arity(fn);
         Tile t;
-        t.kind = Kind::Silu;
+        t.kind = Kind::Ewise;
+        t.ew = ewise_name(fn);
+        size_t o = 1;
+        if (arity == 2) {
+          if (c.args.size() != 5 && !(t.ew == "mul" && c.args.size() == 4))
+            reject("kernel " + f.name + ": " + fn + " expects 5 operands, got " + std::to_string(c.args.size()));
+          if (c.args.size() == 4) o = 0;
+          t.in = {c.args[o], c.args[o + 1]};
+        } else {
+          need(4);
+          t.in = {c.args[1]};
+        }
+        t.rows = cx.int_of(c.args[o + arity], "rows");
+        t.cols = cx.int_of(c.args[o + arity + 1], "cols");
+        t.dtype = cx.tile_of(t.in[0]).dtype;
+        cx.tiles[c.result] = t;
+      } else if (starts_with(fn, "__tile_clamp_") && has_dt) {
+        need(6);  // (dst, src, lo, hi, rows, cols)
+        Tile t;
+        t.kind = Kind::Ewise;
+        t.ew = "clamp";
         t.in = {c.args[1]};
-        t.rows = cx.int_of(c.args[2], "rows");
-        t.cols = cx.int_of(c.args[3], "cols");
+        auto lo = cx.floats.find(c.args[2]), hi = cx.floats.find(c.args[3]);
+        if (lo == cx.floats.end() || hi == cx.floats.end())
+          reject("kernel " + f.name + ": clamp bounds must be compile-time float constants");
+        t.scalar = lo->second;
+        t.scalar2 = hi->second;
+        t.rows = cx.int_of(c.args[4], "rows");
+        t.cols = cx.int_of(c.args[5], "cols");
         t.dtype = cx.tile_of(c.args[1]).dtype;
         cx.tiles[c.result] = t;
-      } else if (starts_with(fn, "__tile_mul_") && has_dt) {
-        // (dst, a, b, rows, cols), or the four-operand form (a, b, rows, cols) the reference's
-        // SiLU*Mul fusion also accepts
-        if (c.args.size() != 5 && c.args.size() != 4)
-          reject("kernel " + f.name + ": " + fn + " expects 4 or 5 operands, got " + std::to_string(c.args.size()));
-        const size_t o = c.args.size() == 5 ? 1 : 0;
+      } else if (starts_with(fn, "__tile_fill_") && has_dt) {
+        need(4);  // (dst, scalar, rows, cols)
         Tile t;
-        t.kind = Kind::Mul;
-        t.in = {c.args[o], c.args[o + 1]};
-        t.rows = cx.int_of(c.args[o + 2], "rows");
-        t.cols = cx.int_of(c.args[o + 3], "cols");
-        t.dtype = cx.tile_of(c.args[o]).dtype;
+        t.kind = Kind::Ewise;
+        t.ew = "fill";
+        auto it = cx.floats.find(c.args[1]);
+        if (it == cx.floats.end()) reject("kernel " + f.name + ": the fill value must be a compile-time float constant");
+        t.scalar = it->second;
+        t.rows = cx.int_of(c.args[2], "rows");
+        t.cols = cx.int_of(c.args[3], "cols");
+        t.dtype = dt;
         cx.tiles[c.result] = t;
       } else if ((starts_with(fn, "__tile_matmul_transposed_") || starts_with(fn, "__tile_matmul_")) && has_dt &&
                  !contains(fn, "dequant") && !contains(fn, "_i8")) {
@@ -538,7 +596,7 @@ Kernel lower(const Func& f) {
         t.dtype = cx.tile_of(c.args[1]).dtype;
         cx.tiles[c.result] = t;
       } else {
-        reject("kernel " + f.name + ": intrinsic " + fn + " is outside the cuda_sm100 target (matmul, softmax, attention, rms_norm, reduce_sum/max, silu, silu*mul)");
+        reject("kernel " + f.name + ": intrinsic " + fn + " is outside the cuda_sm100 target (matmul, softmax, attention, rms_norm, row reductions, element-wise operators)");
       }
       continue;
     }
@@ -621,38 +679,148 @@ Kernel lower(const Func& f) {
          << ";\n  d.cols = " << root.cols << ";\n"
          << "  st = tsm100::ops::reduce(&msg, &d, args[" << x.arg << "], args[" << store_arg << "], stream);\n";
     inst << row_op_instantiation(x.dtype, is_max ? "kReduceMax" : "kReduceSum", root.cols);
-  } else if (root.kind == Kind::Silu || root.kind == Kind::Mul) {
-    // silu(gate), or silu(gate) * up with the pair fused as the reference's NVIDIA emitter does
-    const Tile* silu = &root;
+  } else if (root.kind == Kind::Ewise || root.kind == Kind::Scale) {
+    auto is_op = [](const Tile& t, const char* name) { return t.kind == Kind::Ewise && t.ew == name; };
+    // silu(gate), or silu(gate) * up with the pair fused as the reference's NVIDIA emitter does:
+    // the library's kernel
+    const Tile* silu = nullptr;
     const Tile* up = nullptr;
-    if (root.kind == Kind::Mul) {
+    if (is_op(root, "silu") && cx.tile_of(root.in[0]).kind == Kind::Load) {
+      silu = &root;
+    } else if (is_op(root, "mul")) {
       const Tile& a = cx.tile_of(root.in[0]);
       const Tile& b = cx.tile_of(root.in[1]);
-      if (a.kind == Kind::Silu && b.kind == Kind::Load) { silu = &a; up = &b; }
-      else if (b.kind == Kind::Silu && a.kind == Kind::Load) { silu = &b; up = &a; }
-      else reject("kernel " + f.name + ": an element-wise product is supported as silu(gate) * up of two loaded tiles");
+      if (is_op(a, "silu") && b.kind == Kind::Load && cx.tile_of(a.in[0]).kind == Kind::Load) { silu = &a; up = &b; }
+      else if (is_op(b, "silu") && a.kind == Kind::Load && cx.tile_of(b.in[0]).kind == Kind::Load) { silu = &b; up = &a; }
     }
-    const Tile& gate = load_of(silu->in[0], "silu input");
-    if (gate.rows != root.rows || gate.cols != root.cols || store_rows != root.rows || store_cols != root.cols ||
-        (up && (up->rows != root.rows || up->cols != root.cols)))
-      reject("kernel " + f.name + ": silu / mul tile shapes disagree between loads, ops and store");
-    if (out_dt != gate.dtype || (up && up->dtype != gate.dtype))
-      reject("kernel " + f.name + ": silu / mul operands and output must share one storage type");
-    k.op = "silu_mul";
-    sum << (up ? "__tile_silu * __tile_mul fused" : "__tile_silu") << " on " << root.rows << " x " << root.cols << " "
-        << dt_name(gate.dtype) << " tiles, one per block";
-    body << "  tsm100_silu_mul_desc d;\n  d.dtype = " << dt_enum(gate.dtype) << ";\n  d.rows = static_cast<int64_t>(blocks) * " << root.rows
-         << ";\n  d.cols = " << root.cols << ";\n"
-         << "  st = tsm100::ops::silu_mul(&msg, &d, args[" << gate.arg << "], " << (up ? "args[" + std::to_string(up->arg) + "]" : std::string("nullptr"))
-         << ", args[" << store_arg << "], stream);\n";
-    const std::string t = cxx_type(gate.dtype);
-    const long per_vec = gate.dtype == Dt::F32 ? 4 : 8;
-    if ((root.rows * root.cols) % per_vec == 0)
-      inst << "template __global__ void tsm100::rowops::silu_mul_kernel<" << t << ", " << (up ? "true" : "false") << ", 4, 256>(const " << t
-           << "*, const " << t << "*, " << t << "*, int64_t);\n";
-    else
-      inst << "template __global__ void tsm100::rowops::silu_mul_scalar_kernel<" << t << ", " << (up ? "true" : "false") << ", 256>(const " << t
-           << "*, const " << t << "*, " << t << "*, int64_t);\n";
+    const Tile* gate = silu ? &cx.tile_of(silu->in[0]) : nullptr;
+    if (silu && out_dt == gate->dtype && (!up || up->dtype == gate->dtype)) {
+      if (gate->rows != root.rows || gate->cols != root.cols || store_rows != root.rows || store_cols != root.cols ||
+          (up && (up->rows != root.rows || up->cols != root.cols)))
+        reject("kernel " + f.name + ": silu / mul tile shapes disagree between loads, ops and store");
+      k.op = "silu_mul";
+      sum << (up ? "__tile_silu * __tile_mul fused" : "__tile_silu") << " on " << root.rows << " x " << root.cols << " "
+          << dt_name(gate->dtype) << " tiles, one per block";
+      body << "  tsm100_silu_mul_desc d;\n  d.dtype = " << dt_enum(gate->dtype) << ";\n  d.rows = static_cast<int64_t>(blocks) * " << root.rows
+           << ";\n  d.cols = " << root.cols << ";\n"
+           << "  st = tsm100::ops::silu_mul(&msg, &d, args[" << gate->arg << "], " << (up ? "args[" + std::to_string(up->arg) + "]" : std::string("nullptr"))
+           << ", args[" << store_arg << "], stream);\n";
+      const std::string t = cxx_type(gate->dtype);
+      const long per_vec = gate->dtype == Dt::F32 ? 4 : 8;
+      if ((root.rows * root.cols) % per_vec == 0)
+        inst << "template __global__ void tsm100::rowops::silu_mul_kernel<" << t << ", " << (up ? "true" : "false") << ", 4, 256>(const " << t
+             << "*, const " << t << "*, " << t << "*, int64_t);\n";
+      else
+        inst << "template __global__ void tsm100::rowops::silu_mul_scalar_kernel<" << t << ", " << (up ? "true" : "false") << ", 256>(const " << t
+             << "*, const " << t << "*, " << t << "*, int64_t);\n";
+    } else {
+      // Any other chain of element-wise operators between loads and the store: one generated
+      // kernel, one pass over memory, f32 arithmetic, 16-byte accesses.
+      if (store_rows != root.rows || store_cols != root.cols)
+        reject("kernel " + f.name + ": element-wise tile shapes disagree between op and store");
+      std::vector<std::pair<int, Dt>> inputs;     // distinct loaded pointers in order of first use
+      std::map<std::string, std::string> value;   // tile SSA -> C++ value name
+      std::map<std::string, std::string> leaf_name;  // loaded tile SSA -> "in<k>" for the summary line
+      std::ostringstream stmts, text;
+      int next_v = 0;
+      std::function<std::string(const std::string&, std::string*)> gen = [&](const std::string& ssa, std::string* expr) -> std::string {
+        auto done = value.find(ssa);
+        if (done != value.end()) {  // a value used more than once is computed once
+          if (expr) *expr = leaf_name.count(ssa) ? leaf_name[ssa] : done->second;
+          return done->second;
+        }
+        const Tile& t = cx.tile_of(ssa);
+        if (t.kind != Kind::Load && (t.rows != root.rows || t.cols != root.cols))
+          reject("kernel " + f.name + ": element-wise operands must share the stored tile's shape");
+        std::string rhs, shown;
+        if (t.kind == Kind::Load) {
+          if (t.rows != root.rows || t.cols != root.cols)
+            reject("kernel " + f.name + ": element-wise operands must share the stored tile's shape (no broadcast)");
+          size_t slot = 0;
+          while (slot < inputs.size() && inputs[slot].first != t.arg) ++slot;
+          if (slot == inputs.size()) inputs.push_back({t.arg, t.dtype});
+          else if (inputs[slot].second != t.dtype) reject("kernel " + f.name + ": one pointer is loaded with two storage types");
+          rhs = "a" + std::to_string(slot) + "[e]";
+          shown = "in" + std::to_string(slot);
+          leaf_name[ssa] = shown;
+        } else if (t.kind == Kind::Scale) {
+          std::string x;
+          gen(t.in[0], &x);
+          rhs = value[t.in[0]] + " * " + float_literal(t.scalar);
+          shown = "scale(" + x + ", " + float_literal(t.scalar) + ")";
+        } else if (t.kind == Kind::Ewise) {
+          std::string x, y;
+          if (!t.in.empty()) gen(t.in[0], &x);
+          if (t.in.size() > 1) gen(t.in[1], &y);
+          const std::string a = t.in.empty() ? "" : value[t.in[0]], b = t.in.size() > 1 ? value[t.in[1]] : "";
+          const std::string& o = t.ew;
+          if (o == "add") rhs = a + " + " + b;
+          else if (o == "sub") rhs = a + " - " + b;
+          else if (o == "mul") rhs = a + " * " + b;
+          else if (o == "div") rhs = a + " / " + b;
+          else if (o == "max") rhs = "fmaxf(" + a + ", " + b + ")";
+          else if (o == "min") rhs = "fminf(" + a + ", " + b + ")";
+          else if (o == "exp") rhs = "expf(" + a + ")";
+          else if (o == "log") rhs = "logf(" + a + ")";
+          else if (o == "neg") rhs = "-" + a;
+          else if (o == "tanh") rhs = "tanhf(" + a + ")";
+          else if (o == "abs") rhs = "fabsf(" + a + ")";
+          else if (o == "sqrt") rhs = "sqrtf(" + a + ")";
+          else if (o == "rsqrt") rhs = "tsm100::ewise::op_rsqrt(" + a + ")";
+          else if (o == "sigmoid") rhs = "tsm100::ewise::op_sigmoid(" + a + ")";
+          else if (o == "silu") rhs = "tsm100::ewise::op_silu(" + a + ")";
+          else if (o == "relu") rhs = "tsm100::ewise::op_relu(" + a + ")";
+          else if (o == "clamp") rhs = "tsm100::ewise::op_clamp(" + a + ", " + float_literal(t.scalar) + ", " + float_literal(t.scalar2) + ")";
+          else if (o == "fill") rhs = float_literal(t.scalar);
+          else reject("kernel " + f.name + ": element-wise operator " + o + " has no lowering");
+          shown = o + "(" + (o == "fill" ? float_literal(t.scalar) : x) + (y.empty() ? "" : ", " + y) +
+                  (o == "clamp" ? ", " + float_literal(t.scalar) + ", " + float_literal(t.scalar2) : "") + ")";
+        } else {
+          reject("kernel " + f.name + ": an element-wise chain may only consume loaded tiles and other element-wise results");
+        }
+        const std::string name = "v" + std::to_string(next_v++);
+        stmts << "      const float " << name << " = " << rhs << ";\n";
+        value[ssa] = name;
+        if (expr) *expr = shown;
+        return name;
+      };
+      std::string shown;
+      const std::string result = gen(stored_tile, &shown);
+      if (inputs.empty()) inputs.push_back({-1, out_dt});  // a pure fill: no input stream
+      k.op = "ewise";
+      sum << "element-wise chain fused into one pass: out = " << shown << " on " << root.rows << " x " << root.cols << " tiles, one per block";
+      const std::string to = cxx_type(out_dt);
+      std::ostringstream params, call_args, loads8, loads1, align;
+      for (size_t i = 0; i < inputs.size(); ++i) {
+        if (inputs[i].first < 0) continue;
+        const std::string ti = cxx_type(inputs[i].second);
+        params << "const " << ti << "* __restrict__ p" << i << ", ";
+        call_args << "static_cast<const " << ti << "*>(args[" << inputs[i].first << "]), ";
+        loads8 << "    float a" << i << "[8];\n    tsm100::ewise::load8(p" << i << ", i, a" << i << ");\n";
+        loads1 << "    float a" << i << "[1] = {tsm100::ewise::load1(p" << i << ", i)};\n";
+        align << " && tsm100::ops::aligned16(args[" << inputs[i].first << "])";
+      }
+      inst << "// out = " << shown << "\n"
+           << "__global__ void __launch_bounds__(256) " << f.name << "_ewise_vec(" << params.str() << to << "* __restrict__ out, int64_t n8) {\n"
+           << "  const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;\n"
+           << "  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += step) {\n"
+           << loads8.str() << "    float r[8];\n#pragma unroll\n    for (int e = 0; e < 8; ++e) {\n"
+           << stmts.str() << "      r[e] = " << result << ";\n    }\n    tsm100::ewise::store8(out, i, r);\n  }\n}\n"
+           << "__global__ void __launch_bounds__(256) " << f.name << "_ewise_scalar(" << params.str() << to << "* __restrict__ out, int64_t n) {\n"
+           << "  const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;\n"
+           << "  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += step) {\n"
+           << loads1.str() << "    const int e = 0;\n" << stmts.str() << "    tsm100::ewise::store1(out, i, " << result << ");\n  }\n}\n";
+      body << "  const int64_t n = static_cast<int64_t>(blocks) * " << root.rows << " * " << root.cols << ";\n"
+           << "  const bool vec = (n % 8 == 0)" << align.str() << " && tsm100::ops::aligned16(args[" << store_arg << "]);\n"
+           << "  int sms = 0;\n  st = tsm100::ops::sm_count(&msg, &sms);\n"
+           << "  if (st == TSM100_OK && n > 0) {\n"
+           << "    cudaStream_t s = static_cast<cudaStream_t>(stream);\n"
+           << "    const int64_t items = vec ? n / 8 : n;\n"
+           << "    const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((items + 255) / 256, static_cast<int64_t>(sms) * 8)));\n"
+           << "    if (vec) " << f.name << "_ewise_vec<<<grid, 256, 0, s>>>(" << call_args.str() << "static_cast<" << to << "*>(args[" << store_arg << "]), items);\n"
+           << "    else " << f.name << "_ewise_scalar<<<grid, 256, 0, s>>>(" << call_args.str() << "static_cast<" << to << "*>(args[" << store_arg << "]), items);\n"
+           << "    st = tsm100::ops::cuda_ok(&msg, cudaGetLastError(), \"" << f.name << " launch\");\n  }\n";
+    }
   } else if (root.kind == Kind::Matmul || root.kind == Kind::MatmulT) {
     const Tile* prod = &root;
     bool causal_chain = false;
@@ -781,7 +949,7 @@ std::string emit_source(const std::string& mlir, std::vector<std::string>* names
        "// Compile: nvcc -gencode arch=compute_100a,code=sm_100a -std=c++17 -O3 -lineinfo --expt-relaxed-constexpr \\\n"
        "//          -shared -Xcompiler -fPIC -I<tile_sm100>/csrc -cudart static -o <module>.so <this file>\n"
        "// Load with tsm100_module_load(); launch <kernel> with tsm100_launch(module, \"<kernel>\", blocks, args, nargs, stream).\n"
-       "#include <cstdint>\n#include <cstdio>\n#include <string>\n\n#include \"ops.cuh\"\n\n";
+       "#include <algorithm>\n#include <cstdint>\n#include <cstdio>\n#include <string>\n\n#include \"ops.cuh\"\n\n";
   for (const Kernel& k : kernels) {
     o << "// ---- kernel " << k.name << ": " << k.summary << "\n";
     o << k.instantiation;

@@ -18,6 +18,7 @@
 #include "../../include/tile_sm100.h"
 #include "attention_simt.cuh"
 #include "attention_tc.cuh"
+#include "ewise.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_tc2.cuh"
