@@ -275,6 +275,16 @@ int32_t tsm100_shard_range(int64_t units, int32_t world, int32_t rank, int64_t* 
  * scope — never a silent TODO comment. */
 int32_t tsm100_emit(const char* mlir, size_t mlir_len, char* source, size_t source_cap,
                     size_t* source_len, char* names, size_t names_cap, size_t* names_len);
+/* The TileKernel descriptors of the module's entry kernels ("the compiler emits a TileKernel
+ * descriptor alongside the compiled binary", crates/tile_hal/src/kernel.rs:160-181; TileOp
+ * :93-158), as a JSON array with one object per kernel in the order of tsm100_emit's names:
+ *   {"name", "mode": "Vector" | "General" (TileKernel::inferred_mode, kernel.rs:204-211),
+ *    "num_inputs", "num_outputs", "ops": [{"op": "<TileOp variant>", <its fields>} ...],
+ *    "args": [{"index", "role": "input" | "output" | "unused", "dtype", "elements_per_block"} ...]}
+ * "args" is what a launcher needs to validate buffer sizes for a LaunchGrid (blocks *
+ * elements_per_block elements of dtype).  Same purity and error behaviour as tsm100_emit. */
+int32_t tsm100_emit_descriptors(const char* mlir, size_t mlir_len, char* json, size_t json_cap,
+                                size_t* json_len);
 const char* tsm100_target_name(void); /* CodegenTarget::name -> "cuda_sm100" */
 const char* tsm100_target_ext(void);  /* EmitOut.ext        -> "cu"         */
 

@@ -144,3 +144,39 @@ def test_emitted_module_compiles(target, pkg, tmp_path):
     assert out.meta.kernel_names == ["sm_compile_check", "chain_compile_check", "misc_compile_check"]
     so = pkg.build.build_module(out.source, tmp_path / "mod.so")
     assert so.exists() and so.stat().st_size > 0
+
+
+def test_tile_kernel_descriptors(target, cg):
+    """EmitOut.meta carries one TileKernel descriptor per entry kernel (tile_hal kernel.rs:93-212)."""
+    out = target.emit(F.matmul("mm", 64, 128, 32, dt="f16", out_dt="f32"))
+    (k,) = out.meta.kernels
+    assert k.name == "mm" and k.mode == "General" and k.uses_matmul() and k.inferred_mode() == "General"
+    assert (k.num_inputs, k.num_outputs) == (2, 1)
+    assert [o.op for o in k.ops] == ["Load", "Load", "Matmul", "Store"]
+    assert k.ops[2].params == {"m": 64, "k": 128, "n": 32}
+    assert k.ops[3].params == {"rows": 64, "cols": 32, "dtype": "F32"}
+    assert [(a.role, a.dtype, a.elements_per_block) for a in k.args] == [("input", "F16", 64 * 128), ("input", "F16", 128 * 32),
+                                                                         ("output", "F32", 64 * 32)]
+    assert k.args[2].bytes_for(3) == 3 * 64 * 32 * 4
+
+    (k,) = target.emit(F.ewise_chain()).meta.kernels
+    assert k.mode == "Vector" and not k.uses_matmul()
+    assert [o.op for o in k.ops] == ["Load", "Load", "Scale", "Tanh", "Mul", "Abs", "Neg", "Exp", "Add", "Clamp", "Abs", "Sqrt",
+                                     "Sigmoid", "Max", "Div", "Store"]
+    assert k.ops[2].params == {"rows": 2, "cols": 512, "scalar": 0.5}
+    assert k.ops[9].params == {"rows": 2, "cols": 512, "lo": -0.75, "hi": 2.5}
+
+    (k,) = target.emit(F.rms_norm(rows=4, cols=4096, dt="bf16", eps="1.0e-6")).meta.kernels
+    assert [o.op for o in k.ops] == ["Load", "RmsNorm", "Store"] and abs(k.ops[1].params["eps"] - 1e-6) < 1e-12
+    (k,) = target.emit(F.reduce("max", rows=2, cols=1000)).meta.kernels
+    assert [o.op for o in k.ops] == ["Load", "ReduceMax", "Store"]
+    assert [(a.role, a.elements_per_block) for a in k.args] == [("input", 2000), ("output", 2)]
+    (k,) = target.emit(F.attention_gqa()).meta.kernels
+    assert k.mode == "General" and k.ops[3].op == "Attention" and k.ops[3].params["kv_heads"] == 2
+    (k,) = target.emit(F.causal_chain()).meta.kernels
+    assert [o.op for o in k.ops if o.op not in ("Load", "Store")] == ["Matmul", "Scale", "CausalMask", "Softmax", "Matmul"]
+    assert k.ops[3].params["b_transposed"] is True
+    two = F.softmax("k_one").rsplit("}", 1)[0] + F.matmul("k_two", dt="bf16").split("module {", 1)[1]
+    assert [k.name for k in target.emit(two).meta.kernels] == ["k_one", "k_two"]
+    with pytest.raises(cg.EmitError):
+        target.describe("")

@@ -197,3 +197,23 @@ def test_generated_elementwise_kernels(dev, pkg, oracle, tmp_path):
     want = (a.view(np.float16).astype(np.float32) + b.view(np.float16).astype(np.float32)).astype(np.float16)
     assert np.array_equal(got, want)  # one exact f32 sum, one RNE rounding
     assert dev.status(s) == 0
+
+
+def test_launch_with_tile_kernel_descriptor(dev, pkg, oracle, tmp_path):
+    """KernelLauncher.launch_described: the descriptor emitted beside the binary sizes and validates the buffers."""
+    rows_per_block, cols, blocks = 4, 512, 9
+    out, so = _module(pkg, tmp_path, F.softmax("softmax_desc", rows_per_block, cols), "desc")
+    (k,) = out.meta.kernels
+    launcher = dev.create_launcher()
+    launcher.load(so, pkg.hal.KernelMode[k.mode])
+    s = dev.create_stream()
+    x = util.softmax_input(pkg.capi, blocks * rows_per_block, cols)
+    xb = dev.alloc_from_slice(x, s)
+    yb = dev.alloc(k.args[1].elements_per_block * blocks, np.float32)
+    launcher.launch_described(k, pkg.hal.LaunchGrid.blocks_(blocks), [xb, yb], s)
+    m = oracle.compare(yb.copy_to_host(s).reshape(x.shape), oracle.softmax_f32(x), floor_r=1e-30)
+    assert m["rel_max"] <= util.F32_REL, m
+    with pytest.raises(pkg.hal.KernelError, match="blocks need"):
+        launcher.launch_described(k, pkg.hal.LaunchGrid.blocks_(blocks + 1), [xb, yb], s)  # buffers too small for ten tiles
+    with pytest.raises(pkg.hal.KernelError, match="takes 2 buffers"):
+        launcher.launch_described(k, pkg.hal.LaunchGrid.blocks_(blocks), [xb], s)

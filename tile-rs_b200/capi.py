@@ -92,6 +92,7 @@ PROTOTYPES = {
     "tsm100_attention_host": (c_i32, [c_vp, P(AttentionDesc), c_vp, c_vp, c_vp, c_vp]),
     "tsm100_shard_range": (c_i32, [c_i64, c_i32, c_i32, P(c_i64), P(c_i64)]),
     "tsm100_emit": (c_i32, [C.c_char_p, c_sz, C.c_char_p, c_sz, P(c_sz), C.c_char_p, c_sz, P(c_sz)]),
+    "tsm100_emit_descriptors": (c_i32, [C.c_char_p, c_sz, C.c_char_p, c_sz, P(c_sz)]),
     "tsm100_target_name": (C.c_char_p, []),
     "tsm100_target_ext": (C.c_char_p, []),
     "tsm100_fill_uniform_f32": (c_i32, [c_vp, c_i64, c_u64, c_i64]),

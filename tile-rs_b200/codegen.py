@@ -5,6 +5,8 @@
   crates/tile_codegen/src/target.rs:17-65
 * ``TargetRegistry``   crates/tile_codegen/src/registry.rs:21-68
 * ``DebugTarget`` / ``EmitterTarget``  crates/tile_codegen/src/targets.rs:32-102
+* ``TileKernel`` / ``TileOp`` (the descriptor "the compiler emits alongside the compiled
+  binary")  crates/tile_hal/src/kernel.rs:93-212
 
 ``CudaSm100Target.emit`` forwards to the C ABI's ``tsm100_emit`` (C++), so the
 Rust implementation of the trait is the same few lines of forwarding.
@@ -12,8 +14,9 @@ Rust implementation of the trait is the same few lines of forwarding.
 from __future__ import annotations
 
 import ctypes as C
+import json
 from dataclasses import dataclass, field
-from typing import Callable, List, Optional
+from typing import Callable, Dict, List, Optional
 
 from . import capi
 
@@ -28,10 +31,47 @@ class EmitOpts:
     hw: HardwareParams = HardwareParams()
 
 
+@dataclass(frozen=True)
+class TileOp:
+    """One ``TileOp`` of tile_hal (kernel.rs:93-158): the variant name and its fields."""
+    op: str
+    params: Dict[str, object] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class ArgInfo:
+    """What a launcher needs to validate one pointer argument of a kernel."""
+    index: int
+    role: str                # "input" | "output" | "unused"
+    dtype: str               # "F32" | "F16" | "BF16"
+    elements_per_block: int
+
+    def bytes_for(self, blocks: int) -> int:
+        return blocks * self.elements_per_block * (4 if self.dtype == "F32" else 2)
+
+
+@dataclass
+class TileKernel:
+    """``TileKernel`` of tile_hal (kernel.rs:160-212): the descriptor the compiler emits beside the binary."""
+    name: str
+    ops: List[TileOp]
+    num_inputs: int
+    num_outputs: int
+    mode: str                # "Vector" | "Matrix" | "General"
+    args: List[ArgInfo] = field(default_factory=list)
+
+    def uses_matmul(self) -> bool:
+        return any(o.op == "Matmul" for o in self.ops)
+
+    def inferred_mode(self) -> str:
+        return "General" if self.uses_matmul() else "Vector"
+
+
 @dataclass
 class TargetMeta:
     has_cube_kernel: bool = False
     kernel_names: List[str] = field(default_factory=list)
+    kernels: List[TileKernel] = field(default_factory=list)   # one descriptor per entry kernel (cuda_sm100 only)
 
 
 @dataclass
@@ -103,7 +143,30 @@ class CudaSm100Target(CodegenTarget):
                 raise EmitError(capi.last_error())
             break
         kernel_names = [n for n in names.value.decode().split("\n") if n]
-        return EmitOut(src.value.decode(), lib.tsm100_target_ext().decode(), TargetMeta(False, kernel_names))
+        return EmitOut(src.value.decode(), lib.tsm100_target_ext().decode(),
+                       TargetMeta(False, kernel_names, self.describe(mlir_text)))
+
+    def describe(self, mlir_text: str) -> List[TileKernel]:
+        """The TileKernel descriptors of the module's entry kernels."""
+        lib = capi.lib()
+        raw = mlir_text.encode()
+        n = C.c_size_t()
+        cap = max(4096, 4 * len(raw))
+        while True:
+            buf = C.create_string_buffer(cap)
+            st = lib.tsm100_emit_descriptors(raw, len(raw), buf, cap, C.byref(n))
+            if st == capi.ERR_BUFFER:
+                cap = n.value + 1
+                continue
+            if st != capi.OK:
+                raise EmitError(capi.last_error())
+            break
+        out = []
+        for k in json.loads(buf.value.decode()):
+            ops = [TileOp(o["op"], {f: v for f, v in o.items() if f != "op"}) for o in k["ops"]]
+            args = [ArgInfo(a["index"], a["role"], a["dtype"], a["elements_per_block"]) for a in k["args"]]
+            out.append(TileKernel(k["name"], ops, k["num_inputs"], k["num_outputs"], k["mode"], args))
+        return out
 
 
 class TargetRegistry:

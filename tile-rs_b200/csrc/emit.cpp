@@ -20,6 +20,7 @@
 //
 // Pure and deterministic: reads the text, touches no file, no environment.
 // Anything outside the target's scope is an error, never a TODO comment.
+#include <cctype>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -276,6 +277,7 @@ struct Kernel {
   std::string summary;   // comment line
   std::string body;      // statements of the launcher
   std::string instantiation;  // explicit instantiation(s) of the __global__ kernel(s)
+  std::string descriptor;     // the TileKernel descriptor of the kernel, one JSON object
 };
 
 struct FuncCtx {
@@ -378,6 +380,104 @@ std::string row_op_instantiation(Dt d, const char* op, long cols) {
                     : nvec <= 512 ? "4, 128, 128" : nvec <= 1024 ? "8, 128, 128" : "8, 256, 256";
   return "template __global__ void tsm100::rowops::row_op_kernel<" + t + ", tsm100::rowops::" + op + ", " + shape + ">(const " + t + "*, " +
          t + "*, int64_t, int32_t, float);\n";
+}
+
+// The TileKernel descriptor of one kernel (crates/tile_hal/src/kernel.rs:93-212: name, the ordered
+// TileOp sequence, input / output buffer counts, preferred mode), as one JSON object, plus
+// what a launcher needs to validate buffers: per pointer argument its role, storage type and
+// element count per block.
+std::string describe(const Func& f, const FuncCtx& cx, int store_arg, Dt store_dt, long store_rows, long store_cols) {
+  auto dt_tag = [](Dt d) { return d == Dt::F32 ? "F32" : d == Dt::F16 ? "F16" : "BF16"; };
+  auto camel = [](const std::string& n) {  // "reduce_max" -> "ReduceMax"
+    std::string o;
+    bool up = true;
+    for (char ch : n) {
+      if (ch == '_') { up = true; continue; }
+      o += up ? static_cast<char>(toupper(static_cast<unsigned char>(ch))) : ch;
+      up = false;
+    }
+    return o;
+  };
+  std::ostringstream ops;
+  bool first = true, uses_matmul = false;
+  struct ArgInfo { bool seen = false; bool output = false; Dt dt = Dt::F32; long elems = 0; };
+  std::vector<ArgInfo> args(static_cast<size_t>(cx.nptr()));
+  auto op = [&](const std::string& body) {
+    ops << (first ? "" : ", ") << "{" << body << "}";
+    first = false;
+  };
+  auto rc = [](long r, long c) { return "\"rows\": " + std::to_string(r) + ", \"cols\": " + std::to_string(c); };
+  for (const std::string& line : f.body) {
+    Call c;
+    if (!parse_call(line, &c)) continue;
+    const std::string& fn = c.callee;
+    Dt dt = Dt::F32;
+    const bool has_dt = suffix_dtype(fn, &dt);
+    auto it = cx.tiles.find(c.result);
+    const Tile* t = it == cx.tiles.end() ? nullptr : &it->second;
+    if (starts_with(fn, "__tile_load_") && t) {
+      op("\"op\": \"Load\", " + rc(t->rows, t->cols) + ", \"dtype\": \"" + dt_tag(t->dtype) + "\"");
+      ArgInfo& a = args[static_cast<size_t>(t->arg)];
+      a.seen = true;
+      a.dt = t->dtype;
+      a.elems = std::max(a.elems, t->rows * t->cols);
+    } else if (starts_with(fn, "__tile_store_") && has_dt) {
+      op("\"op\": \"Store\", " + rc(store_rows, store_cols) + ", \"dtype\": \"" + dt_tag(store_dt) + "\"");
+    } else if (starts_with(fn, "__tile_cast_")) {
+      const std::string n = fn.substr(std::strlen("__tile_cast_"));  // "f32_f16"
+      const size_t u = n.find('_');
+      std::string from = n.substr(0, u), to = u == std::string::npos ? "" : n.substr(u + 1);
+      for (char& ch : from) ch = static_cast<char>(toupper(static_cast<unsigned char>(ch)));
+      for (char& ch : to) ch = static_cast<char>(toupper(static_cast<unsigned char>(ch)));
+      if (t) op("\"op\": \"Cast" + from + "To" + to + "\", " + rc(t->rows, t->cols));
+    } else if (t && t->kind == Kind::Softmax) {
+      op("\"op\": \"Softmax\", " + rc(t->rows, t->cols));
+    } else if (t && (t->kind == Kind::Matmul || t->kind == Kind::MatmulT)) {
+      uses_matmul = true;
+      op("\"op\": \"Matmul\", \"m\": " + std::to_string(t->m) + ", \"k\": " + std::to_string(t->k) + ", \"n\": " + std::to_string(t->n) +
+         (t->kind == Kind::MatmulT ? ", \"b_transposed\": true" : ""));
+    } else if (t && t->kind == Kind::Transpose) {
+      op("\"op\": \"Transpose\", " + rc(t->cols, t->rows));  // the operand's shape, as the intrinsic states it
+    } else if (t && t->kind == Kind::Scale) {
+      op("\"op\": \"Scale\", " + rc(t->rows, t->cols) + ", \"scalar\": " + float_literal(t->scalar).substr(0, float_literal(t->scalar).size() - 1));
+    } else if (t && t->kind == Kind::CausalMask) {
+      op("\"op\": \"CausalMask\", " + rc(t->rows, t->cols));
+    } else if (t && (t->kind == Kind::Attention || t->kind == Kind::AttentionGqa)) {
+      uses_matmul = true;
+      op("\"op\": \"Attention\", \"b\": " + std::to_string(t->heads) + ", \"s\": " + std::to_string(t->seq) + ", \"d\": " + std::to_string(t->dim) +
+         (t->kind == Kind::AttentionGqa ? ", \"kv_heads\": " + std::to_string(t->kv_heads) + ", \"causal\": true" : ""));
+    } else if (t && t->kind == Kind::RmsNorm) {
+      op("\"op\": \"RmsNorm\", " + rc(t->rows, t->cols) + ", \"eps\": " + float_literal(t->scalar).substr(0, float_literal(t->scalar).size() - 1));
+    } else if (t && (t->kind == Kind::ReduceSum || t->kind == Kind::ReduceMax)) {
+      op(std::string("\"op\": \"") + (t->kind == Kind::ReduceSum ? "ReduceSum" : "ReduceMax") + "\", " + rc(t->rows, t->cols));
+    } else if (t && t->kind == Kind::Ewise) {
+      auto num = [](double v) { const std::string l = float_literal(v); return l.substr(0, l.size() - 1); };
+      std::string extra;
+      if (t->ew == "fill") extra = ", \"scalar\": " + num(t->scalar);
+      if (t->ew == "clamp") extra = ", \"lo\": " + num(t->scalar) + ", \"hi\": " + num(t->scalar2);
+      op("\"op\": \"" + camel(t->ew) + "\", " + rc(t->rows, t->cols) + extra);
+    }
+  }
+  if (store_arg >= 0) {
+    ArgInfo& a = args[static_cast<size_t>(store_arg)];
+    a.seen = true;
+    a.output = true;
+    a.dt = store_dt;
+    a.elems = std::max(a.elems, store_rows * store_cols);
+  }
+  int n_in = 0, n_out = 0;
+  std::ostringstream aj;
+  for (size_t i = 0; i < args.size(); ++i) {
+    n_in += args[i].seen && !args[i].output;
+    n_out += args[i].output;
+    aj << (i ? ", " : "") << "{\"index\": " << i << ", \"role\": \"" << (args[i].output ? "output" : args[i].seen ? "input" : "unused")
+       << "\", \"dtype\": \"" << dt_tag(args[i].dt) << "\", \"elements_per_block\": " << args[i].elems << "}";
+  }
+  std::ostringstream o;
+  // TileKernel::inferred_mode (kernel.rs:204-211): General when a matrix product is involved
+  o << "{\"name\": \"" << f.name << "\", \"mode\": \"" << (uses_matmul ? "General" : "Vector") << "\", \"num_inputs\": " << n_in
+    << ", \"num_outputs\": " << n_out << ", \"ops\": [" << ops.str() << "], \"args\": [" << aj.str() << "]}";
+  return o.str();
 }
 
 Kernel lower(const Func& f) {
@@ -929,12 +1029,13 @@ Kernel lower(const Func& f) {
     reject("kernel " + f.name + ": the stored tile is not produced by an operator of the cuda_sm100 target");
   }
   k.summary = sum.str();
+  k.descriptor = describe(f, cx, store_arg, store_dt, store_rows, store_cols);
   k.body = body.str();
   k.instantiation = inst.str();
   return k;
 }
 
-std::string emit_source(const std::string& mlir, std::vector<std::string>* names) {
+std::string emit_source(const std::string& mlir, std::vector<std::string>* names, std::string* descriptors = nullptr) {
   if (trim(mlir).empty()) reject("empty MLIR module");
   const std::vector<Func> funcs = parse_module(mlir);
   std::vector<Kernel> kernels;
@@ -965,6 +1066,11 @@ std::string emit_source(const std::string& mlir, std::vector<std::string>* names
     while (std::getline(bl, l)) o << "  " << l << "\n";
     o << "  }\n  if (st != TSM100_OK && err != nullptr && err_cap > 0) snprintf(err, err_cap, \"%s\", msg.c_str());\n  return st;\n}\n\n";
     names->push_back(k.name);
+  }
+  if (descriptors) {
+    *descriptors = "[";
+    for (size_t i = 0; i < kernels.size(); ++i) *descriptors += (i ? ",\n " : "") + kernels[i].descriptor;
+    *descriptors += "]";
   }
   return o.str();
 }
@@ -998,6 +1104,29 @@ int32_t tsm100_emit(const char* mlir, size_t mlir_len, char* source, size_t sour
     const int32_t a = copy_out(src, source, source_cap, source_len);
     const int32_t b = copy_out(joined, names, names_cap, names_len);
     if (a != TSM100_OK || b != TSM100_OK) {
+      tsm100::last_error_ref() = "output buffer too small";
+      return TSM100_ERR_BUFFER;
+    }
+    return TSM100_OK;
+  } catch (const EmitFailure& e) {
+    tsm100::last_error_ref() = e.msg;
+    return TSM100_ERR_EMIT;
+  } catch (const std::exception& e) {
+    tsm100::last_error_ref() = std::string("emit failed: ") + e.what();
+    return TSM100_ERR_EMIT;
+  }
+}
+
+int32_t tsm100_emit_descriptors(const char* mlir, size_t mlir_len, char* json, size_t json_cap, size_t* json_len) {
+  if (!mlir && mlir_len) {
+    tsm100::last_error_ref() = "null MLIR text";
+    return TSM100_ERR_INVALID;
+  }
+  try {
+    std::vector<std::string> kernel_names;
+    std::string desc;
+    emit_source(std::string(mlir ? mlir : "", mlir_len), &kernel_names, &desc);
+    if (copy_out(desc, json, json_cap, json_len) != TSM100_OK) {
       tsm100::last_error_ref() = "output buffer too small";
       return TSM100_ERR_BUFFER;
     }

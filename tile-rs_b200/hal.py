@@ -294,6 +294,22 @@ class KernelLauncher:
                 break
         check(last)
 
+    def launch_described(self, kernel, grid: LaunchGrid, buffers: Sequence["DeviceBuffer"], stream: Optional[Stream]) -> None:
+        """Launch with the kernel's TileKernel descriptor (codegen.TileKernel): the three uses
+        kernel.rs:163-168 names - the argument count, and every buffer's size against
+        ``grid.blocks`` per-block tiles, are checked before anything reaches the device."""
+        if len(buffers) != len(kernel.args):
+            raise KernelError(f"{kernel.name} takes {len(kernel.args)} buffers ({kernel.num_inputs} in, "
+                              f"{kernel.num_outputs} out), got {len(buffers)}")
+        for a, b in zip(kernel.args, buffers):
+            need = a.bytes_for(grid.blocks)
+            have = b.len() * b.dtype.itemsize
+            if have < need:
+                raise KernelError(f"{kernel.name}: buffer {a.index} ({a.role}, {a.dtype}) holds {have} bytes, "
+                                  f"{grid.blocks} blocks need {need}")
+        ptrs = [b.as_raw_mut_ptr() if a.role == "output" else b.as_raw_ptr() for a, b in zip(kernel.args, buffers)]
+        self.launch(kernel.name, grid, ptrs, stream)
+
     def __del__(self):
         try:
             for m in self._modules:
