@@ -277,6 +277,32 @@ class AttentionWL(Workload):
                 "kv_groups_per_gpu": self.units}
 
 
+class DecodeWL(Workload):
+    """One decode step: `units` (batch, KV head) caches of 16384 x 128 bf16, 8 query heads each."""
+    unit_name = "kv_caches"
+    bound = "hbm"
+    dtype = "bf16"
+
+    def __init__(self, ctx, units, seq=16384, group=8, name="attention_decode_bf16"):
+        super().__init__(ctx, units)
+        torch = _torch()
+        self.seq, self.group, self.name = seq, group, name
+        g = torch.Generator(device=ctx.tdev).manual_seed(801)
+        self.q = torch.randn(units, group, 128, device=ctx.tdev, generator=g).to(torch.bfloat16)
+        self.k = torch.randn(units, 1, seq, 128, device=ctx.tdev, generator=g).to(torch.bfloat16)
+        self.v = torch.randn(units, 1, seq, 128, device=ctx.tdev, generator=g).to(torch.bfloat16)
+        self.o = torch.empty_like(self.q)
+        self.work_per_unit = 2.0 * seq * 128 * 2 + 2.0 * group * 128 * 2  # K and V once, q in, o out
+
+    def step(self):
+        self.ctx.dev.attention_decode(self.ctx.pkg.capi.BF16, self.units, self.group, 1, self.seq, self.seq, 128,
+                                      self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.o.data_ptr(),
+                                      stream=self.ctx.stream)
+
+    def describe(self):
+        return {"q_heads_per_kv_head": self.group, "seq_len": self.seq, "head_dim": 128, "kv_caches_per_gpu": self.units}
+
+
 # name -> (units at one GPU, factory(ctx, units, first_unit))
 def catalogue():
     return {
@@ -292,6 +318,7 @@ def catalogue():
         "reduce_sum_f32": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "reduce_sum")),
         "silu_mul_f32": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "silu_mul")),
         "silu_mul_bf16": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "silu_mul", "bf16")),
+        "attention_decode_bf16": (256, lambda c, u, f: DecodeWL(c, u)),
     }
 
 

@@ -243,6 +243,25 @@ int32_t tsm100_attention(tsm100_device_t dev, const tsm100_attention_desc* desc,
                          const void* k, const void* v, void* o, void* stream);
 
 /* ---- operators on HOST memory (upload, compute, download in one call) ---- */
+/* Single-token (decode) attention against a KV cache:
+ *   o[b,h,:] = softmax_p(q[b,h,:] . K[b,g,p,:] / sqrt(d)) V[b,g,p,:],  p < seq_len,  g = h / (heads_q / heads_kv).
+ * __tile_attention_decode_f32 (tile.rs:2120-2124; wrapper :3004-3018): q, o [heads_q][d], caches
+ * [heads_kv][max_seq][d]; opaque in the linalg bridge (mlir_to_linalg.rs:502-505), arithmetic as the
+ * five phases of the Metal lowering (crates/rustc_codegen_tile/src/mlir_to_msl.rs:10747-10812), whose
+ * run-time constants seq_len, max_seq and the head counts are the fields below.  `batch` repeats the
+ * problem: q, o [batch][heads_q][d], caches [batch][heads_kv][max_seq][d].  head_dim 64 or 128. */
+typedef struct {
+  int32_t dtype;    /* storage type of q, the caches and o; math is f32 */
+  int32_t batch;
+  int32_t heads_q;
+  int32_t heads_kv;
+  int32_t seq_len;  /* positions of the cache that are filled */
+  int32_t max_seq;  /* row pitch of the cache, in positions */
+  int32_t head_dim;
+} tsm100_attention_decode_desc;
+int32_t tsm100_attention_decode(tsm100_device_t dev, const tsm100_attention_decode_desc* desc, const void* q,
+                                const void* k_cache, const void* v_cache, void* o, void* stream);
+
 /* The path a tile_hal host program takes per kernel: alloc_from_slice ->
  * launch -> copy_to_host (crates/tile_hal/src/cuda.rs:348-371, :245-288,
  * :190-199), here chunked through page-locked staging so that copies in both

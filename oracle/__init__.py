@@ -49,13 +49,15 @@ def lib() -> C.CDLL:
         h.orc_reduce_f32.argtypes = [_vp, _vp, _i64, _i64, C.c_int, C.c_int]
         h.orc_silu_mul_f32.argtypes = [_vp, _vp, _vp, _i64, C.c_int]
         h.orc_silu_mul_bf16.argtypes = [_vp, _vp, _vp, _vp, _i64]
+        h.orc_attention_decode_f32.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]
+        h.orc_attention_decode_bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64]
         h.orc_compare_f32.argtypes = [_vp, _vp, _i64, C.c_double, _vp]
         h.orc_bf16_to_f32.argtypes = [_vp, _vp, _i64]
         h.orc_f32_to_bf16.argtypes = [_vp, _vp, _i64]
         for name in ("orc_gemm_f32", "orc_gemm_f64acc", "orc_gemm_bf16", "orc_softmax_f32", "orc_softmax_f64acc",
                      "orc_softmax_bf16", "orc_attention_f32", "orc_attention_bf16", "orc_compare_f32",
                      "orc_bf16_to_f32", "orc_f32_to_bf16", "orc_rms_norm_f32", "orc_rms_norm_bf16", "orc_reduce_f32",
-                     "orc_silu_mul_f32", "orc_silu_mul_bf16"):
+                     "orc_silu_mul_f32", "orc_silu_mul_bf16", "orc_attention_decode_f32", "orc_attention_decode_bf16"):
             getattr(h, name).restype = None
         _LIB = h
     return _LIB
@@ -164,6 +166,31 @@ def silu_mul_bf16(gate: np.ndarray, up):
     y16 = np.empty(gate.shape, np.uint16)
     lib().orc_silu_mul_bf16(_p(gate), None if upc is None else _p(upc), _p(y32), _p(y16), gate.size)
     return y32, y16
+
+
+def attention_decode_f32(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, seq_len: int, f64_acc: bool = False) -> np.ndarray:
+    """q: [batch, hq, d]; caches: [batch, hkv, max_seq, d]; positions < seq_len take part."""
+    q = np.ascontiguousarray(q, np.float32)
+    k_cache = np.ascontiguousarray(k_cache, np.float32)
+    v_cache = np.ascontiguousarray(v_cache, np.float32)
+    b, hq, d = q.shape
+    _, hkv, max_seq, _ = k_cache.shape
+    o = np.empty_like(q)
+    lib().orc_attention_decode_f32(_p(q), _p(k_cache), _p(v_cache), _p(o), b, hq, hkv, seq_len, max_seq, d, int(f64_acc))
+    return o
+
+
+def attention_decode_bf16(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, seq_len: int):
+    """bf16 bit patterns in; returns (unrounded f32 result, RNE bf16 bit patterns)."""
+    q = np.ascontiguousarray(q, np.uint16)
+    k_cache = np.ascontiguousarray(k_cache, np.uint16)
+    v_cache = np.ascontiguousarray(v_cache, np.uint16)
+    b, hq, d = q.shape
+    _, hkv, max_seq, _ = k_cache.shape
+    o32 = np.empty(q.shape, np.float32)
+    o16 = np.empty(q.shape, np.uint16)
+    lib().orc_attention_decode_bf16(_p(q), _p(k_cache), _p(v_cache), _p(o32), _p(o16), b, hq, hkv, seq_len, max_seq, d)
+    return o32, o16
 
 
 def attention_f32(q: np.ndarray, k: np.ndarray, v: np.ndarray, causal: bool) -> np.ndarray:

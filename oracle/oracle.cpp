@@ -448,4 +448,84 @@ void orc_compare_f32(const float* y, const float* r, int64_t n, double floor_r, 
   out[4] = mrel;
 }
 
+// __tile_attention_decode_f32 with a leading batch: q, o [batch][hq][d], caches
+// [batch][hkv][max_seq][d], positions p < seq_len, kv head = h / (hq / hkv).  The five phases
+// of crates/rustc_codegen_tile/src/mlir_to_msl.rs:10747-10812: score = (q . K_p) * rsqrt(d),
+// max, e = exp(score - max) and its sum, normalise, weighted V sum over positions in order.
+// f64acc != 0 keeps every intermediate in double (the truth for the error bound).
+void orc_attention_decode_f32(const float* q, const float* kc, const float* vc, float* o, int64_t batch, int64_t hq,
+                              int64_t hkv, int64_t seq_len, int64_t max_seq, int64_t d, int f64acc) {
+  const int64_t group = hq / hkv;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t b = 0; b < batch; ++b)
+    for (int64_t h = 0; h < hq; ++h) {
+      const float* qh = q + (b * hq + h) * d;
+      const float* kh = kc + (b * hkv + h / group) * max_seq * d;
+      const float* vh = vc + (b * hkv + h / group) * max_seq * d;
+      float* oh = o + (b * hq + h) * d;
+      if (f64acc) {
+        std::vector<double> sc(seq_len);
+        const double scale = 1.0 / std::sqrt(static_cast<double>(d));
+        double mx = -std::numeric_limits<double>::infinity();
+        for (int64_t p = 0; p < seq_len; ++p) {
+          double dot = 0;
+          for (int64_t j = 0; j < d; ++j) dot += static_cast<double>(qh[j]) * kh[p * d + j];
+          sc[p] = dot * scale;
+          mx = sc[p] > mx ? sc[p] : mx;
+        }
+        double sum = 0;
+        for (int64_t p = 0; p < seq_len; ++p) {
+          sc[p] = std::exp(sc[p] - mx);
+          sum += sc[p];
+        }
+        for (int64_t j = 0; j < d; ++j) {
+          double acc = 0;
+          for (int64_t p = 0; p < seq_len; ++p) acc += sc[p] / sum * vh[p * d + j];
+          oh[j] = static_cast<float>(acc);
+        }
+      } else {
+        std::vector<float> sc(seq_len);
+        const float scale = 1.0f / std::sqrt(static_cast<float>(d));
+        float mx = -std::numeric_limits<float>::infinity();
+        for (int64_t p = 0; p < seq_len; ++p) {
+          float dot = 0.f;
+          for (int64_t j = 0; j < d; ++j) dot += qh[j] * kh[p * d + j];
+          sc[p] = dot * scale;
+          mx = sc[p] > mx ? sc[p] : mx;
+        }
+        float sum = 0.f;
+        for (int64_t p = 0; p < seq_len; ++p) {
+          sc[p] = expf(sc[p] - mx);
+          sum += sc[p];
+        }
+        const float inv = 1.0f / sum;
+        for (int64_t p = 0; p < seq_len; ++p) sc[p] *= inv;
+        for (int64_t j = 0; j < d; ++j) {
+          float acc = 0.f;
+          for (int64_t p = 0; p < seq_len; ++p) acc += sc[p] * vh[p * d + j];
+          oh[j] = acc;
+        }
+      }
+    }
+}
+
+// bf16 storage: widen q and the caches exactly, f32 arithmetic as above, unrounded f32 result
+// to o_f32 (may be NULL) and RNE bf16 to o_bf16 (may be NULL).
+void orc_attention_decode_bf16(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, float* o_f32, uint16_t* o_bf16,
+                               int64_t batch, int64_t hq, int64_t hkv, int64_t seq_len, int64_t max_seq, int64_t d) {
+  const int64_t nq = batch * hq * d, nkv = batch * hkv * max_seq * d;
+  std::vector<float> qf(nq), kf(nkv), vf(nkv), of(nq);
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < nq; ++i) qf[i] = bf16_to_f32(q[i]);
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < nkv; ++i) {
+    kf[i] = bf16_to_f32(kc[i]);
+    vf[i] = bf16_to_f32(vc[i]);
+  }
+  orc_attention_decode_f32(qf.data(), kf.data(), vf.data(), of.data(), batch, hq, hkv, seq_len, max_seq, d, 0);
+  if (o_f32) std::memcpy(o_f32, of.data(), sizeof(float) * nq);
+  if (o_bf16)
+    for (int64_t i = 0; i < nq; ++i) o_bf16[i] = f32_to_bf16(of[i]);
+}
+
 }  // extern "C"

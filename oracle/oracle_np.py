@@ -67,6 +67,18 @@ EWISE = {
 }
 
 
+def attention_decode(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, seq_len: int) -> np.ndarray:
+    """One query token per head against the first seq_len cache positions (mlir_to_msl.rs:10747-10812), in float64.
+    q: [batch, hq, d]; caches: [batch, hkv, max_seq, d]."""
+    q, k, v = q.astype(np.float64), k_cache.astype(np.float64)[:, :, :seq_len], v_cache.astype(np.float64)[:, :, :seq_len]
+    b, hq, d = q.shape
+    group = hq // k.shape[1]
+    k, v = np.repeat(k, group, axis=1), np.repeat(v, group, axis=1)
+    s = np.einsum("bhd,bhpd->bhp", q, k) / np.sqrt(d)
+    s = np.exp(s - s.max(axis=2, keepdims=True))
+    return np.einsum("bhp,bhpd->bhd", s / s.sum(axis=2, keepdims=True), v)
+
+
 def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, causal: bool) -> np.ndarray:
     """transpose, matmul, scale 1/sqrt(D), [causal mask col > row -> -inf], softmax, matmul
     (mlir_to_linalg.rs:1781-1902, :1191-1244); grouped KV heads with

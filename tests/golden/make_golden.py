@@ -49,6 +49,10 @@ def main() -> None:
     gate, up = util.gen_normal(capi, (6, 96), 602, 4.0), util.gen_normal(capi, (6, 96), 603)
     np.savez(out / "rowops.npz", x=xr, eps=np.float32(1e-5), rms=onp.rms_norm(xr, 1e-5), row_sum=onp.reduce(xr, "sum"),
              row_max=onp.reduce(xr, "max"), gate=gate, up=up, silu=onp.silu_mul(gate), silu_mul=onp.silu_mul(gate, up))
+    # decode attention: one query token per head against a partly filled, grouped KV cache
+    qd = util.gen_normal(capi, (2, 4, 16), 801)
+    kd, vd = util.gen_normal(capi, (2, 2, 24, 16), 802), util.gen_normal(capi, (2, 2, 24, 16), 803)
+    np.savez(out / "attention_decode.npz", q=qd, k_cache=kd, v_cache=vd, seq_len=np.int64(19), o=onp.attention_decode(qd, kd, vd, 19))
     print("wrote", sorted(p.name for p in out.glob("*.npz")))
 
 

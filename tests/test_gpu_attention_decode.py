@@ -1,0 +1,97 @@
+"""Single-token attention against a KV cache on the GPU through the C ABI against the CPU oracle."""
+import numpy as np
+import pytest
+
+import util
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def run_decode(dev, capi, q, k, v, seq_len, dtype):
+    b, hq, d = q.shape
+    _, hkv, max_seq, _ = k.shape
+    qd, kd, vd = (util.dev_tensor(torch, t) for t in (q, k, v))
+    od = torch.full_like(qd, 12345 if qd.dtype == torch.int16 else float("nan"))
+    dev.attention_decode(dtype, b, hq, hkv, seq_len, max_seq, d, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), od.data_ptr(),
+                         stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    assert dev.status() == 0
+    return od.cpu().numpy()
+
+
+# (batch, heads_q, heads_kv, seq_len, max_seq, head_dim): group sizes 1, 2, 3 (padded to 4), 8 and 12 (two passes);
+# ranges that end inside a warp's slots; one position; long caches that are split over a cluster
+CASES = [(1, 1, 1, 1, 8, 64), (2, 4, 4, 33, 40, 128), (1, 8, 4, 100, 128, 64), (2, 6, 2, 257, 300, 128), (1, 16, 2, 1000, 1024, 128),
+         (1, 24, 2, 515, 600, 64), (3, 8, 1, 4096, 4096, 128), (1, 2, 2, 20000, 20480, 128), (1, 8, 1, 16384, 16384, 64)]
+
+
+@pytest.mark.parametrize("b,hq,hkv,n,max_seq,d", CASES)
+def test_decode_f32_matches_oracle(dev, pkg, oracle, b, hq, hkv, n, max_seq, d):
+    capi = pkg.capi
+    q = util.gen_normal(capi, (b, hq, d), 801)
+    k = util.gen_normal(capi, (b, hkv, max_seq, d), 802)
+    v = util.gen_normal(capi, (b, hkv, max_seq, d), 803)
+    k[:, :, n:], v[:, :, n:] = np.nan, np.nan  # positions beyond seq_len must not be read
+    o = run_decode(dev, capi, q, k, v, n, capi.F32)
+    kz, vz = np.nan_to_num(k), np.nan_to_num(v)
+    for ref in (oracle.attention_decode_f32(q, kz, vz, n), oracle.attention_decode_f32(q, kz, vz, n, f64_acc=True)):
+        m = oracle.compare(o, ref)
+        assert m["rel_max"] <= util.F32_REL and m["rel_fro"] <= util.F32_REL, m
+
+
+@pytest.mark.parametrize("b,hq,hkv,n,max_seq,d", [(1, 1, 1, 5, 8, 64), (2, 8, 2, 300, 320, 128), (1, 32, 4, 2048, 2048, 128),
+                                                     (2, 5, 1, 777, 800, 64), (1, 8, 8, 9000, 9000, 128)])
+def test_decode_bf16_matches_oracle(dev, pkg, oracle, b, hq, hkv, n, max_seq, d):
+    capi = pkg.capi
+    q = util.to_bf16(capi, util.gen_normal(capi, (b, hq, d), 801))
+    k = util.to_bf16(capi, util.gen_normal(capi, (b, hkv, max_seq, d), 802))
+    v = util.to_bf16(capi, util.gen_normal(capi, (b, hkv, max_seq, d), 803))
+    o = run_decode(dev, capi, q, k, v, n, capi.BF16).view(np.uint16)
+    ref32, _ = oracle.attention_decode_bf16(q, k, v, n)
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(o), ref32)
+
+
+def test_decode_f16_and_large_scores(dev, pkg, oracle):
+    capi = pkg.capi
+    q = util.f32_to_f16_bits(8.0 * util.gen_normal(capi, (1, 4, 128), 811))   # scores of a few hundred: max subtraction matters
+    k = util.f32_to_f16_bits(util.gen_normal(capi, (1, 2, 600, 128), 812))
+    v = util.f32_to_f16_bits(util.gen_normal(capi, (1, 2, 600, 128), 813))
+    o = run_decode(dev, capi, q, k, v, 600, capi.F16).view(np.float16).astype(np.float32)
+    f = lambda t: t.view(np.float16).astype(np.float32)
+    ref = oracle.attention_decode_f32(f(q), f(k), f(v), 600, f64_acc=True)
+    assert np.abs(o - ref).max() <= 2.0 ** -10 * max(1.0, float(np.abs(ref).max())) + 1e-3
+
+
+def test_decode_equals_last_row_of_causal_attention(dev, pkg, oracle):
+    """Size-independent property at a full-size cache: decoding the last token of a sequence reproduces the
+    last row of the fused causal attention over the same keys and values."""
+    capi = pkg.capi
+    b, hq, hkv, s, d = 1, 8, 2, 4096, 128
+    q = util.to_bf16(capi, util.gen_normal(capi, (b, hq, s, d), 821))
+    k = util.to_bf16(capi, util.gen_normal(capi, (b, hkv, s, d), 822))
+    v = util.to_bf16(capi, util.gen_normal(capi, (b, hkv, s, d), 823))
+    qd, kd, vd = (util.dev_tensor(torch, t) for t in (q, k, v))
+    full = torch.empty_like(qd)
+    dev.attention(capi.BF16, b, hq, hkv, s, d, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), full.data_ptr(), causal=True,
+                  stream=util.cur_stream(torch))
+    last_q = qd[:, :, -1].contiguous()
+    dec = torch.empty_like(last_q)
+    dev.attention_decode(capi.BF16, b, hq, hkv, s, s, d, last_q.data_ptr(), kd.data_ptr(), vd.data_ptr(), dec.data_ptr(),
+                         stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    a = oracle.bf16_to_f32(full[:, :, -1].contiguous().cpu().numpy().view(np.uint16))
+    c = oracle.bf16_to_f32(dec.cpu().numpy().view(np.uint16))
+    assert np.abs(a - c).max() <= 2.0 ** -7  # two independently rounded bf16 results of values below one
+
+
+def test_decode_rejects_bad_arguments(dev, pkg):
+    capi = pkg.capi
+    with pytest.raises(pkg.hal.HalError):
+        dev.attention_decode(capi.F32, 1, 4, 3, 8, 8, 64, 16, 16, 16, 16)      # heads_q not a multiple of heads_kv
+    with pytest.raises(pkg.hal.HalError):
+        dev.attention_decode(capi.F32, 1, 4, 4, 9, 8, 64, 16, 16, 16, 16)      # seq_len beyond the cache
+    with pytest.raises(pkg.hal.HalError):
+        dev.attention_decode(capi.F32, 1, 4, 4, 8, 8, 80, 16, 16, 16, 16)      # head_dim
+    with pytest.raises(pkg.hal.HalError):
+        dev.attention_decode(capi.F32, 1, 4, 4, 8, 8, 64, 0, 16, 16, 16)       # null q

@@ -145,3 +145,25 @@ def test_row_operators_known_answers_and_bf16(oracle):
     s32, s16 = oracle.silu_mul_bf16(gb, ub)
     assert np.abs(s32 - onp.silu_mul(onp.bf16_bits_to_f32(gb), onp.bf16_bits_to_f32(ub))).max() <= 2e-6
     assert np.array_equal(s16, onp.f32_to_bf16_bits(s32))
+
+
+def test_attention_decode_matches_golden_and_known_answers(oracle):
+    g = np.load(GOLD / "attention_decode.npz")
+    n = int(g["seq_len"])
+    assert np.abs(oracle.attention_decode_f32(g["q"], g["k_cache"], g["v_cache"], n) - g["o"]).max() <= 2e-6
+    assert np.abs(oracle.attention_decode_f32(g["q"], g["k_cache"], g["v_cache"], n, f64_acc=True) - g["o"]).max() <= 3e-7
+    # the unfilled part of the cache is never read
+    k2, v2 = g["k_cache"].copy(), g["v_cache"].copy()
+    k2[:, :, n:], v2[:, :, n:] = np.nan, np.nan
+    assert np.array_equal(oracle.attention_decode_f32(g["q"], k2, v2, n), oracle.attention_decode_f32(g["q"], g["k_cache"], g["v_cache"], n))
+    # one filled position returns its V row; identical keys average V; decode equals the last row of causal attention
+    assert np.array_equal(oracle.attention_decode_f32(g["q"], g["k_cache"], g["v_cache"], 1)[:, :2], g["v_cache"][:, :, 0][:, [0, 0]])
+    rng = np.random.default_rng(4)
+    q, k, v = (rng.standard_normal(s).astype(np.float32) for s in ((1, 3, 12, 8), (1, 3, 12, 8), (1, 3, 12, 8)))
+    full = oracle.attention_f32(q, k, v, True)
+    dec = oracle.attention_decode_f32(np.ascontiguousarray(q[:, :, -1]), k, v, 12)
+    assert np.abs(dec - full[:, :, -1]).max() <= 1e-6
+    qb, kb, vb = (oracle.f32_to_bf16(t) for t in (np.ascontiguousarray(q[:, :, -1]), k, v))
+    o32, o16 = oracle.attention_decode_bf16(qb, kb, vb, 12)
+    assert np.abs(o32 - onp.attention_decode(*(onp.bf16_bits_to_f32(t) for t in (qb, kb, vb)), 12)).max() <= 2e-6
+    assert np.array_equal(o16, onp.f32_to_bf16_bits(o32))

@@ -43,6 +43,11 @@ class SiluMulDesc(C.Structure):
 REDUCE_SUM, REDUCE_MAX = 0, 1
 
 
+class AttentionDecodeDesc(C.Structure):
+    _fields_ = [("dtype", c_i32), ("batch", c_i32), ("heads_q", c_i32), ("heads_kv", c_i32), ("seq_len", c_i32),
+                ("max_seq", c_i32), ("head_dim", c_i32)]
+
+
 class AttentionDesc(C.Structure):
     _fields_ = [("dtype", c_i32), ("causal", c_i32), ("batch", c_i32), ("heads_q", c_i32),
                 ("heads_kv", c_i32), ("seq", c_i32), ("head_dim", c_i32)]
@@ -87,6 +92,7 @@ PROTOTYPES = {
     "tsm100_gemm": (c_i32, [c_vp, P(GemmDesc), c_vp, c_vp, c_vp, c_vp]),
     "tsm100_gemm_static_scratch": (c_i32, [P(GemmDesc), c_vp, c_vp, c_vp, c_vp, P(c_u32)]),
     "tsm100_attention": (c_i32, [c_vp, P(AttentionDesc), c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "tsm100_attention_decode": (c_i32, [c_vp, P(AttentionDecodeDesc), c_vp, c_vp, c_vp, c_vp, c_vp]),
     "tsm100_softmax_host": (c_i32, [c_vp, P(SoftmaxDesc), c_vp, c_vp]),
     "tsm100_gemm_host": (c_i32, [c_vp, P(GemmDesc), c_vp, c_vp, c_vp]),
     "tsm100_attention_host": (c_i32, [c_vp, P(AttentionDesc), c_vp, c_vp, c_vp, c_vp]),

@@ -85,6 +85,14 @@ int32_t tsm100_silu_mul(tsm100_device_t dev, const tsm100_silu_mul_desc* desc, c
   return finish(ops::silu_mul(&err, desc, gate, up, y, stream), err);
 }
 
+int32_t tsm100_attention_decode(tsm100_device_t dev, const tsm100_attention_decode_desc* desc, const void* q,
+                                const void* k_cache, const void* v_cache, void* o, void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::attention_decode(&err, desc, q, k_cache, v_cache, o, stream), err);
+}
+
 int32_t tsm100_gemm(tsm100_device_t dev, const tsm100_gemm_desc* desc, const void* a, const void* b, void* c,
                     void* stream) {
   int32_t st = use_device(dev);

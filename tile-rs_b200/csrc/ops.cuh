@@ -16,6 +16,7 @@
 #include <string>
 
 #include "../../include/tile_sm100.h"
+#include "attention_decode.cuh"
 #include "attention_simt.cuh"
 #include "attention_tc.cuh"
 #include "ewise.cuh"
@@ -483,6 +484,98 @@ inline int32_t attention_simt_launch(std::string* err, const tsm100_attention_de
   attn_simt::attention_simt_kernel<T><<<static_cast<unsigned>(grid), attn_simt::kWarps * 32, 0, s>>>(
       static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(o), p);
   return cuda_ok(err, cudaGetLastError(), "attention_simt launch");
+}
+
+// ---------------------------------------------------------------------------
+// decode attention (one query token against a KV cache)
+// ---------------------------------------------------------------------------
+template <typename T, int G, int D>
+inline int32_t attention_decode_launch(std::string* err, const tsm100_attention_decode_desc* d, const T* q, const T* k,
+                                       const T* v, T* o, int head_base, int heads_here, int splits, cudaStream_t s) {
+  namespace ad = attn_decode;
+  ad::Params p;
+  p.batch = d->batch;
+  p.heads_q = d->heads_q;
+  p.heads_kv = d->heads_kv;
+  p.seq_len = d->seq_len;
+  p.max_seq = d->max_seq;
+  p.group = d->heads_q / d->heads_kv;
+  p.head_base = head_base;
+  p.heads_here = heads_here;
+  p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
+  auto kern = ad::attention_decode_kernel<T, G, D>;
+  constexpr int smem = ad::smem_floats<T, G, D>() * static_cast<int>(sizeof(float));
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_decode_kernel)");
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.blockDim = dim3(ad::kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cfg.gridDim = dim3(static_cast<unsigned>(static_cast<int64_t>(d->batch) * d->heads_kv * splits));
+  e = cudaLaunchKernelEx(&cfg, kern, q, k, v, o, p);
+  return cuda_ok(err, e, "attention_decode_kernel launch");
+}
+
+template <typename T, int D>
+inline int32_t attention_decode_typed(std::string* err, const tsm100_attention_decode_desc* d, const void* q, const void* k,
+                                      const void* v, void* o, cudaStream_t s) {
+  int sms = 0;
+  int32_t st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  const int64_t units = static_cast<int64_t>(d->batch) * d->heads_kv;
+  // split the positions of one (batch, KV head) over a cluster until the GPU is covered about twice, keeping
+  // at least 256 positions per CTA
+  int splits = 1;
+  while (splits < attn_decode::kMaxSplits && units * splits < 2ll * sms && d->seq_len / (2 * splits) >= 256) splits *= 2;
+  const int group = d->heads_q / d->heads_kv;
+  const T* qp = static_cast<const T*>(q);
+  const T* kp = static_cast<const T*>(k);
+  const T* vp = static_cast<const T*>(v);
+  T* op = static_cast<T*>(o);
+  // groups wider than 8 query heads run in passes of 8 (the cache is then re-read, from L2 when it fits)
+  for (int base = 0; base < group && st == TSM100_OK; base += 8) {
+    const int here = std::min(8, group - base);
+    if (here == 1) st = attention_decode_launch<T, 1, D>(err, d, qp, kp, vp, op, base, here, splits, s);
+    else if (here == 2) st = attention_decode_launch<T, 2, D>(err, d, qp, kp, vp, op, base, here, splits, s);
+    else if (here <= 4) st = attention_decode_launch<T, 4, D>(err, d, qp, kp, vp, op, base, here, splits, s);
+    else st = attention_decode_launch<T, 8, D>(err, d, qp, kp, vp, op, base, here, splits, s);
+  }
+  return st;
+}
+
+inline int32_t attention_decode(std::string* err, const tsm100_attention_decode_desc* d, const void* q, const void* k,
+                                const void* v, void* o, void* stream) {
+  if (!d || !q || !k || !v || !o) return op_fail(err, TSM100_ERR_INVALID, "attention_decode: null argument");
+  if (!dtype_valid(d->dtype)) return op_fail(err, TSM100_ERR_INVALID, "attention_decode: unknown dtype");
+  if (d->batch < 0 || d->heads_q <= 0 || d->heads_kv <= 0 || d->seq_len < 0 || d->max_seq < d->seq_len)
+    return op_fail(err, TSM100_ERR_INVALID, "attention_decode: bad shape (need heads > 0 and 0 <= seq_len <= max_seq)");
+  if (d->heads_q % d->heads_kv != 0)
+    return op_fail(err, TSM100_ERR_INVALID, "attention_decode: heads_q must be a multiple of heads_kv");
+  if (d->head_dim != 64 && d->head_dim != 128)
+    return op_fail(err, TSM100_ERR_INVALID, "attention_decode: head_dim must be 64 or 128");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
+    return op_fail(err, TSM100_ERR_INVALID, "attention_decode: buffers must be 16-byte aligned");
+  if (d->batch == 0) return TSM100_OK;
+  if (static_cast<int64_t>(d->batch) * d->heads_kv * attn_decode::kMaxSplits > 0x7fffffff)
+    return op_fail(err, TSM100_ERR_INVALID, "attention_decode: too many (batch, KV head) units for one launch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool d128 = d->head_dim == 128;
+  switch (d->dtype) {
+    case TSM100_F32:
+      return d128 ? attention_decode_typed<float, 128>(err, d, q, k, v, o, s) : attention_decode_typed<float, 64>(err, d, q, k, v, o, s);
+    case TSM100_BF16:
+      return d128 ? attention_decode_typed<__nv_bfloat16, 128>(err, d, q, k, v, o, s)
+                  : attention_decode_typed<__nv_bfloat16, 64>(err, d, q, k, v, o, s);
+    default:
+      return d128 ? attention_decode_typed<__half, 128>(err, d, q, k, v, o, s) : attention_decode_typed<__half, 64>(err, d, q, k, v, o, s);
+  }
 }
 
 template <bool kBf16>

@@ -407,6 +407,12 @@ class CudaSm100Device:
         d = capi.AttentionDesc(dtype, int(causal), batch, heads_q, heads_kv, seq, head_dim)
         check(capi.lib().tsm100_attention(self._h, C.byref(d), q, k, v, o, stream or None))
 
+    def attention_decode(self, dtype: int, batch: int, heads_q: int, heads_kv: int, seq_len: int, max_seq: int, head_dim: int,
+                         q: int, k_cache: int, v_cache: int, o: int, stream: int = 0) -> None:
+        """One query token per head against the first ``seq_len`` positions of a [batch, heads_kv, max_seq, d] cache."""
+        d = capi.AttentionDecodeDesc(dtype, batch, heads_q, heads_kv, seq_len, max_seq, head_dim)
+        check(capi.lib().tsm100_attention_decode(self._h, C.byref(d), q, k_cache, v_cache, o, stream or None))
+
     # -- operators on host buffers (upload + compute + download) --
     def softmax_host(self, dtype: int, rows: int, cols: int, x: int, y: int) -> None:
         d = capi.SoftmaxDesc(dtype, rows, cols)
