@@ -18,6 +18,8 @@
 // Roofline: HBM.
 #pragma once
 
+#include <type_traits>
+
 #include "ptx.cuh"
 #include "softmax.cuh"
 
@@ -219,5 +221,273 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ kc, const
   ptx::cluster_sync_all();  // nobody leaves while its shared memory may still be read
 }
 
+// ===========================================================================
+// 16-bit caches: the same operator on tensor cores.  With 16-bit storage the FP32 pipe
+// cannot keep up with HBM once several query heads share a cache row (8 heads: ~145
+// instructions per row and warp above), so the query heads of a group become the M
+// dimension of mma.sync m16n8k16 tiles: S[16 heads x 16 positions] = Q K^T and
+// O[16 heads x D] += P V, f32 accumulation, online softmax on the accumulator fragments.
+// (tcgen05 needs 64 or 128 rows per tile; 16 padded rows per (batch, KV head) is what a
+// decode step has, so this is the one place the warp-level MMA is the right size.)
+//
+// Per CTA 4 warps; each warp streams its own tiles of 16 positions through a two-stage
+// cp.async ring in shared memory (K and V rows padded by 16 bytes: conflict-free
+// ldmatrix), keeps its own running (max, sum, O) and the partial results are merged as
+// above: warps through shared memory, CTAs of the cluster through distributed shared memory.
+// ===========================================================================
+namespace mma {
+
+constexpr int kThreads = 128;
+constexpr int kWarps = 4;
+constexpr int kTilePos = 16;   // positions per tile
+constexpr int kRows = 16;      // query heads per pass (rows of the MMA tile)
+
+template <int D>
+constexpr int pitch_bytes() { return D * 2 + 16; }
+template <int D>
+constexpr int stage_bytes() { return 2 * kTilePos * pitch_bytes<D>(); }   // K tile + V tile
+// ring (a warp's record for the merge later overlays its own part of it), Q, the CTA's merged record
+template <int D>
+constexpr int smem_bytes() { return kWarps * 2 * stage_bytes<D>() + kRows * D * 2 + kRows * (D + 2) * 4; }
+
+__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr, bool valid) {
+  const int n = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+template <bool kIsBf16>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if (kIsBf16)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <bool kIsBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (kIsBf16) return ptx::pack_bf16x2(lo, hi);
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads)
+attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc, T* __restrict__ o,
+                            const Params p) {
+  constexpr bool kIsBf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+  constexpr int PITCH = pitch_bytes<D>();
+  constexpr int KSTEPS = D / 16;      // k-steps of Q K^T; pairs of 8-wide output tiles of P V
+  constexpr int REC = D + 2;
+  constexpr int CHUNKS = D * 2 / 16;  // 16-byte pieces per cache row
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  uint8_t* ring = smem_raw;                                           // [warp][stage][K | V][16 rows][PITCH]
+  T* q_s = reinterpret_cast<T*>(smem_raw + kWarps * 2 * stage_bytes<D>());   // [16][D], rows beyond heads_here zero
+  float* mine = reinterpret_cast<float*>(q_s + kRows * D);            // [16][REC]
+  constexpr int WARP_FLOATS = 2 * stage_bytes<D>() / 4;              // a warp's ring share, reused for its record [16][REC]
+  static_assert(kRows * REC <= WARP_FLOATS, "a warp's record must fit into its ring share");
+  float* part = reinterpret_cast<float*>(ring);                       // warp w's record at part + w * WARP_FLOATS
+
+  const uint32_t rank = ptx::cluster_ctarank(), splits = ptx::cluster_nctarank();
+  const int unit = blockIdx.x / splits;
+  const int b = unit / p.heads_kv, g = unit % p.heads_kv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gr = lane >> 2, tq = lane & 3;   // fragment row group and column pair
+  const int h0 = g * p.group + p.head_base;
+
+  for (int i = tid; i < kRows * D; i += kThreads) {
+    const int hh = i / D, dd = i % D;
+    q_s[i] = hh < p.heads_here ? q[(static_cast<int64_t>(b) * p.heads_q + h0 + hh) * D + dd] : softmax::Elem<T>::zero();
+  }
+  __syncthreads();
+  // A fragments of Q for every k-step: a0 (row gr, k 2tq..), a1 (row gr+8, ..), a2 (row gr, k 2tq+8..), a3 (row gr+8, ..)
+  uint32_t qa[KSTEPS][4];
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+    const uint32_t* r0 = reinterpret_cast<const uint32_t*>(q_s + gr * D + kk * 16);
+    const uint32_t* r1 = reinterpret_cast<const uint32_t*>(q_s + (gr + 8) * D + kk * 16);
+    qa[kk][0] = r0[tq];
+    qa[kk][1] = r1[tq];
+    qa[kk][2] = r0[tq + 4];
+    qa[kk][3] = r1[tq + 4];
+  }
+
+  const int chunk = ((p.seq_len + static_cast<int>(splits) - 1) / static_cast<int>(splits) + 63) & ~63;
+  const int p_begin = static_cast<int>(rank) * chunk;
+  const int p_end = min(p.seq_len, p_begin + chunk);
+  const int n_tiles = p_end > p_begin ? (p_end - p_begin + kTilePos - 1) / kTilePos : 0;
+  const int64_t cache_off = (static_cast<int64_t>(b) * p.heads_kv + g) * p.max_seq * D;
+  const uint8_t* kbase = reinterpret_cast<const uint8_t*>(kc + cache_off);
+  const uint8_t* vbase = reinterpret_cast<const uint8_t*>(vc + cache_off);
+  const uint32_t ring_w = ptx::smem_u32(ring) + warp * 2 * stage_bytes<D>();
+
+  auto prefetch = [&](int tile, int stage) {  // this warp's tile `tile` of the CTA's range into its ring stage
+    const int row0 = p_begin + tile * kTilePos;
+    const uint32_t dst = ring_w + stage * stage_bytes<D>();
+#pragma unroll
+    for (int c = lane; c < kTilePos * CHUNKS; c += 32) {
+      const int r = c / CHUNKS, cc = c % CHUNKS;
+      const bool ok = row0 + r < p_end;
+      const int64_t src = (static_cast<int64_t>(ok ? row0 + r : p_begin)) * (D * 2) + cc * 16;
+      cp_async_16(dst + r * PITCH + cc * 16, kbase + src, ok);
+      cp_async_16(dst + kTilePos * PITCH + r * PITCH + cc * 16, vbase + src, ok);
+    }
+  };
+
+  float oacc[2 * KSTEPS][4];
+#pragma unroll
+  for (int j = 0; j < 2 * KSTEPS; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oacc[j][e] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows gr and gr + 8 (this thread's share of the sums)
+  const float sl2 = p.scale_log2;
+
+  if (warp < n_tiles) prefetch(warp, 0);
+  cp_async_commit();
+  int stage = 0;
+  for (int t = warp; t < n_tiles; t += kWarps, stage ^= 1) {
+    if (t + kWarps < n_tiles) prefetch(t + kWarps, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();  // everything but the newest group: this tile has landed
+    __syncwarp();
+    const uint32_t ks = ring_w + stage * stage_bytes<D>();
+    const uint32_t vs = ks + kTilePos * PITCH;
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      uint32_t kb[4];  // (positions 0-7, k lo), (0-7, k hi), (8-15, k lo), (8-15, k hi)
+      ldmatrix_x4(ks + ((lane & 7) + ((lane >> 4) & 1) * 8) * PITCH + (kk * 16 + ((lane >> 3) & 1) * 8) * 2, kb);
+      mma_16816<kIsBf16>(s[0], qa[kk], kb[0], kb[1]);
+      mma_16816<kIsBf16>(s[1], qa[kk], kb[2], kb[3]);
+    }
+    // scale to log2 units; positions past the end of the range carry no weight
+    const int pos = p_begin + t * kTilePos + 2 * tq;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int pp = pos + j * 8 + (e & 1);
+        s[j][e] = pp < p_end ? s[j][e] * sl2 : -INFINITY;
+      }
+    float t0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+    float t1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+    const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);  // finite: a tile has at least one valid position
+    const float a0 = ptx::ex2_approx(m0 - n0), a1 = ptx::ex2_approx(m1 - n1);  // first tile: 2^(-inf) = 0
+    m0 = n0;
+    m1 = n1;
+    uint32_t pa[4];
+    {
+      const float p00 = ptx::ex2_approx(s[0][0] - n0), p01 = ptx::ex2_approx(s[0][1] - n0);
+      const float p02 = ptx::ex2_approx(s[0][2] - n1), p03 = ptx::ex2_approx(s[0][3] - n1);
+      const float p10 = ptx::ex2_approx(s[1][0] - n0), p11 = ptx::ex2_approx(s[1][1] - n0);
+      const float p12 = ptx::ex2_approx(s[1][2] - n1), p13 = ptx::ex2_approx(s[1][3] - n1);
+      l0 = fmaf(l0, a0, (p00 + p01) + (p10 + p11));
+      l1 = fmaf(l1, a1, (p02 + p03) + (p12 + p13));
+      pa[0] = pack2<kIsBf16>(p00, p01);  // row gr,     positions 2tq..
+      pa[1] = pack2<kIsBf16>(p02, p03);  // row gr + 8, positions 2tq..
+      pa[2] = pack2<kIsBf16>(p10, p11);  // row gr,     positions 2tq + 8..
+      pa[3] = pack2<kIsBf16>(p12, p13);  // row gr + 8, positions 2tq + 8..
+    }
+#pragma unroll
+    for (int j = 0; j < 2 * KSTEPS; ++j) {
+      oacc[j][0] *= a0;
+      oacc[j][1] *= a0;
+      oacc[j][2] *= a1;
+      oacc[j][3] *= a1;
+    }
+#pragma unroll
+    for (int jj = 0; jj < KSTEPS; ++jj) {
+      uint32_t vb[4];  // (positions 0-7, d lo), (8-15, d lo), (0-7, d hi), (8-15, d hi), transposed on load
+      ldmatrix_x4_trans(vs + ((lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + (jj * 16 + ((lane >> 4) & 1) * 8) * 2, vb);
+      mma_16816<kIsBf16>(oacc[2 * jj], pa, vb[0], vb[1]);
+      mma_16816<kIsBf16>(oacc[2 * jj + 1], pa, vb[2], vb[3]);
+    }
+    __syncwarp();  // the stage is refilled two iterations from now; every lane is done reading it
+  }
+  cp_async_wait<0>();
+  __syncwarp();  // the warp's ring share is free: it now receives the warp's record
+  // this thread's share of the row sums -> the whole row's
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+  // warp records -> shared memory: row r of warp w at part[(w * 16 + r) * REC]: O[D], max, sum
+  {
+    float* r0 = part + warp * WARP_FLOATS + gr * REC;
+    float* r1 = part + warp * WARP_FLOATS + (gr + 8) * REC;
+#pragma unroll
+    for (int j = 0; j < 2 * KSTEPS; ++j) {
+      r0[j * 8 + 2 * tq] = oacc[j][0];
+      r0[j * 8 + 2 * tq + 1] = oacc[j][1];
+      r1[j * 8 + 2 * tq] = oacc[j][2];
+      r1[j * 8 + 2 * tq + 1] = oacc[j][3];
+    }
+    if (tq == 0) {
+      r0[D] = m0;
+      r0[D + 1] = l0;
+      r1[D] = m1;
+      r1[D + 1] = l1;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < kRows * D; i += kThreads) {
+    const int hh = i / D, dd = i % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, part[w * WARP_FLOATS + hh * REC + D]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float* rec = part + w * WARP_FLOATS + hh * REC;
+      const float wgt = rec[D] == -INFINITY ? 0.f : ptx::ex2_approx(rec[D] - mm);  // a warp without tiles carries no weight
+      ll = fmaf(rec[D + 1], wgt, ll);
+      oo = fmaf(rec[dd], wgt, oo);
+    }
+    mine[hh * REC + dd] = oo;
+    if (dd == 0) {
+      mine[hh * REC + D] = mm;
+      mine[hh * REC + D + 1] = ll;
+    }
+  }
+  ptx::cluster_sync_all();
+  if (rank == 0) {
+    const uint32_t mine_addr = ptx::smem_u32(mine);
+    for (int i = tid; i < kRows * D; i += kThreads) {
+      const int hh = i / D, dd = i % D;
+      if (hh >= p.heads_here) continue;
+      float mm = -INFINITY;
+      for (uint32_t r = 0; r < splits; ++r)
+        mm = fmaxf(mm, ptx::ld_shared_cluster_f32(ptx::mapa_shared(mine_addr + (hh * REC + D) * 4, r)));
+      float ll = 0.f, oo = 0.f;
+      for (uint32_t r = 0; r < splits; ++r) {
+        const uint32_t base = ptx::mapa_shared(mine_addr + hh * REC * 4, r);
+        const float mr = ptx::ld_shared_cluster_f32(base + D * 4);
+        const float wgt = mr == -INFINITY ? 0.f : ptx::ex2_approx(mr - mm);
+        ll = fmaf(ptx::ld_shared_cluster_f32(base + (D + 1) * 4), wgt, ll);
+        oo = fmaf(ptx::ld_shared_cluster_f32(base + dd * 4), wgt, oo);
+      }
+      softmax::Elem<T>::store1(o + (static_cast<int64_t>(b) * p.heads_q + h0 + hh) * D + dd, oo / ll);
+    }
+  }
+  ptx::cluster_sync_all();  // nobody leaves while its shared memory may still be read
+}
+
+}  // namespace mma
 }  // namespace attn_decode
 }  // namespace tsm100

@@ -524,6 +524,40 @@ inline int32_t attention_decode_launch(std::string* err, const tsm100_attention_
 }
 
 template <typename T, int D>
+inline int32_t attention_decode_mma_launch(std::string* err, const tsm100_attention_decode_desc* d, const T* q, const T* k,
+                                           const T* v, T* o, int head_base, int heads_here, int splits, cudaStream_t s) {
+  namespace ad = attn_decode;
+  ad::Params p;
+  p.batch = d->batch;
+  p.heads_q = d->heads_q;
+  p.heads_kv = d->heads_kv;
+  p.seq_len = d->seq_len;
+  p.max_seq = d->max_seq;
+  p.group = d->heads_q / d->heads_kv;
+  p.head_base = head_base;
+  p.heads_here = heads_here;
+  p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
+  auto kern = ad::mma::attention_decode_mma_kernel<T, D>;
+  constexpr int smem = ad::mma::smem_bytes<D>();
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_decode_mma_kernel)");
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.blockDim = dim3(ad::mma::kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cfg.gridDim = dim3(static_cast<unsigned>(static_cast<int64_t>(d->batch) * d->heads_kv * splits));
+  e = cudaLaunchKernelEx(&cfg, kern, q, k, v, o, p);
+  return cuda_ok(err, e, "attention_decode_mma_kernel launch");
+}
+
+template <typename T, int D>
 inline int32_t attention_decode_typed(std::string* err, const tsm100_attention_decode_desc* d, const void* q, const void* k,
                                       const void* v, void* o, cudaStream_t s) {
   int sms = 0;
@@ -539,6 +573,15 @@ inline int32_t attention_decode_typed(std::string* err, const tsm100_attention_d
   const T* kp = static_cast<const T*>(k);
   const T* vp = static_cast<const T*>(v);
   T* op = static_cast<T*>(o);
+  if constexpr (sizeof(T) == 2) {
+    // 16-bit storage: tensor cores, up to 16 query heads of a group per pass; 4 warps x 16 positions per CTA,
+    // so the GPU is covered about four times before the ranges get shorter than 256 positions
+    splits = 1;
+    while (splits < attn_decode::kMaxSplits && units * splits < 4ll * sms && d->seq_len / (2 * splits) >= 256) splits *= 2;
+    for (int base = 0; base < group && st == TSM100_OK; base += 16)
+      st = attention_decode_mma_launch<T, D>(err, d, qp, kp, vp, op, base, std::min(16, group - base), splits, s);
+    return st;
+  }
   // groups wider than 8 query heads run in passes of 8 (the cache is then re-read, from L2 when it fits)
   for (int base = 0; base < group && st == TSM100_OK; base += 8) {
     const int here = std::min(8, group - base);

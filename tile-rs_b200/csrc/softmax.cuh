@@ -75,6 +75,7 @@ struct Elem<__nv_bfloat16> {
     }
     return v;
   }
+  __device__ static __forceinline__ __nv_bfloat16 zero() { return __float2bfloat16_rn(0.f); }
   __device__ static __forceinline__ float load1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
   __device__ static __forceinline__ void store1(__nv_bfloat16* p, float f) { *p = __float2bfloat16_rn(f); }
 };
@@ -100,6 +101,7 @@ struct Elem<__half> {
     }
     return v;
   }
+  __device__ static __forceinline__ __half zero() { return __float2half_rn(0.f); }
   __device__ static __forceinline__ float load1(const __half* p) { return __half2float(*p); }
   __device__ static __forceinline__ void store1(__half* p, float f) { *p = __float2half_rn(f); }
 };
