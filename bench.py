@@ -371,6 +371,10 @@ NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per full-size la
     "gemm_bf16_8192": 1064.7e6 + 127.0e6,
     "attention_causal": 4 * (201.4e6 + 48.2e6),   # captured on 64 of 256 heads, scaled by heads
     "attention_noncausal": 4 * (201.4e6 + 48.0e6),
+    "rms_norm_f32": 4 * (268.4e6 + 214.9e6),
+    "reduce_sum_f32": 4 * (268.5e6 + 3.2e6),
+    "silu_mul_f32": 4 * (536.9e6 + 229.3e6),
+    "attention_decode_bf16": 4 * (537.0e6 + 4.6e6),
 }
 
 
