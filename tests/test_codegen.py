@@ -57,7 +57,8 @@ def test_debug_target(cg):
 CASES = {
     "softmax": (F.softmax(), ["softmax_rows_warp<float, 8, 4>", "d.cols = 1024", "tsm100::ops::softmax"]),
     "softmax_bf16_io": (F.softmax_bf16_io(), ["softmax_rows_cta<__nv_bfloat16, 4, 128>", "TSM100_BF16", "d.cols = 4096"]),
-    "matmul_f32": (F.matmul(), ["gemm_simt_kernel<float, float", "d.m = 128", "tsm100::ops::gemm"]),
+    "matmul_f32": (F.matmul(), ["gemm_tf32x3_kernel<false>", "d.m = 128", "tsm100::ops::gemm"]),
+    "matmul_f32_odd": (F.matmul(m=33, k=30, n=17), ["gemm_simt_kernel<float, float", "d.k = 30"]),
     "matmul_f16": (F.matmul(dt="f16", m=64, k=128, n=64), ["gemm_tc_kernel<__half, false, false>", "TSM100_F16", "tcgen05"]),
     "matmul_bf16": (F.matmul(dt="bf16", m=8192, k=8192, n=8192), ["gemm_tc_kernel<__nv_bfloat16, false, true>", "d.k = 8192"]),
     "matmul_f16_acc_f32": (F.matmul(dt="f16", out_dt="f32"), ["gemm_tc_kernel<float, false, false>", "d.out_dtype = TSM100_F32"]),

@@ -21,8 +21,12 @@ def run_gemm(dev, capi, a, b, m, n, k, dtype, out_dtype=None, b_transposed=False
     return cd.cpu().numpy()
 
 
+# aligned rows (K % 4 == 0, N % 4 == 0): tensor cores with three TF32 products per product, with and without a
+# cluster splitting K; anything else: the FP32 pipe
 @pytest.mark.parametrize("m,n,k,bt", [(512, 512, 512, False), (512, 512, 512, True), (65, 33, 17, False),
-                                       (1, 1, 1, False), (100, 300, 77, True), (130, 70, 260, False)])
+                                       (1, 1, 1, False), (100, 300, 77, True), (130, 70, 260, False),
+                                       (100, 300, 76, True), (130, 72, 260, False), (64, 64, 4096, False), (1, 4, 8, False),
+                                       (1024, 1024, 1024, False), (70, 2, 128, True), (3, 1000, 36, False)])
 def test_gemm_f32(dev, pkg, oracle, m, n, k, bt):
     capi = pkg.capi
     a = util.gen_uniform(capi, (m, k), 101)
@@ -32,6 +36,21 @@ def test_gemm_f32(dev, pkg, oracle, m, n, k, bt):
         mt = oracle.compare(c, ref)
         assert mt["rel_max"] <= util.F32_REL, mt
         assert mt["rel_fro"] <= util.F32_REL, mt
+
+
+def test_gemm_f32_wide_dynamic_range_and_batch(dev, pkg, oracle):
+    """Entries spread over six decades: the split into hi and lo halves must keep f32 accuracy for every magnitude."""
+    capi = pkg.capi
+    batch, m, n, k = 3, 96, 80, 512
+    mag = 10.0 ** (3.0 * util.gen_uniform(capi, (batch, m, k), 111))
+    a = (util.gen_uniform(capi, (batch, m, k), 112) * mag).astype(np.float32)
+    b = util.gen_normal(capi, (batch, k, n), 113)
+    c = run_gemm(dev, capi, a, b, m, n, k, capi.F32, batch=batch)
+    for i in range(batch):
+        truth = oracle.gemm_f32(a[i], b[i], False, f64_acc=True)
+        # row-wise bound: every output row against the largest magnitude of that row (rows differ by decades)
+        err = np.abs(c[i] - truth).max(axis=1) / np.abs(truth).max(axis=1)
+        assert err.max() <= util.F32_REL, err.max()
 
 
 TC_SHAPES = [

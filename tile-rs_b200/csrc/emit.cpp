@@ -992,7 +992,11 @@ Kernel lower(const Func& f) {
            << "], status, stream);\n";
       const bool tma = a.dtype != Dt::F32 && prod->k % 8 == 0 && (bt || prod->n % 8 == 0) &&
                        (prod->n * (out_dt == Dt::F32 ? 4 : 2)) % 16 == 0;
-      if (tma)
+      const bool tf32x3 = a.dtype == Dt::F32 && prod->k % 4 == 0 && (bt || prod->n % 4 == 0) && prod->n % 2 == 0;
+      if (tf32x3)
+        inst << "template __global__ void tsm100::gemm_tf32x3::gemm_tf32x3_kernel<" << (bt ? "true" : "false")
+             << ">(const float*, const float*, float*, const tsm100::gemm_tf32x3::Params);\n";
+      else if (tma)
         inst << "template __global__ void tsm100::gemm_tc::gemm_tc_kernel<" << cxx_type(out_dt) << ", " << (bt ? "true" : "false")
              << ", " << (a.dtype == Dt::BF16 ? "true" : "false") << ">(const __grid_constant__ CUtensorMap, const __grid_constant__ CUtensorMap, " << cxx_type(out_dt)
              << "*, const tsm100::gemm_tc::Params);\n";

@@ -2,11 +2,10 @@
 //
 // This is the kernel behind __tile_matmul_f32 (crates/tile_std/src/tile.rs:192-193;
 // linalg.fill 0 + linalg.matmul, crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1345-1393)
-// and __tile_matmul_transposed_f32 (tile.rs:2017-2031).  f32 inputs must agree
-// with an f32 CPU contraction to 1e-5, which the tensor cores' TF32 mode (10-bit
-// mantissa) cannot give, so the contraction runs on the FP32 pipe.  It is also
-// the any-shape path for 16-bit inputs whose leading dimensions are not
-// 16-byte multiples (TMA cannot address those).
+// and __tile_matmul_transposed_f32 (tile.rs:2017-2031) when the rows of the operands
+// do not start on 16-byte boundaries (aligned f32 problems run on tensor cores with three
+// TF32 products per product, gemm_tf32x3.cuh), and the any-shape path for 16-bit inputs
+// whose leading dimensions are not 16-byte multiples (TMA cannot address those).
 //
 // Tiling: BM x BN output tile per CTA, BK-deep shared-memory panels, TM x TN
 // register micro-tile per thread, every access bounds-checked.

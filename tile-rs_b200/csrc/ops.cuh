@@ -23,6 +23,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_tc2.cuh"
+#include "gemm_tf32x3.cuh"
 #include "rowops.cuh"
 #include "softmax.cuh"
 
@@ -333,6 +334,51 @@ inline int32_t gemm_simt_launch(std::string* err, const tsm100_gemm_desc* d, con
   return cuda_ok(err, cudaGetLastError(), "gemm_simt launch");
 }
 
+// f32 inputs on tensor cores (three TF32 products per product, see gemm_tf32x3.cuh)
+inline int32_t gemm_tf32x3_launch(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
+                                  cudaStream_t s) {
+  namespace g = gemm_tf32x3;
+  int sms = 0;
+  int32_t st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  const int64_t tiles = ((d->m + g::kBM - 1) / g::kBM) * ((d->n + g::kBN - 1) / g::kBN) * d->batch;
+  if (tiles * g::kMaxSplit > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "gemm: too many tiles for one launch");
+  // fewer tiles than SMs: a cluster splits K, as long as every CTA keeps at least four 32-deep slices
+  int splits = 1;
+  while (splits < g::kMaxSplit && tiles * splits * 2 <= sms && d->k / (2 * splits) >= 4 * g::kBK) splits *= 2;
+  g::Params p;
+  p.m = static_cast<int32_t>(d->m);
+  p.n = static_cast<int32_t>(d->n);
+  p.k = static_cast<int32_t>(d->k);
+  p.batch = d->batch;
+  p.k_per_cta = static_cast<int32_t>(((d->k + splits - 1) / splits + g::kBK - 1) / g::kBK * g::kBK);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.blockDim = dim3(g::kThreads);
+  cfg.dynamicSmemBytes = g::kSmemBytes;
+  cfg.stream = s;
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * splits));
+  cudaError_t e;
+  if (d->b_transposed) {
+    auto kern = g::gemm_tf32x3_kernel<true>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaLaunchKernelEx(&cfg, kern, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), p);
+  } else {
+    auto kern = g::gemm_tf32x3_kernel<false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaLaunchKernelEx(&cfg, kern, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), p);
+  }
+  return cuda_ok(err, e, "gemm_tf32x3_kernel launch");
+}
+
 template <typename OutT, bool kBT, bool kBf16>
 inline int32_t gemm_tc_launch(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
                               uint32_t* status, cudaStream_t s) {
@@ -440,7 +486,13 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
     const size_t bytes = static_cast<size_t>(d->batch) * d->m * d->n * dtype_size(d->out_dtype);
     return cuda_ok(err, cudaMemsetAsync(c, 0, bytes, s), "cudaMemsetAsync");
   }
-  if (d->dtype == TSM100_F32) return gemm_simt_launch<float, float>(err, d, a, b, c, s);
+  if (d->dtype == TSM100_F32) {
+    // rows that start on 16-byte boundaries: tensor cores; anything else: the FP32 pipe
+    const bool vec_ok = aligned16(a) && aligned16(b) && aligned16(c) && d->k % 4 == 0 && (d->b_transposed || d->n % 4 == 0) &&
+                        d->n % 2 == 0;
+    if (vec_ok) return gemm_tf32x3_launch(err, d, a, b, c, s);
+    return gemm_simt_launch<float, float>(err, d, a, b, c, s);
+  }
 
   const bool bf16 = d->dtype == TSM100_BF16;
   const bool out_f32 = d->out_dtype == TSM100_F32;
