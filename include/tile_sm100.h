@@ -243,6 +243,37 @@ int32_t tsm100_attention(tsm100_device_t dev, const tsm100_attention_desc* desc,
                          const void* k, const void* v, void* o, void* stream);
 
 /* ---- operators on HOST memory (upload, compute, download in one call) ---- */
+/* Rotary position embedding, in place: the pair (x[2i], x[2i+1]) of every head of token s is rotated by
+ * the angle (start_pos + s) * theta^(-2i / head_dim).  x is [batch][seq_len][heads][head_dim].
+ * __tile_rope_inplace_f32 (seq_len 1, start_pos = the position) and __tile_rope_prefill_f32
+ * (tile.rs:2113-2115, :2128-2129); arithmetic of crates/rustc_codegen_tile/src/mlir_to_msl.rs:10707-10728,
+ * :10883-10908, whose run-time constants position / start_pos and theta are fields here. */
+typedef struct {
+  int32_t dtype;
+  int32_t batch;
+  int32_t seq_len;
+  int32_t heads;
+  int32_t head_dim; /* even */
+  int32_t start_pos;
+  float theta;
+} tsm100_rope_desc;
+int32_t tsm100_rope(tsm100_device_t dev, const tsm100_rope_desc* desc, void* x, void* stream);
+
+/* KV-cache append: cache[b, h, start_pos + s, :] = src[b, s, h, :] with src [batch][seq_len][heads][head_dim]
+ * and cache [batch][heads][max_seq][head_dim].  __tile_kv_cache_update_f32 (seq_len 1) and
+ * __tile_kv_cache_update_prefill_f32 (tile.rs:2117-2119, :2131-2132; mlir_to_msl.rs:10730-10741, :10910-10926). */
+typedef struct {
+  int32_t dtype;
+  int32_t batch;
+  int32_t seq_len;
+  int32_t heads;
+  int32_t head_dim;
+  int32_t start_pos;
+  int32_t max_seq;
+} tsm100_kv_cache_update_desc;
+int32_t tsm100_kv_cache_update(tsm100_device_t dev, const tsm100_kv_cache_update_desc* desc, const void* src,
+                               void* cache, void* stream);
+
 /* Single-token (decode) attention against a KV cache:
  *   o[b,h,:] = softmax_p(q[b,h,:] . K[b,g,p,:] / sqrt(d)) V[b,g,p,:],  p < seq_len,  g = h / (heads_q / heads_kv).
  * __tile_attention_decode_f32 (tile.rs:2120-2124; wrapper :3004-3018): q, o [heads_q][d], caches

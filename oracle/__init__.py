@@ -51,13 +51,15 @@ def lib() -> C.CDLL:
         h.orc_silu_mul_bf16.argtypes = [_vp, _vp, _vp, _vp, _i64]
         h.orc_attention_decode_f32.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]
         h.orc_attention_decode_bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64]
+        h.orc_rope_f32.argtypes = [_vp, _i64, _i64, _i64, _i64, _i64, C.c_float, C.c_int]
+        h.orc_kv_cache_update.argtypes = [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64]
         h.orc_compare_f32.argtypes = [_vp, _vp, _i64, C.c_double, _vp]
         h.orc_bf16_to_f32.argtypes = [_vp, _vp, _i64]
         h.orc_f32_to_bf16.argtypes = [_vp, _vp, _i64]
         for name in ("orc_gemm_f32", "orc_gemm_f64acc", "orc_gemm_bf16", "orc_softmax_f32", "orc_softmax_f64acc",
                      "orc_softmax_bf16", "orc_attention_f32", "orc_attention_bf16", "orc_compare_f32",
                      "orc_bf16_to_f32", "orc_f32_to_bf16", "orc_rms_norm_f32", "orc_rms_norm_bf16", "orc_reduce_f32",
-                     "orc_silu_mul_f32", "orc_silu_mul_bf16", "orc_attention_decode_f32", "orc_attention_decode_bf16"):
+                     "orc_silu_mul_f32", "orc_silu_mul_bf16", "orc_attention_decode_f32", "orc_attention_decode_bf16", "orc_rope_f32", "orc_kv_cache_update"):
             getattr(h, name).restype = None
         _LIB = h
     return _LIB
@@ -166,6 +168,24 @@ def silu_mul_bf16(gate: np.ndarray, up):
     y16 = np.empty(gate.shape, np.uint16)
     lib().orc_silu_mul_bf16(_p(gate), None if upc is None else _p(upc), _p(y32), _p(y16), gate.size)
     return y32, y16
+
+
+def rope_f32(x: np.ndarray, start_pos: int, theta: float, f64_acc: bool = False) -> np.ndarray:
+    """x: [batch, seq_len, heads, d]; returns the rotated copy."""
+    y = np.array(x, np.float32, order="C", copy=True)
+    b, s, h, d = y.shape
+    lib().orc_rope_f32(_p(y), b, s, h, d, start_pos, theta, int(f64_acc))
+    return y
+
+
+def kv_cache_update(src: np.ndarray, cache: np.ndarray, start_pos: int) -> np.ndarray:
+    """src: [batch, seq_len, heads, d]; cache: [batch, heads, max_seq, d] (same dtype); returns the updated copy."""
+    src = np.ascontiguousarray(src)
+    out = np.array(cache, order="C", copy=True)
+    assert src.dtype == out.dtype
+    b, s, h, d = src.shape
+    lib().orc_kv_cache_update(_p(src), _p(out), src.dtype.itemsize, b, s, h, d, start_pos, out.shape[2])
+    return out
 
 
 def attention_decode_f32(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, seq_len: int, f64_acc: bool = False) -> np.ndarray:

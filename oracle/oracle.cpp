@@ -528,4 +528,53 @@ void orc_attention_decode_bf16(const uint16_t* q, const uint16_t* kc, const uint
     for (int64_t i = 0; i < nq; ++i) o_bf16[i] = f32_to_bf16(of[i]);
 }
 
+// __tile_rope_inplace_f32 / __tile_rope_prefill_f32 on x [batch][seq_len][heads][d], in place
+// (crates/rustc_codegen_tile/src/mlir_to_msl.rs:10707-10728, :10883-10908): for pair index i of
+// the token at position pos = start_pos + s: freq = 1 / pow(theta, 2 i / d), angle = float(pos) * freq,
+// (x0, x1) -> (x0 cos - x1 sin, x0 sin + x1 cos), all in f32; f64acc != 0 evaluates the same in double.
+void orc_rope_f32(float* x, int64_t batch, int64_t seq_len, int64_t heads, int64_t d, int64_t start_pos, float theta, int f64acc) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t b = 0; b < batch; ++b)
+    for (int64_t s = 0; s < seq_len; ++s)
+      for (int64_t i = 0; i < d / 2; ++i) {
+        const int64_t pos = start_pos + s;
+        double c, sn;
+        if (f64acc) {
+          const double ang = static_cast<double>(pos) / std::pow(static_cast<double>(theta), 2.0 * i / static_cast<double>(d));
+          c = std::cos(ang);
+          sn = std::sin(ang);
+        } else {
+          const float freq = 1.0f / powf(theta, 2.0f * static_cast<float>(i) / static_cast<float>(d));
+          const float ang = static_cast<float>(pos) * freq;
+          c = cosf(ang);
+          sn = sinf(ang);
+        }
+        for (int64_t h = 0; h < heads; ++h) {
+          float* p = x + ((b * seq_len + s) * heads + h) * d + 2 * i;
+          if (f64acc) {
+            const double x0 = p[0], x1 = p[1];
+            p[0] = static_cast<float>(x0 * c - x1 * sn);
+            p[1] = static_cast<float>(x0 * sn + x1 * c);
+          } else {
+            const float x0 = p[0], x1 = p[1], cf = static_cast<float>(c), sf = static_cast<float>(sn);
+            p[0] = x0 * cf - x1 * sf;
+            p[1] = x0 * sf + x1 * cf;
+          }
+        }
+      }
+}
+
+// __tile_kv_cache_update_f32 / _prefill_f32 (mlir_to_msl.rs:10730-10741, :10910-10926), any 4-byte or 2-byte
+// element: cache[b][h][start_pos + s][:] = src[b][s][h][:].
+void orc_kv_cache_update(const void* src, void* cache, int64_t elem_bytes, int64_t batch, int64_t seq_len, int64_t heads,
+                         int64_t d, int64_t start_pos, int64_t max_seq) {
+  const char* sp = static_cast<const char*>(src);
+  char* cp = static_cast<char*>(cache);
+  for (int64_t b = 0; b < batch; ++b)
+    for (int64_t s = 0; s < seq_len; ++s)
+      for (int64_t h = 0; h < heads; ++h)
+        std::memcpy(cp + (((b * heads + h) * max_seq + start_pos + s) * d) * elem_bytes,
+                    sp + (((b * seq_len + s) * heads + h) * d) * elem_bytes, d * elem_bytes);
+}
+
 }  // extern "C"

@@ -67,6 +67,20 @@ EWISE = {
 }
 
 
+def rope(x: np.ndarray, start_pos: int, theta: float) -> np.ndarray:
+    """Rotary embedding of x [batch, seq_len, heads, d] (mlir_to_msl.rs:10883-10908), in float64."""
+    x = x.astype(np.float64)
+    b, s, h, d = x.shape
+    i = np.arange(d // 2, dtype=np.float64)
+    ang = (start_pos + np.arange(s, dtype=np.float64))[:, None] / np.float64(np.float32(theta)) ** (2.0 * i / d)[None, :]
+    c, sn = np.cos(ang)[None, :, None, :], np.sin(ang)[None, :, None, :]
+    x0, x1 = x[..., 0::2], x[..., 1::2]
+    out = np.empty_like(x)
+    out[..., 0::2] = x0 * c - x1 * sn
+    out[..., 1::2] = x0 * sn + x1 * c
+    return out
+
+
 def attention_decode(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, seq_len: int) -> np.ndarray:
     """One query token per head against the first seq_len cache positions (mlir_to_msl.rs:10747-10812), in float64.
     q: [batch, hq, d]; caches: [batch, hkv, max_seq, d]."""

@@ -95,3 +95,78 @@ def test_decode_rejects_bad_arguments(dev, pkg):
         dev.attention_decode(capi.F32, 1, 4, 4, 8, 8, 80, 16, 16, 16, 16)      # head_dim
     with pytest.raises(pkg.hal.HalError):
         dev.attention_decode(capi.F32, 1, 4, 4, 8, 8, 64, 0, 16, 16, 16)       # null q
+
+
+def rope_tol(x, last_pos):
+    """f32 pow / sin / cos differ between libraries by a few ulp; an ulp of the angle is worth |angle| * 6e-8 of
+    the rotated values, so the bound grows with the position."""
+    return (1e-6 + 4e-7 * last_pos) * float(np.abs(x).max())
+
+
+@pytest.mark.parametrize("b,s,h,d,start,theta", [(1, 1, 1, 2, 0, 10000.0), (2, 1, 8, 128, 777, 10000.0), (1, 37, 5, 64, 3, 10000.0),
+                                                   (2, 300, 4, 128, 1000, 500000.0), (1, 4, 3, 6, 0, 100.0)])
+def test_rope_f32_matches_oracle(dev, pkg, oracle, b, s, h, d, start, theta):
+    capi = pkg.capi
+    x = util.gen_normal(capi, (b, s, h, d), 901)
+    xd = util.dev_tensor(torch, x)
+    dev.rope(capi.F32, b, s, h, d, start, theta, xd.data_ptr(), stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    got = xd.cpu().numpy()
+    tol = rope_tol(x, start + s)
+    assert np.abs(got - oracle.rope_f32(x, start, theta)).max() <= tol
+    assert np.abs(got - oracle.rope_f32(x, start, theta, f64_acc=True)).max() <= tol
+    # rotations keep the norm of every pair whatever the angle
+    assert np.abs((got[..., 0::2] ** 2 + got[..., 1::2] ** 2) - (x[..., 0::2] ** 2 + x[..., 1::2] ** 2)).max() <= 1e-5 * float((x ** 2).max() * 2)
+
+
+def test_rope_bf16(dev, pkg, oracle):
+    capi = pkg.capi
+    xb = util.to_bf16(capi, util.gen_normal(capi, (2, 9, 4, 128), 902))
+    xd = util.dev_tensor(torch, xb)
+    dev.rope(capi.BF16, 2, 9, 4, 128, 50, 10000.0, xd.data_ptr(), stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    got = oracle.bf16_to_f32(xd.cpu().numpy().view(np.uint16))
+    ref = oracle.rope_f32(oracle.bf16_to_f32(xb), 50, 10000.0, f64_acc=True)
+    util.assert_16bit_close(oracle, got, ref)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("b,s,h,d,start,max_seq", [(1, 1, 1, 8, 0, 1), (2, 1, 8, 128, 41, 64), (2, 33, 4, 64, 7, 40), (1, 5, 3, 6, 2, 9)])
+def test_kv_cache_update_is_exact(dev, pkg, oracle, dt, b, s, h, d, start, max_seq):
+    capi = pkg.capi
+    src = util.gen_normal(capi, (b, s, h, d), 903)
+    cache = util.gen_normal(capi, (b, h, max_seq, d), 904)
+    code = capi.F32
+    if dt == "bf16":
+        src, cache, code = util.to_bf16(capi, src), util.to_bf16(capi, cache), capi.BF16
+    sd, cd = util.dev_tensor(torch, src), util.dev_tensor(torch, cache)
+    dev.kv_cache_update(code, b, s, h, d, start, max_seq, sd.data_ptr(), cd.data_ptr(), stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    got = cd.cpu().numpy().view(src.dtype)
+    assert np.array_equal(got, oracle.kv_cache_update(src, cache, start))
+    with pytest.raises(pkg.hal.HalError):
+        dev.kv_cache_update(code, b, s, h, d, max_seq, max_seq, sd.data_ptr(), cd.data_ptr())  # would write past the cache
+
+
+def test_decode_step_chain(dev, pkg, oracle):
+    """rope(q), rope(k), append k and v to the caches, attend: one decode step through the C ABI against the same
+    chain in the oracle."""
+    capi = pkg.capi
+    b, hq, hkv, d, pos, max_seq, theta = 2, 8, 2, 128, 300, 512, 10000.0
+    q = util.gen_normal(capi, (b, 1, hq, d), 911)
+    k_new, v_new = util.gen_normal(capi, (b, 1, hkv, d), 912), util.gen_normal(capi, (b, 1, hkv, d), 913)
+    kc, vc = util.gen_normal(capi, (b, hkv, max_seq, d), 914), util.gen_normal(capi, (b, hkv, max_seq, d), 915)
+    qd, knd, vnd, kcd, vcd = (util.dev_tensor(torch, t) for t in (q, k_new, v_new, kc, vc))
+    od = torch.empty(b, hq, d, device="cuda:0")
+    s = util.cur_stream(torch)
+    dev.rope(capi.F32, b, 1, hq, d, pos, theta, qd.data_ptr(), stream=s)
+    dev.rope(capi.F32, b, 1, hkv, d, pos, theta, knd.data_ptr(), stream=s)
+    dev.kv_cache_update(capi.F32, b, 1, hkv, d, pos, max_seq, knd.data_ptr(), kcd.data_ptr(), stream=s)
+    dev.kv_cache_update(capi.F32, b, 1, hkv, d, pos, max_seq, vnd.data_ptr(), vcd.data_ptr(), stream=s)
+    dev.attention_decode(capi.F32, b, hq, hkv, pos + 1, max_seq, d, qd.data_ptr(), kcd.data_ptr(), vcd.data_ptr(), od.data_ptr(), stream=s)
+    torch.cuda.synchronize()
+    qr, kr = oracle.rope_f32(q, pos, theta, f64_acc=True), oracle.rope_f32(k_new, pos, theta, f64_acc=True)
+    ref = oracle.attention_decode_f32(qr[:, 0], oracle.kv_cache_update(kr, kc, pos), oracle.kv_cache_update(v_new, vc, pos), pos + 1,
+                                      f64_acc=True)
+    assert np.abs(od.cpu().numpy() - ref).max() <= 2e-4 * float(np.abs(ref).max())  # rope at position 300 in f32 dominates
+    assert dev.status() == 0

@@ -167,3 +167,24 @@ def test_attention_decode_matches_golden_and_known_answers(oracle):
     o32, o16 = oracle.attention_decode_bf16(qb, kb, vb, 12)
     assert np.abs(o32 - onp.attention_decode(*(onp.bf16_bits_to_f32(t) for t in (qb, kb, vb)), 12)).max() <= 2e-6
     assert np.array_equal(o16, onp.f32_to_bf16_bits(o32))
+
+
+def test_rope_and_kv_cache_update(oracle):
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((2, 6, 3, 32)).astype(np.float32)
+    ref = onp.rope(x, 11, 10000.0)
+    assert np.abs(oracle.rope_f32(x, 11, 10000.0) - ref).max() <= 5e-6   # f32 pow / cos / sin at angles up to 16
+    assert np.abs(oracle.rope_f32(x, 11, 10000.0, f64_acc=True) - ref).max() <= 3e-7
+    # position 0 is the identity; a rotation keeps the norm of every pair
+    assert np.array_equal(oracle.rope_f32(x[:, :1], 0, 10000.0), x[:, :1])
+    y = oracle.rope_f32(x, 100, 500000.0)
+    assert np.abs((y[..., 0::2] ** 2 + y[..., 1::2] ** 2) - (x[..., 0::2] ** 2 + x[..., 1::2] ** 2)).max() <= 1e-5
+    # decode form = prefill form of one token at that position
+    assert np.array_equal(oracle.rope_f32(x, 11, 10000.0)[:, 4:5], oracle.rope_f32(x[:, 4:5], 15, 10000.0))
+    src = rng.standard_normal((2, 3, 4, 8)).astype(np.float32)
+    cache = rng.standard_normal((2, 4, 10, 8)).astype(np.float32)
+    out = oracle.kv_cache_update(src, cache, 5)
+    assert np.array_equal(out[:, :, 5:8], src.transpose(0, 2, 1, 3))
+    assert np.array_equal(out[:, :, :5], cache[:, :, :5]) and np.array_equal(out[:, :, 8:], cache[:, :, 8:])
+    s16 = oracle.f32_to_bf16(src)
+    assert np.array_equal(oracle.kv_cache_update(s16, np.zeros((2, 4, 10, 8), np.uint16), 0)[:, :, :3], s16.transpose(0, 2, 1, 3))

@@ -43,6 +43,16 @@ class SiluMulDesc(C.Structure):
 REDUCE_SUM, REDUCE_MAX = 0, 1
 
 
+class RopeDesc(C.Structure):
+    _fields_ = [("dtype", c_i32), ("batch", c_i32), ("seq_len", c_i32), ("heads", c_i32), ("head_dim", c_i32),
+                ("start_pos", c_i32), ("theta", C.c_float)]
+
+
+class KvCacheUpdateDesc(C.Structure):
+    _fields_ = [("dtype", c_i32), ("batch", c_i32), ("seq_len", c_i32), ("heads", c_i32), ("head_dim", c_i32),
+                ("start_pos", c_i32), ("max_seq", c_i32)]
+
+
 class AttentionDecodeDesc(C.Structure):
     _fields_ = [("dtype", c_i32), ("batch", c_i32), ("heads_q", c_i32), ("heads_kv", c_i32), ("seq_len", c_i32),
                 ("max_seq", c_i32), ("head_dim", c_i32)]
@@ -92,6 +102,8 @@ PROTOTYPES = {
     "tsm100_gemm": (c_i32, [c_vp, P(GemmDesc), c_vp, c_vp, c_vp, c_vp]),
     "tsm100_gemm_static_scratch": (c_i32, [P(GemmDesc), c_vp, c_vp, c_vp, c_vp, P(c_u32)]),
     "tsm100_attention": (c_i32, [c_vp, P(AttentionDesc), c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "tsm100_rope": (c_i32, [c_vp, P(RopeDesc), c_vp, c_vp]),
+    "tsm100_kv_cache_update": (c_i32, [c_vp, P(KvCacheUpdateDesc), c_vp, c_vp, c_vp]),
     "tsm100_attention_decode": (c_i32, [c_vp, P(AttentionDecodeDesc), c_vp, c_vp, c_vp, c_vp, c_vp]),
     "tsm100_softmax_host": (c_i32, [c_vp, P(SoftmaxDesc), c_vp, c_vp]),
     "tsm100_gemm_host": (c_i32, [c_vp, P(GemmDesc), c_vp, c_vp, c_vp]),

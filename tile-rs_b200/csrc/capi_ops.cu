@@ -85,6 +85,21 @@ int32_t tsm100_silu_mul(tsm100_device_t dev, const tsm100_silu_mul_desc* desc, c
   return finish(ops::silu_mul(&err, desc, gate, up, y, stream), err);
 }
 
+int32_t tsm100_rope(tsm100_device_t dev, const tsm100_rope_desc* desc, void* x, void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::rope(&err, desc, x, stream), err);
+}
+
+int32_t tsm100_kv_cache_update(tsm100_device_t dev, const tsm100_kv_cache_update_desc* desc, const void* src, void* cache,
+                               void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::kv_cache_update(&err, desc, src, cache, stream), err);
+}
+
 int32_t tsm100_attention_decode(tsm100_device_t dev, const tsm100_attention_decode_desc* desc, const void* q,
                                 const void* k_cache, const void* v_cache, void* o, void* stream) {
   int32_t st = use_device(dev);

@@ -309,6 +309,67 @@ inline int32_t silu_mul(std::string* err, const tsm100_silu_mul_desc* d, const v
 }
 
 // ---------------------------------------------------------------------------
+// RoPE and KV-cache update
+// ---------------------------------------------------------------------------
+inline int32_t rope(std::string* err, const tsm100_rope_desc* d, void* x, void* stream) {
+  if (!d) return op_fail(err, TSM100_ERR_INVALID, "rope: null descriptor");
+  if (!dtype_valid(d->dtype)) return op_fail(err, TSM100_ERR_INVALID, "rope: unknown dtype");
+  if (d->batch < 0 || d->seq_len < 0 || d->heads < 0 || d->head_dim < 0 || d->start_pos < 0 || d->head_dim % 2 != 0)
+    return op_fail(err, TSM100_ERR_INVALID, "rope: bad shape (head_dim must be even, nothing negative)");
+  if (!(d->theta > 0.f)) return op_fail(err, TSM100_ERR_INVALID, "rope: theta must be positive");
+  const int64_t tokens = static_cast<int64_t>(d->batch) * d->seq_len;
+  if (tokens == 0 || d->heads == 0 || d->head_dim == 0) return TSM100_OK;
+  if (!x) return op_fail(err, TSM100_ERR_INVALID, "rope: null buffer");
+  int sms = 0;
+  int32_t st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  const int64_t n = tokens * (d->head_dim / 2);
+  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, static_cast<int64_t>(sms) * 8)));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (d->dtype == TSM100_F32)
+    rowops::rope_kernel<float><<<grid, 256, 0, s>>>(static_cast<float*>(x), tokens, d->seq_len, d->heads, d->head_dim, d->start_pos, d->theta);
+  else if (d->dtype == TSM100_BF16)
+    rowops::rope_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(x), tokens, d->seq_len, d->heads, d->head_dim,
+                                                            d->start_pos, d->theta);
+  else
+    rowops::rope_kernel<__half><<<grid, 256, 0, s>>>(static_cast<__half*>(x), tokens, d->seq_len, d->heads, d->head_dim, d->start_pos, d->theta);
+  return cuda_ok(err, cudaGetLastError(), "rope_kernel launch");
+}
+
+template <typename T>
+inline cudaError_t kv_cache_update_typed(const tsm100_kv_cache_update_desc* d, const void* src, void* cache, int sms, cudaStream_t s) {
+  constexpr int PV = softmax::Elem<T>::kPerVec;
+  const bool vec = d->head_dim % PV == 0 && aligned16(src) && aligned16(cache);
+  const int64_t n = static_cast<int64_t>(d->batch) * d->seq_len * d->heads * (vec ? d->head_dim / PV : d->head_dim);
+  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, static_cast<int64_t>(sms) * 8)));
+  if (vec)
+    rowops::kv_cache_update_kernel<T, PV><<<grid, 256, 0, s>>>(static_cast<const T*>(src), static_cast<T*>(cache), d->batch, d->seq_len,
+                                                               d->heads, d->head_dim, d->start_pos, d->max_seq);
+  else
+    rowops::kv_cache_update_kernel<T, 1><<<grid, 256, 0, s>>>(static_cast<const T*>(src), static_cast<T*>(cache), d->batch, d->seq_len,
+                                                              d->heads, d->head_dim, d->start_pos, d->max_seq);
+  return cudaGetLastError();
+}
+
+inline int32_t kv_cache_update(std::string* err, const tsm100_kv_cache_update_desc* d, const void* src, void* cache, void* stream) {
+  if (!d) return op_fail(err, TSM100_ERR_INVALID, "kv_cache_update: null descriptor");
+  if (!dtype_valid(d->dtype)) return op_fail(err, TSM100_ERR_INVALID, "kv_cache_update: unknown dtype");
+  if (d->batch < 0 || d->seq_len < 0 || d->heads < 0 || d->head_dim < 0 || d->start_pos < 0 ||
+      static_cast<int64_t>(d->start_pos) + d->seq_len > d->max_seq)
+    return op_fail(err, TSM100_ERR_INVALID, "kv_cache_update: bad shape (need start_pos + seq_len <= max_seq, nothing negative)");
+  if (static_cast<int64_t>(d->batch) * d->seq_len * d->heads * d->head_dim == 0) return TSM100_OK;
+  if (!src || !cache) return op_fail(err, TSM100_ERR_INVALID, "kv_cache_update: null buffer");
+  int sms = 0;
+  int32_t st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = d->dtype == TSM100_F32    ? kv_cache_update_typed<float>(d, src, cache, sms, s)
+                  : d->dtype == TSM100_BF16 ? kv_cache_update_typed<__nv_bfloat16>(d, src, cache, sms, s)
+                                            : kv_cache_update_typed<__half>(d, src, cache, sms, s);
+  return cuda_ok(err, e, "kv_cache_update_kernel launch");
+}
+
+// ---------------------------------------------------------------------------
 // GEMM
 // ---------------------------------------------------------------------------
 template <typename InT, typename OutT>

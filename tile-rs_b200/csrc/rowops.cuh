@@ -212,3 +212,69 @@ silu_mul_scalar_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* 
 
 }  // namespace rowops
 }  // namespace tsm100
+
+// ===========================================================================
+// The two steps before decode / prefill attention in a transformer layer.
+//
+//   rope             x[b, s, h, 2i], x[b, s, h, 2i+1] rotated by angle (start_pos + s) * theta^(-2i / d), in place;
+//                    x is [batch][seq_len][heads][d] (token-major).
+//                    __tile_rope_inplace_f32 (seq_len = 1) and __tile_rope_prefill_f32
+//                    (crates/tile_std/src/tile.rs:2113-2115, :2128-2129); arithmetic of the Metal
+//                    lowering (crates/rustc_codegen_tile/src/mlir_to_msl.rs:10707-10728, :10883-10908):
+//                    freq = 1 / pow(theta, 2 i / d), angle = float(pos) * freq, f32 cos and sin.
+//   kv_cache_update  cache[b, h, start_pos + s, :] = src[b, s, h, :]; cache is [batch][heads][max_seq][d].
+//                    __tile_kv_cache_update_f32 and __tile_kv_cache_update_prefill_f32 (tile.rs:2117-2119,
+//                    :2131-2132; mlir_to_msl.rs:10730-10741, :10910-10926).
+// position, start_pos, theta, max_seq and the head count are run-time constants of those kernels.
+// ===========================================================================
+namespace tsm100 {
+namespace rowops {
+
+// one thread per (batch, token, pair index): the angle is computed once and used for every head
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kernel(T* __restrict__ x, int64_t tokens, int32_t seq_len, int32_t heads, int32_t d, int32_t start_pos, float theta) {
+  const int half = d / 2;
+  const int64_t n = tokens * half;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < n;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t tok = idx / half;
+    const int i = static_cast<int>(idx % half);
+    const int pos = start_pos + static_cast<int>(tok % seq_len);
+    const float freq = 1.0f / powf(theta, 2.0f * static_cast<float>(i) / static_cast<float>(d));
+    const float angle = static_cast<float>(pos) * freq;
+    float s, c;
+    sincosf(angle, &s, &c);
+    T* p = x + tok * heads * d + 2 * i;
+    for (int h = 0; h < heads; ++h, p += d) {
+      const float x0 = Elem<T>::load1(p), x1 = Elem<T>::load1(p + 1);
+      Elem<T>::store1(p, x0 * c - x1 * s);
+      Elem<T>::store1(p + 1, x0 * s + x1 * c);
+    }
+  }
+}
+
+// VEC = elements per access (16 bytes when rows allow it, else 1)
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+kv_cache_update_kernel(const T* __restrict__ src, T* __restrict__ cache, int64_t batch, int32_t seq_len, int32_t heads,
+                       int32_t d, int32_t start_pos, int32_t max_seq) {
+  const int dv = d / VEC;
+  const int64_t n = batch * seq_len * heads * dv;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < n;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int dd = static_cast<int>(idx % dv) * VEC;
+    int64_t r = idx / dv;
+    const int h = static_cast<int>(r % heads);
+    r /= heads;
+    const int si = static_cast<int>(r % seq_len);
+    const int64_t b = r / seq_len;
+    const T* s = src + ((b * seq_len + si) * heads + h) * d + dd;
+    T* c = cache + ((b * heads + h) * max_seq + start_pos + si) * d + dd;
+    if (VEC == 1) *c = *s;
+    else *reinterpret_cast<Vec16*>(c) = *reinterpret_cast<const Vec16*>(s);
+  }
+}
+
+}  // namespace rowops
+}  // namespace tsm100

@@ -407,6 +407,18 @@ class CudaSm100Device:
         d = capi.AttentionDesc(dtype, int(causal), batch, heads_q, heads_kv, seq, head_dim)
         check(capi.lib().tsm100_attention(self._h, C.byref(d), q, k, v, o, stream or None))
 
+    def rope(self, dtype: int, batch: int, seq_len: int, heads: int, head_dim: int, start_pos: int, theta: float, x: int,
+             stream: int = 0) -> None:
+        """In-place rotary embedding of x [batch, seq_len, heads, head_dim] at positions start_pos .. start_pos + seq_len - 1."""
+        d = capi.RopeDesc(dtype, batch, seq_len, heads, head_dim, start_pos, theta)
+        check(capi.lib().tsm100_rope(self._h, C.byref(d), x, stream or None))
+
+    def kv_cache_update(self, dtype: int, batch: int, seq_len: int, heads: int, head_dim: int, start_pos: int, max_seq: int,
+                        src: int, cache: int, stream: int = 0) -> None:
+        """cache[b, h, start_pos + s] = src[b, s, h] for src [batch, seq_len, heads, d], cache [batch, heads, max_seq, d]."""
+        d = capi.KvCacheUpdateDesc(dtype, batch, seq_len, heads, head_dim, start_pos, max_seq)
+        check(capi.lib().tsm100_kv_cache_update(self._h, C.byref(d), src, cache, stream or None))
+
     def attention_decode(self, dtype: int, batch: int, heads_q: int, heads_kv: int, seq_len: int, max_seq: int, head_dim: int,
                          q: int, k_cache: int, v_cache: int, o: int, stream: int = 0) -> None:
         """One query token per head against the first ``seq_len`` positions of a [batch, heads_kv, max_seq, d] cache."""
