@@ -274,6 +274,24 @@ typedef struct {
 int32_t tsm100_kv_cache_update(tsm100_device_t dev, const tsm100_kv_cache_update_desc* desc, const void* src,
                                void* cache, void* stream);
 
+/* Prefill attention: seq_len new tokens, already appended to the KV cache behind start_pos earlier ones, attend
+ * causally: token s sees cache positions 0 .. start_pos + s.  q, o are token-major [seq_len][heads_q][head_dim],
+ * the caches [heads_kv][max_seq][head_dim], kv head = h / (heads_q / heads_kv).
+ * __tile_attention_prefill_f32 (tile.rs:2134-2136; wrapper :3062-3074); arithmetic of
+ * crates/rustc_codegen_tile/src/mlir_to_msl.rs:10928-11010 without that lowering's limit of 256 cache positions
+ * (its `threadgroup float scores[256]`).  head_dim 128 in 16 bit runs on tensor cores. */
+typedef struct {
+  int32_t dtype;
+  int32_t heads_q;
+  int32_t heads_kv;
+  int32_t seq_len;
+  int32_t start_pos;
+  int32_t max_seq;
+  int32_t head_dim;
+} tsm100_attention_prefill_desc;
+int32_t tsm100_attention_prefill(tsm100_device_t dev, const tsm100_attention_prefill_desc* desc, const void* q,
+                                 const void* k_cache, const void* v_cache, void* o, void* stream);
+
 /* Single-token (decode) attention against a KV cache:
  *   o[b,h,:] = softmax_p(q[b,h,:] . K[b,g,p,:] / sqrt(d)) V[b,g,p,:],  p < seq_len,  g = h / (heads_q / heads_kv).
  * __tile_attention_decode_f32 (tile.rs:2120-2124; wrapper :3004-3018): q, o [heads_q][d], caches

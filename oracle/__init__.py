@@ -53,13 +53,14 @@ def lib() -> C.CDLL:
         h.orc_attention_decode_bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64]
         h.orc_rope_f32.argtypes = [_vp, _i64, _i64, _i64, _i64, _i64, C.c_float, C.c_int]
         h.orc_kv_cache_update.argtypes = [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64]
+        h.orc_attention_prefill_f32.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, C.c_int]
         h.orc_compare_f32.argtypes = [_vp, _vp, _i64, C.c_double, _vp]
         h.orc_bf16_to_f32.argtypes = [_vp, _vp, _i64]
         h.orc_f32_to_bf16.argtypes = [_vp, _vp, _i64]
         for name in ("orc_gemm_f32", "orc_gemm_f64acc", "orc_gemm_bf16", "orc_softmax_f32", "orc_softmax_f64acc",
                      "orc_softmax_bf16", "orc_attention_f32", "orc_attention_bf16", "orc_compare_f32",
                      "orc_bf16_to_f32", "orc_f32_to_bf16", "orc_rms_norm_f32", "orc_rms_norm_bf16", "orc_reduce_f32",
-                     "orc_silu_mul_f32", "orc_silu_mul_bf16", "orc_attention_decode_f32", "orc_attention_decode_bf16", "orc_rope_f32", "orc_kv_cache_update"):
+                     "orc_silu_mul_f32", "orc_silu_mul_bf16", "orc_attention_decode_f32", "orc_attention_decode_bf16", "orc_rope_f32", "orc_kv_cache_update", "orc_attention_prefill_f32"):
             getattr(h, name).restype = None
         _LIB = h
     return _LIB
@@ -186,6 +187,18 @@ def kv_cache_update(src: np.ndarray, cache: np.ndarray, start_pos: int) -> np.nd
     b, s, h, d = src.shape
     lib().orc_kv_cache_update(_p(src), _p(out), src.dtype.itemsize, b, s, h, d, start_pos, out.shape[2])
     return out
+
+
+def attention_prefill_f32(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, start_pos: int, f64_acc: bool = False) -> np.ndarray:
+    """q: [seq_len, hq, d] (token-major); caches: [hkv, max_seq, d]; token s sees positions 0 .. start_pos + s."""
+    q = np.ascontiguousarray(q, np.float32)
+    k_cache = np.ascontiguousarray(k_cache, np.float32)
+    v_cache = np.ascontiguousarray(v_cache, np.float32)
+    s, hq, d = q.shape
+    hkv, max_seq, _ = k_cache.shape
+    o = np.empty_like(q)
+    lib().orc_attention_prefill_f32(_p(q), _p(k_cache), _p(v_cache), _p(o), hq, hkv, s, start_pos, max_seq, d, int(f64_acc))
+    return o
 
 
 def attention_decode_f32(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, seq_len: int, f64_acc: bool = False) -> np.ndarray:

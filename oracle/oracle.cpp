@@ -577,4 +577,62 @@ void orc_kv_cache_update(const void* src, void* cache, int64_t elem_bytes, int64
                     sp + (((b * seq_len + s) * heads + h) * d) * elem_bytes, d * elem_bytes);
 }
 
+// __tile_attention_prefill_f32 (crates/rustc_codegen_tile/src/mlir_to_msl.rs:10928-11010, without its cap of 256
+// cache positions): q, o token-major [seq_len][hq][d], caches [hkv][max_seq][d]; the token at index s sits at
+// position start_pos + s and sees cache positions 0 .. start_pos + s; scale rsqrt(d); the five phases in f32
+// (f64acc != 0: in double).
+void orc_attention_prefill_f32(const float* q, const float* kc, const float* vc, float* o, int64_t hq, int64_t hkv,
+                               int64_t seq_len, int64_t start_pos, int64_t max_seq, int64_t d, int f64acc) {
+  const int64_t group = hq / hkv;
+#pragma omp parallel for collapse(2) schedule(dynamic, 4)
+  for (int64_t s = 0; s < seq_len; ++s)
+    for (int64_t h = 0; h < hq; ++h) {
+      const int64_t n = start_pos + s + 1;  // visible positions
+      const float* qh = q + (s * hq + h) * d;
+      const float* kh = kc + (h / group) * max_seq * d;
+      const float* vh = vc + (h / group) * max_seq * d;
+      float* oh = o + (s * hq + h) * d;
+      if (f64acc) {
+        std::vector<double> sc(n);
+        const double scale = 1.0 / std::sqrt(static_cast<double>(d));
+        double mx = -std::numeric_limits<double>::infinity(), sum = 0;
+        for (int64_t p = 0; p < n; ++p) {
+          double dot = 0;
+          for (int64_t j = 0; j < d; ++j) dot += static_cast<double>(qh[j]) * kh[p * d + j];
+          sc[p] = dot * scale;
+          mx = sc[p] > mx ? sc[p] : mx;
+        }
+        for (int64_t p = 0; p < n; ++p) {
+          sc[p] = std::exp(sc[p] - mx);
+          sum += sc[p];
+        }
+        for (int64_t j = 0; j < d; ++j) {
+          double acc = 0;
+          for (int64_t p = 0; p < n; ++p) acc += sc[p] / sum * vh[p * d + j];
+          oh[j] = static_cast<float>(acc);
+        }
+      } else {
+        std::vector<float> sc(n);
+        const float scale = 1.0f / std::sqrt(static_cast<float>(d));
+        float mx = -std::numeric_limits<float>::infinity(), sum = 0.f;
+        for (int64_t p = 0; p < n; ++p) {
+          float dot = 0.f;
+          for (int64_t j = 0; j < d; ++j) dot += qh[j] * kh[p * d + j];
+          sc[p] = dot * scale;
+          mx = sc[p] > mx ? sc[p] : mx;
+        }
+        for (int64_t p = 0; p < n; ++p) {
+          sc[p] = expf(sc[p] - mx);
+          sum += sc[p];
+        }
+        const float inv = 1.0f / sum;
+        for (int64_t j = 0; j < d; ++j) {
+          float acc = 0.f;
+          for (int64_t p = 0; p < n; ++p) acc += sc[p] * inv * vh[p * d + j];
+          oh[j] = acc;
+        }
+      }
+    }
+}
+
 }  // extern "C"

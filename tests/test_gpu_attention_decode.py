@@ -170,3 +170,64 @@ def test_decode_step_chain(dev, pkg, oracle):
                                       f64_acc=True)
     assert np.abs(od.cpu().numpy() - ref).max() <= 2e-4 * float(np.abs(ref).max())  # rope at position 300 in f32 dominates
     assert dev.status() == 0
+
+
+def run_prefill(dev, capi, q, k, v, start, dtype):
+    s, hq, d = q.shape
+    hkv, max_seq, _ = k.shape
+    qd, kd, vd = (util.dev_tensor(torch, t) for t in (q, k, v))
+    od = torch.full_like(qd, 12345 if qd.dtype == torch.int16 else float("nan"))
+    dev.attention_prefill(dtype, hq, hkv, s, start, max_seq, d, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), od.data_ptr(),
+                          stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    assert dev.status() == 0
+    return od.cpu().numpy()
+
+
+@pytest.mark.parametrize("s,hq,hkv,d,start,max_seq", [(1, 1, 1, 64, 0, 4), (7, 4, 2, 64, 5, 16), (130, 6, 3, 128, 0, 130),
+                                                        (33, 8, 2, 96, 100, 200), (256, 2, 2, 128, 300, 600)])
+def test_prefill_f32_matches_oracle(dev, pkg, oracle, s, hq, hkv, d, start, max_seq):
+    capi = pkg.capi
+    q = util.gen_normal(capi, (s, hq, d), 921)
+    k, v = util.gen_normal(capi, (hkv, max_seq, d), 922), util.gen_normal(capi, (hkv, max_seq, d), 923)
+    k[:, start + s:], v[:, start + s:] = np.nan, np.nan  # beyond the filled part: must not be read
+    o = run_prefill(dev, capi, q, k, v, start, capi.F32)
+    kz, vz = np.nan_to_num(k), np.nan_to_num(v)
+    for ref in (oracle.attention_prefill_f32(q, kz, vz, start), oracle.attention_prefill_f32(q, kz, vz, start, f64_acc=True)):
+        m = oracle.compare(o, ref)
+        assert m["rel_max"] <= util.F32_REL and m["rel_fro"] <= util.F32_REL, m
+
+
+# tensor-core path: offsets that are and are not multiples of the 128-key step, ragged lengths, grouped heads
+@pytest.mark.parametrize("s,hq,hkv,start,max_seq", [(1, 2, 2, 0, 8), (256, 4, 2, 0, 256), (200, 8, 2, 100, 512), (384, 2, 1, 128, 600),
+                                                      (130, 4, 4, 1000, 1200), (1024, 4, 1, 77, 2048)])
+def test_prefill_bf16_tensor_core(dev, pkg, oracle, s, hq, hkv, start, max_seq):
+    capi = pkg.capi
+    d = 128
+    q = util.to_bf16(capi, util.gen_normal(capi, (s, hq, d), 921))
+    k = util.to_bf16(capi, util.gen_normal(capi, (hkv, max_seq, d), 922))
+    v = util.to_bf16(capi, util.gen_normal(capi, (hkv, max_seq, d), 923))
+    o = run_prefill(dev, capi, q, k, v, start, capi.BF16).view(np.uint16)
+    f = oracle.bf16_to_f32
+    ref = oracle.attention_prefill_f32(f(q), f(k), f(v), start)
+    util.assert_16bit_close(oracle, f(o), ref)
+
+
+def test_prefill_in_chunks_equals_one_shot_and_plain_causal(dev, pkg, oracle):
+    """Size-independent properties at seq 2048: prefill from position 0 reproduces plain causal attention over the
+    same K / V, and prefilling the second half on top of the first gives the same rows."""
+    capi = pkg.capi
+    s, hq, hkv, d = 2048, 4, 2, 128
+    q = util.to_bf16(capi, util.gen_normal(capi, (s, hq, d), 931))
+    k = util.to_bf16(capi, util.gen_normal(capi, (hkv, s, d), 932))
+    v = util.to_bf16(capi, util.gen_normal(capi, (hkv, s, d), 933))
+    one = run_prefill(dev, capi, q, k, v, 0, capi.BF16)
+    second = run_prefill(dev, capi, np.ascontiguousarray(q[s // 2:]), k, v, s // 2, capi.BF16)
+    assert np.array_equal(second, one[s // 2:])  # same tiles, same arithmetic
+    qh = util.dev_tensor(torch, np.ascontiguousarray(q.transpose(1, 0, 2))[None])
+    kd, vd = util.dev_tensor(torch, k[None]), util.dev_tensor(torch, v[None])
+    full = torch.empty_like(qh)
+    dev.attention(capi.BF16, 1, hq, hkv, s, d, qh.data_ptr(), kd.data_ptr(), vd.data_ptr(), full.data_ptr(), causal=True,
+                  stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    assert np.array_equal(full.cpu().numpy()[0].transpose(1, 0, 2), one)

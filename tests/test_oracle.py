@@ -188,3 +188,19 @@ def test_rope_and_kv_cache_update(oracle):
     assert np.array_equal(out[:, :, :5], cache[:, :, :5]) and np.array_equal(out[:, :, 8:], cache[:, :, 8:])
     s16 = oracle.f32_to_bf16(src)
     assert np.array_equal(oracle.kv_cache_update(s16, np.zeros((2, 4, 10, 8), np.uint16), 0)[:, :, :3], s16.transpose(0, 2, 1, 3))
+
+
+def test_attention_prefill_oracle(oracle):
+    rng = np.random.default_rng(9)
+    s, hq, hkv, d, start, max_seq = 7, 4, 2, 16, 5, 16
+    q = rng.standard_normal((s, hq, d)).astype(np.float32)
+    k, v = (rng.standard_normal((hkv, max_seq, d)).astype(np.float32) for _ in range(2))
+    o = oracle.attention_prefill_f32(q, k, v, start)
+    # token i of the prefill is a decode step against the first start + i + 1 positions
+    for i in range(s):
+        dec = oracle.attention_decode_f32(q[None, i], k[None], v[None], start + i + 1)
+        assert np.abs(o[i] - dec[0]).max() <= 1e-6
+    assert np.abs(oracle.attention_prefill_f32(q, k, v, start, f64_acc=True) - o).max() <= 2e-6
+    # start_pos 0 with the cache equal to K / V is plain causal attention in the other layout
+    full = oracle.attention_f32(np.ascontiguousarray(q.transpose(1, 0, 2))[None], k[None, :, :s], v[None, :, :s], True)
+    assert np.abs(oracle.attention_prefill_f32(q, k, v, 0) - full[0].transpose(1, 0, 2)).max() <= 1e-6

@@ -53,6 +53,11 @@ class KvCacheUpdateDesc(C.Structure):
                 ("start_pos", c_i32), ("max_seq", c_i32)]
 
 
+class AttentionPrefillDesc(C.Structure):
+    _fields_ = [("dtype", c_i32), ("heads_q", c_i32), ("heads_kv", c_i32), ("seq_len", c_i32), ("start_pos", c_i32),
+                ("max_seq", c_i32), ("head_dim", c_i32)]
+
+
 class AttentionDecodeDesc(C.Structure):
     _fields_ = [("dtype", c_i32), ("batch", c_i32), ("heads_q", c_i32), ("heads_kv", c_i32), ("seq_len", c_i32),
                 ("max_seq", c_i32), ("head_dim", c_i32)]
@@ -104,6 +109,7 @@ PROTOTYPES = {
     "tsm100_attention": (c_i32, [c_vp, P(AttentionDesc), c_vp, c_vp, c_vp, c_vp, c_vp]),
     "tsm100_rope": (c_i32, [c_vp, P(RopeDesc), c_vp, c_vp]),
     "tsm100_kv_cache_update": (c_i32, [c_vp, P(KvCacheUpdateDesc), c_vp, c_vp, c_vp]),
+    "tsm100_attention_prefill": (c_i32, [c_vp, P(AttentionPrefillDesc), c_vp, c_vp, c_vp, c_vp, c_vp]),
     "tsm100_attention_decode": (c_i32, [c_vp, P(AttentionDecodeDesc), c_vp, c_vp, c_vp, c_vp, c_vp]),
     "tsm100_softmax_host": (c_i32, [c_vp, P(SoftmaxDesc), c_vp, c_vp]),
     "tsm100_gemm_host": (c_i32, [c_vp, P(GemmDesc), c_vp, c_vp, c_vp]),

@@ -20,11 +20,16 @@
 namespace tsm100 {
 namespace attn_simt {
 
+// Strides in elements.  Plain attention: Q, O [batch*heads_q][seq][d], K, V [batch*heads_kv][seq][d], q_offset 0.
+// Prefill against a KV cache: Q, O token-major [seq][heads_q][d], K, V [heads_kv][max_seq][d] of which seq_kv
+// positions are filled, query row i sits at position q_offset + i.
 struct Params {
-  int32_t seq, head_dim;
+  int32_t seq, head_dim;       // query rows per head
   int32_t heads_q, heads_kv, batch;
   int32_t causal;
   float scale;
+  int32_t seq_kv, q_offset;
+  int64_t q_row_stride, q_head_stride, kv_head_stride, o_row_stride, o_head_stride;
 };
 
 constexpr int kWarps = 4;
@@ -46,9 +51,9 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   const int b = static_cast<int>(bh / p.heads_q), h = static_cast<int>(bh % p.heads_q);
   const int64_t kvh = static_cast<int64_t>(b) * p.heads_kv + h / (p.heads_q / p.heads_kv);
   const int d = p.head_dim;
-  const T* qi = q + (bh * p.seq + i) * d;
-  const T* kb = k + kvh * p.seq * d;
-  const T* vb = v + kvh * p.seq * d;
+  const T* qi = q + bh * p.q_head_stride + i * p.q_row_stride;
+  const T* kb = k + kvh * p.kv_head_stride;
+  const T* vb = v + kvh * p.kv_head_stride;
 
   for (int c = lane; c < d; c += 32) sq[warp][c] = to_f32(qi[c]);
   __syncwarp();
@@ -57,7 +62,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
 #pragma unroll
   for (int t = 0; t < kMaxD / 32; ++t) acc[t] = 0.f;
   float m = -INFINITY, l = 0.f;
-  const int lim = p.causal ? (i + 1) : p.seq;
+  const int lim = p.causal ? min(p.seq_kv, i + p.q_offset + 1) : p.seq_kv;
   for (int j0 = 0; j0 < lim; j0 += 32) {
     const int j = j0 + lane;
     float s = -INFINITY;
@@ -92,7 +97,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     }
   }
   const float inv = 1.0f / l;
-  T* oi = o + (bh * p.seq + i) * d;
+  T* oi = o + bh * p.o_head_stride + i * p.o_row_stride;
 #pragma unroll
   for (int t = 0; t < kMaxD / 32; ++t) {
     const int c = lane + 32 * t;

@@ -75,6 +75,10 @@ struct Params {
   int32_t q_blocks;        // ceil(seq / 256)
   float scale_log2;        // (1/sqrt(d)) * log2(e)
   uint32_t* status;
+  // prefill against a KV cache (kCache kernels only): query row i sits at position q_offset + i of seq_kv
+  // filled positions; O is token-major, row and head strides in elements
+  int32_t seq_kv, q_offset;
+  int64_t o_row_stride, o_head_stride;
 };
 
 #ifdef TSM100_TRACE
@@ -107,7 +111,10 @@ __device__ __forceinline__ float unpack16_hi(uint32_t w) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
 }
 
-template <bool kIsBf16>
+// kCache = false: plain attention, Q, O [batch*heads_q][seq][128], K, V [batch*heads_kv][seq][128] (the tensor
+// maps say so).  kCache = true: causal prefill against a KV cache - the tensor maps describe token-major Q and the
+// filled part of the caches, query rows are offset by q_offset, O is written with the strides of Params.
+template <bool kIsBf16, bool kCache = false>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, uint16_t* __restrict__ o, const Params p) {
@@ -131,10 +138,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int bh = kvh * group + hg;           // flattened (batch, query head)
   const int qb = p.causal ? (p.q_blocks - 1 - qb_raw) : qb_raw;
   const int q0 = qb * 2 * kBQ;
-  const int n_kv_all = (p.seq + kBKV - 1) / kBKV;
-  // number of KV steps each tile needs (causal: up to and including its diagonal step)
-  const int n_a = p.causal ? min(n_kv_all, q0 / kBKV + 1) : n_kv_all;
-  const int n_b = p.causal ? min(n_kv_all, q0 / kBKV + 2) : n_kv_all;
+  const int seq_kv = kCache ? p.seq_kv : p.seq;
+  const int q_off = kCache ? p.q_offset : 0;
+  const int n_kv_all = (seq_kv + kBKV - 1) / kBKV;
+  // number of KV steps each tile needs (causal: up to and including the step of its last row's own position)
+  const int n_a = p.causal ? min(n_kv_all, (q0 + kBQ - 1 + q_off) / kBKV + 1) : n_kv_all;
+  const int n_b = p.causal ? min(n_kv_all, (q0 + 2 * kBQ - 1 + q_off) / kBKV + 1) : n_kv_all;
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(&bars->q_full, 1);
@@ -303,7 +312,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int r = quad * 32 + lane;         // row inside the tile == TMEM lane
     const int n_g = g == 0 ? n_a : n_b;
     const int qrow = q0 + g * kBQ + r;
-    const int limit = p.causal ? min(qrow, p.seq - 1) : (p.seq - 1);  // last visible column
+    const int limit = p.causal ? min(qrow + q_off, seq_kv - 1) : (seq_kv - 1);  // last visible column
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t ts = tmem_s + g * 128 + lane_base;
     const uint32_t to = tmem_o + g * 128 + lane_base;
@@ -435,7 +444,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (__all_sync(0xffffffffu, ready)) {
         ptx::tcgen05_fence_after_thread_sync();
         const float inv = 1.0f / l;
-        uint16_t* orow = o + (static_cast<int64_t>(bh) * p.seq + qrow) * kD;
+        uint16_t* orow = kCache ? o + bh * p.o_head_stride + qrow * p.o_row_stride
+                                : o + (static_cast<int64_t>(bh) * p.seq + qrow) * kD;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t ov[32];

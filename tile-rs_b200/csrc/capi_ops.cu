@@ -124,6 +124,14 @@ int32_t tsm100_attention(tsm100_device_t dev, const tsm100_attention_desc* desc,
   return finish(ops::attention(&err, desc, q, k, v, o, dev->status, stream), err);
 }
 
+int32_t tsm100_attention_prefill(tsm100_device_t dev, const tsm100_attention_prefill_desc* desc, const void* q,
+                                 const void* k_cache, const void* v_cache, void* o, void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  std::string err;
+  return finish(ops::attention_prefill(&err, desc, q, k_cache, v_cache, o, dev->status, stream), err);
+}
+
 // ---------------------------------------------------------------------------
 // host-memory operators
 // ---------------------------------------------------------------------------

@@ -589,14 +589,91 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
 template <typename T>
 inline int32_t attention_simt_launch(std::string* err, const tsm100_attention_desc* d, const void* q, const void* k,
                                      const void* v, void* o, cudaStream_t s) {
+  const int64_t sd = static_cast<int64_t>(d->seq) * d->head_dim;
   attn_simt::Params p{d->seq, d->head_dim, d->heads_q, d->heads_kv, d->batch, d->causal,
-                      static_cast<float>(1.0 / std::sqrt(static_cast<double>(d->head_dim)))};
+                      static_cast<float>(1.0 / std::sqrt(static_cast<double>(d->head_dim))),
+                      d->seq, 0, d->head_dim, sd, sd, d->head_dim, sd};
   const int64_t rows = static_cast<int64_t>(d->batch) * d->heads_q * d->seq;
   const int64_t grid = (rows + attn_simt::kWarps - 1) / attn_simt::kWarps;
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many query rows for one launch");
   attn_simt::attention_simt_kernel<T><<<static_cast<unsigned>(grid), attn_simt::kWarps * 32, 0, s>>>(
       static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(o), p);
   return cuda_ok(err, cudaGetLastError(), "attention_simt launch");
+}
+
+// ---------------------------------------------------------------------------
+// prefill attention: seq_len new tokens against a KV cache that already holds them and start_pos earlier ones
+// ---------------------------------------------------------------------------
+template <typename T>
+inline int32_t attention_prefill_simt_launch(std::string* err, const tsm100_attention_prefill_desc* d, const void* q,
+                                             const void* k, const void* v, void* o, cudaStream_t s) {
+  const int64_t hd = static_cast<int64_t>(d->heads_q) * d->head_dim;
+  attn_simt::Params p{d->seq_len, d->head_dim, d->heads_q, d->heads_kv, 1, 1,
+                      static_cast<float>(1.0 / std::sqrt(static_cast<double>(d->head_dim))),
+                      d->start_pos + d->seq_len, d->start_pos, hd, d->head_dim,
+                      static_cast<int64_t>(d->max_seq) * d->head_dim, hd, d->head_dim};
+  const int64_t rows = static_cast<int64_t>(d->heads_q) * d->seq_len;
+  const int64_t grid = (rows + attn_simt::kWarps - 1) / attn_simt::kWarps;
+  if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: too many query rows for one launch");
+  attn_simt::attention_simt_kernel<T><<<static_cast<unsigned>(grid), attn_simt::kWarps * 32, 0, s>>>(
+      static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(o), p);
+  return cuda_ok(err, cudaGetLastError(), "attention_simt (prefill) launch");
+}
+
+template <bool kBf16>
+inline int32_t attention_prefill_tc_launch(std::string* err, const tsm100_attention_prefill_desc* d, const void* q, const void* k,
+                                           const void* v, void* o, uint32_t* status, cudaStream_t s) {
+  namespace at = attn;
+  CUtensorMap tq, tk, tv;
+  const uint64_t D = at::kD, hq = d->heads_q, hkv = d->heads_kv, kv_len = static_cast<uint64_t>(d->start_pos) + d->seq_len;
+  // token-major Q: row pitch heads_q * D, head pitch D; caches: row pitch D, head pitch max_seq * D, kv_len rows visible
+  int32_t st = make_tmap_16bit_3d(err, &tq, q, D, d->seq_len, hq, hq * D, D, 64, at::kBQ, kBf16);
+  if (st == TSM100_OK) st = make_tmap_16bit_3d(err, &tk, k, D, kv_len, hkv, D, static_cast<uint64_t>(d->max_seq) * D, 64, at::kBKV, kBf16);
+  if (st == TSM100_OK) st = make_tmap_16bit_3d(err, &tv, v, D, kv_len, hkv, D, static_cast<uint64_t>(d->max_seq) * D, 64, at::kBKV, kBf16);
+  if (st != TSM100_OK) return st;
+  at::Params p;
+  p.seq = d->seq_len;
+  p.heads_q = d->heads_q;
+  p.heads_kv = d->heads_kv;
+  p.batch = 1;
+  p.causal = 1;
+  p.q_blocks = (d->seq_len + 2 * at::kBQ - 1) / (2 * at::kBQ);
+  p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
+  p.status = status;
+  p.seq_kv = static_cast<int32_t>(kv_len);
+  p.q_offset = d->start_pos;
+  p.o_row_stride = static_cast<int64_t>(hq * D);
+  p.o_head_stride = static_cast<int64_t>(D);
+  const int64_t grid = static_cast<int64_t>(p.q_blocks) * d->heads_q;
+  if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: too many tiles for one launch");
+  auto kern = at::attention_fwd_kernel<kBf16, true>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, at::kSmemBytes);
+  if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_fwd_kernel, cache)");
+  kern<<<static_cast<unsigned>(grid), at::kThreads, at::kSmemBytes, s>>>(tq, tk, tv, static_cast<uint16_t*>(o), p);
+  return cuda_ok(err, cudaGetLastError(), "attention_fwd_kernel (prefill) launch");
+}
+
+inline int32_t attention_prefill(std::string* err, const tsm100_attention_prefill_desc* d, const void* q, const void* k,
+                                 const void* v, void* o, uint32_t* status, void* stream) {
+  if (!d || !q || !k || !v || !o) return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: null argument");
+  if (!dtype_valid(d->dtype)) return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: unknown dtype");
+  if (d->heads_q <= 0 || d->heads_kv <= 0 || d->seq_len < 0 || d->start_pos < 0 || d->head_dim <= 0 ||
+      static_cast<int64_t>(d->start_pos) + d->seq_len > d->max_seq)
+    return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: bad shape (need heads > 0 and start_pos + seq_len <= max_seq)");
+  if (d->heads_q % d->heads_kv != 0)
+    return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: heads_q must be a multiple of heads_kv");
+  if (d->head_dim > attn_simt::kMaxD) return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: head_dim > 256 unsupported");
+  if (d->seq_len == 0) return TSM100_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc_ok = d->dtype != TSM100_F32 && d->head_dim == attn::kD && status != nullptr && aligned16(q) && aligned16(k) &&
+                     aligned16(v) && aligned16(o);
+  if (tc_ok) {
+    if (d->dtype == TSM100_BF16) return attention_prefill_tc_launch<true>(err, d, q, k, v, o, status, s);
+    return attention_prefill_tc_launch<false>(err, d, q, k, v, o, status, s);
+  }
+  if (d->dtype == TSM100_F32) return attention_prefill_simt_launch<float>(err, d, q, k, v, o, s);
+  if (d->dtype == TSM100_BF16) return attention_prefill_simt_launch<__nv_bfloat16>(err, d, q, k, v, o, s);
+  return attention_prefill_simt_launch<__half>(err, d, q, k, v, o, s);
 }
 
 // ---------------------------------------------------------------------------
@@ -754,6 +831,9 @@ inline int32_t attention_tc_launch(std::string* err, const tsm100_attention_desc
   p.q_blocks = (d->seq + 2 * at::kBQ - 1) / (2 * at::kBQ);
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
   p.status = status;
+  p.seq_kv = d->seq;
+  p.q_offset = 0;
+  p.o_row_stride = p.o_head_stride = 0;
   const int64_t grid = static_cast<int64_t>(p.q_blocks) * nq;
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many tiles for one launch");
   auto kern = at::attention_fwd_kernel<kBf16>;

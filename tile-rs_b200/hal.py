@@ -419,6 +419,12 @@ class CudaSm100Device:
         d = capi.KvCacheUpdateDesc(dtype, batch, seq_len, heads, head_dim, start_pos, max_seq)
         check(capi.lib().tsm100_kv_cache_update(self._h, C.byref(d), src, cache, stream or None))
 
+    def attention_prefill(self, dtype: int, heads_q: int, heads_kv: int, seq_len: int, start_pos: int, max_seq: int, head_dim: int,
+                          q: int, k_cache: int, v_cache: int, o: int, stream: int = 0) -> None:
+        """Causal attention of seq_len new tokens (token-major q, o) against the first start_pos + seq_len cache positions."""
+        d = capi.AttentionPrefillDesc(dtype, heads_q, heads_kv, seq_len, start_pos, max_seq, head_dim)
+        check(capi.lib().tsm100_attention_prefill(self._h, C.byref(d), q, k_cache, v_cache, o, stream or None))
+
     def attention_decode(self, dtype: int, batch: int, heads_q: int, heads_kv: int, seq_len: int, max_seq: int, head_dim: int,
                          q: int, k_cache: int, v_cache: int, o: int, stream: int = 0) -> None:
         """One query token per head against the first ``seq_len`` positions of a [batch, heads_kv, max_seq, d] cache."""
