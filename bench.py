@@ -425,6 +425,33 @@ def run_ours(args):
     roof = roofline_for(wl, statistics.mean(per) / wl.launches_per_step, peaks)
     roof["traffic"] = NCU_TRAFFIC.get(wl.name)
 
+    # verification (untimed): a few rows of every rank's shard, gathered over NCCL when there are several
+    # ranks, against the CPU oracle on rank 0 - the one use of a collective, and not on the data path
+    verify = None
+    if isinstance(wl, SoftmaxWL) and not args.no_verify:
+        idx = torch.tensor(sorted({0, units // 2, units - 1}), device=ctx.tdev)
+        xs, ys = wl.x.view(units, -1)[idx].contiguous(), wl.y.view(units, -1)[idx].contiguous()
+        if world > 1:
+            gx = [torch.empty_like(xs) for _ in range(world)]
+            gy = [torch.empty_like(ys) for _ in range(world)]
+            dist.all_gather(gx, xs)
+            dist.all_gather(gy, ys)
+            xs, ys = torch.cat(gx), torch.cat(gy)
+        if rank == 0:
+            oracle = entry.load_oracle()
+            if wl.dtype == "f32":
+                ref = oracle.softmax_f32(xs.cpu().numpy(), f64_acc=True)
+                got = ys.cpu().numpy()
+                tol = 1e-5
+            else:
+                ref, _ = oracle.softmax_bf16(xs.view(torch.int16).cpu().numpy().view(np.uint16))
+                got = oracle.bf16_to_f32(ys.view(torch.int16).cpu().numpy().view(np.uint16))
+                tol = 2.0 ** -8
+            err = float(np.abs(got - ref).max() / np.abs(ref).max())
+            assert err <= tol, f"verification against the oracle failed: {err}"
+            verify = {"rows": int(xs.shape[0]), "ranks": world, "max_err_rel_to_max": err, "tolerance": tol,
+                      "against": "CPU oracle (float64-accumulating)" if wl.dtype == "f32" else "CPU oracle"}
+
     # end to end through the host-buffer C-ABI call (pinned host memory, copies inside the timed region)
     e2e = None
     if hasattr(wl, "e2e_prepare") and not args.no_e2e:
@@ -491,7 +518,7 @@ def run_ours(args):
                        "l2": "inputs larger than L2 (no flush needed)" if wl.work() > 300e6 else "inputs fit in L2",
                        "sharding": f"{wl.unit_name} split over ranks, no collective on the data path"},
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": args.steps * wl.launches_per_step, "clocks": clk.summary(), "workloads": extras,
+            "gpu_launches": args.steps * wl.launches_per_step, "clocks": clk.summary(), "verify": verify, "workloads": extras,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -543,6 +570,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="measure only the headline workload")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-verify", action="store_true", help="skip the sampled-rows check against the CPU oracle")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--units", type=int, default=0,
                     help="override the number of units (rows, problems, KV groups) per GPU: a reduced case for "
