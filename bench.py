@@ -365,6 +365,29 @@ def roofline_for(wl, ms_per_launch, peaks):
             "peak_source": peaks["source"] if wl.bound != "fp32" else "nominal FP32 FMA rate at max clock"}
 
 
+def sustained_run(ctx, wl, seconds, global_units, peaks, gpu_index):
+    """The tensor-bound kernels draw the board's full power: the short timed run above sees burst clocks, a
+    loop of a second or more runs under the power cap.  Launches back to back for `seconds`, timed on the
+    device, with the clock sampler running; the fraction is of the measured sustained GEMM peak."""
+    torch = _torch()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    chunks = []
+    with ClockSampler(gpu_index) as clk:
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < seconds:
+            e0.record(torch.cuda.current_stream())
+            for _ in range(20):
+                wl.step()
+            e1.record(torch.cuda.current_stream())
+            e1.synchronize()
+            chunks.append(e0.elapsed_time(e1) / 20)
+    ms = statistics.median(chunks[len(chunks) // 2:])  # the second half: after the clocks have come down
+    tf = global_units * wl.work_per_unit / (ms * 1e-3) / 1e12
+    return {"value": round(tf, 2), "unit": "TFLOP/s", "ms_per_step": round(ms, 4), "seconds": seconds,
+            "roofline_frac": round(tf / peaks["bf16_tflops_sustained"], 4), "roofline_peak": peaks["bf16_tflops_sustained"],
+            "clocks": clk.summary()}
+
+
 NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per full-size launch (profiles/*.md)
     "softmax_f32": 4 * (268.5e6 + 215.7e6),       # captured on a quarter of the rows, scaled by rows
     "softmax_bf16": 4 * (134.2e6 + 79.0e6),
@@ -499,6 +522,8 @@ def run_ours(args):
             extras[name] = {"value": round(gu * w2.work_per_unit / (ms * 1e-3) / sc, 2), "unit": "GB/s" if w2.bound == "hbm" else "TFLOP/s",
                             "ms_per_step": round(ms, 4), "ms_per_step_min": round(min(per2), 4), "ms_per_step_max": round(max(per2), 4), "dtype": w2.dtype, "roofline_frac": r2["frac"], "roofline_peak": r2["peak"],
                             "config": w2.describe()}
+            if w2.bound == "tensor" and args.sustained_seconds > 0:
+                extras[name]["sustained"] = sustained_run(ctx, w2, args.sustained_seconds, gu, peaks, local)
             del w2
             torch.cuda.empty_cache()
 
@@ -572,6 +597,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-verify", action="store_true", help="skip the sampled-rows check against the CPU oracle")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--sustained-seconds", type=float, default=1.5,
+                    help="per tensor-bound workload: also a back-to-back loop of this length under the power cap (0: skip)")
     ap.add_argument("--units", type=int, default=0,
                     help="override the number of units (rows, problems, KV groups) per GPU: a reduced case for "
                          "profiler captures, never a benchmark number")
