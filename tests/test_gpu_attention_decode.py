@@ -41,7 +41,9 @@ def test_decode_f32_matches_oracle(dev, pkg, oracle, b, hq, hkv, n, max_seq, d):
 
 
 @pytest.mark.parametrize("b,hq,hkv,n,max_seq,d", [(1, 1, 1, 5, 8, 64), (2, 8, 2, 300, 320, 128), (1, 32, 4, 2048, 2048, 128),
-                                                     (2, 5, 1, 777, 800, 64), (1, 8, 8, 9000, 9000, 128)])
+                                                     (2, 5, 1, 777, 800, 64), (1, 8, 8, 9000, 9000, 128),
+                                                     # few caches, long: eight-warp CTAs in clusters of 16 (ragged last range)
+                                                     (1, 16, 2, 8207, 8208, 128), (1, 4, 4, 8192, 8192, 64)])
 def test_decode_bf16_matches_oracle(dev, pkg, oracle, b, hq, hkv, n, max_seq, d):
     capi = pkg.capi
     q = util.to_bf16(capi, util.gen_normal(capi, (b, hq, d), 801))

@@ -34,7 +34,63 @@ template <typename T, int D>
 constexpr int lanes_per_pos() { return (D / 16) % softmax::Elem<T>::kPerVec == 0 ? 16 : 8; }
 template <typename T, int D>
 constexpr int slots() { return kWarps * (32 / lanes_per_pos<T, D>()); }  // (warp, lane group) pairs, each with its own running state
-constexpr int kMaxSplits = 8;
+constexpr int kMaxSplits = 8;     // portable cluster size
+constexpr int kMaxSplitsWide = 16;  // non-portable size, used for a handful of sequences when the GPU can place such clusters
+
+// Merge of the per-CTA records of a cluster into the output, through distributed shared memory.
+// `mine` is this CTA's record [ROWS][D + 2] (O, running max, sum), at the same shared-memory offset in
+// every CTA; `scratch` (>= (3 * kMaxSplitsWide + 1) * ROWS floats, no longer in use) receives the
+// per-(row, rank) weights.  Every CTA merges its share of the ROWS x D outputs, all its remote loads in
+// flight together; ranks are added in rank order, so the result does not depend on timing.  The caller
+// brackets the call with cluster barriers.  seq_len == 0: no position contributes; 0 / 0 = NaN, as the
+// five phases of the reference give.
+template <typename T, int ROWS, int D, int THREADS>
+__device__ __forceinline__ void cluster_merge(const float* mine, float* scratch, uint32_t rank, uint32_t splits,
+                                              int rows_valid, T* __restrict__ o_rows) {
+  constexpr int REC = D + 2;
+  float* m_all = scratch;                              // [ROWS][kMaxSplitsWide] running maxima of the ranks
+  float* w_all = scratch + ROWS * kMaxSplitsWide;      // ... their weights 2^(m_r - M)
+  float* l_all = scratch + 2 * ROWS * kMaxSplitsWide;  // ... their sums
+  float* l_row = scratch + 3 * ROWS * kMaxSplitsWide;  // [ROWS] merged sums
+  const int tid = threadIdx.x;
+  const uint32_t mine_addr = ptx::smem_u32(mine);
+  const int ns = static_cast<int>(splits);
+  for (int i = tid; i < ROWS * ns; i += THREADS) {
+    const int hh = i / ns, r = i % ns;
+    const uint32_t base = ptx::mapa_shared(mine_addr + (hh * REC + D) * 4, static_cast<uint32_t>(r));
+    m_all[hh * kMaxSplitsWide + r] = ptx::ld_shared_cluster_f32(base);
+    l_all[hh * kMaxSplitsWide + r] = ptx::ld_shared_cluster_f32(base + 4);
+  }
+  __syncthreads();
+  for (int hh = tid; hh < ROWS; hh += THREADS) {
+    float mm = -INFINITY;
+    for (int r = 0; r < ns; ++r) mm = fmaxf(mm, m_all[hh * kMaxSplitsWide + r]);
+    float ll = 0.f;
+    for (int r = 0; r < ns; ++r) {
+      const float mr = m_all[hh * kMaxSplitsWide + r];
+      const float wgt = mr == -INFINITY ? 0.f : ptx::ex2_approx(mr - mm);  // a rank without positions carries no weight
+      w_all[hh * kMaxSplitsWide + r] = wgt;
+      ll = fmaf(l_all[hh * kMaxSplitsWide + r], wgt, ll);
+    }
+    l_row[hh] = ll;
+  }
+  __syncthreads();
+  const int per = (ROWS * D + ns - 1) / ns;
+  const int i_end = min(ROWS * D, (static_cast<int>(rank) + 1) * per);
+  for (int i = static_cast<int>(rank) * per + tid; i < i_end; i += THREADS) {
+    const int hh = i / D, dd = i % D;
+    if (hh >= rows_valid) continue;
+    float part_o[kMaxSplitsWide];
+#pragma unroll
+    for (int r = 0; r < kMaxSplitsWide; ++r)
+      part_o[r] = r < ns ? ptx::ld_shared_cluster_f32(ptx::mapa_shared(mine_addr + (hh * REC + dd) * 4, static_cast<uint32_t>(r))) : 0.f;
+    float oo = 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxSplitsWide; ++r)
+      if (r < ns) oo = fmaf(part_o[r], w_all[hh * kMaxSplitsWide + r], oo);
+    softmax::Elem<T>::store1(o_rows + hh * D + dd, oo / l_row[hh]);
+  }
+}
 
 struct Params {
   int32_t batch, heads_q, heads_kv;
@@ -196,28 +252,9 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ kc, const
       mine[hh * REC + D + 1] = ll;
     }
   }
-  // merge across the cluster through distributed shared memory (rank 0 writes the result)
+  // merge across the cluster through distributed shared memory (every CTA writes its share of the result)
   ptx::cluster_sync_all();
-  if (rank == 0) {
-    const uint32_t mine_addr = ptx::smem_u32(mine);
-    for (int i = tid; i < G * D; i += kThreads) {
-      const int hh = i / D, dd = i % D;
-      if (hh >= p.heads_here) continue;
-      float mm = -INFINITY;
-      for (uint32_t r = 0; r < splits; ++r)
-        mm = fmaxf(mm, ptx::ld_shared_cluster_f32(ptx::mapa_shared(mine_addr + (hh * REC + D) * 4, r)));
-      float ll = 0.f, oo = 0.f;
-      for (uint32_t r = 0; r < splits; ++r) {
-        const uint32_t base = ptx::mapa_shared(mine_addr + hh * REC * 4, r);
-        const float mr = ptx::ld_shared_cluster_f32(base + D * 4);
-        const float w = mr == -INFINITY ? 0.f : ptx::ex2_approx(mr - mm);
-        ll = fmaf(ptx::ld_shared_cluster_f32(base + (D + 1) * 4), w, ll);
-        oo = fmaf(ptx::ld_shared_cluster_f32(base + dd * 4), w, oo);
-      }
-      // seq_len == 0: no position contributes; 0 / 0 = NaN, as the five phases give
-      softmax::Elem<T>::store1(o + (static_cast<int64_t>(b) * p.heads_q + h0 + hh) * D + dd, oo / ll);
-    }
-  }
+  cluster_merge<T, G, D, kThreads>(mine, part, rank, splits, p.heads_here, o + (static_cast<int64_t>(b) * p.heads_q + h0) * D);
   ptx::cluster_sync_all();  // nobody leaves while its shared memory may still be read
 }
 
@@ -230,15 +267,23 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ kc, const
 // (tcgen05 needs 64 or 128 rows per tile; 16 padded rows per (batch, KV head) is what a
 // decode step has, so this is the one place the warp-level MMA is the right size.)
 //
-// Per CTA 4 warps; each warp streams its own tiles of 16 positions through a two-stage
-// cp.async ring in shared memory (K and V rows padded by 16 bytes: conflict-free
+// Per CTA 4 or 8 warps; each warp streams its own tiles of 16 positions through a cp.async
+// ring of 2 or 3 stages in shared memory (K and V rows padded by 16 bytes: conflict-free
 // ldmatrix), keeps its own running (max, sum, O) and the partial results are merged as
 // above: warps through shared memory, CTAs of the cluster through distributed shared memory.
+// The ring is started before anything else is read; Q goes from global memory straight into
+// the A fragments.
 // ===========================================================================
 namespace mma {
+#ifdef TSM100_DECODE_TRACE
+// Development aid (never compiled into the library): clock stamps of thread 0 of CTA 0.
+__device__ long long g_decode_trace[64];
+#define TSD_TRACE(k) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_decode_trace[k] = clock64(); } while (0)
+#else
+#define TSD_TRACE(k) do { } while (0)
+#endif
 
-constexpr int kThreads = 128;
-constexpr int kWarps = 4;
+// warps per CTA: 4 for large launches (several CTAs per SM), 8 when a launch has at most one CTA per SM
 constexpr int kTilePos = 16;   // positions per tile
 constexpr int kRows = 16;      // query heads per pass (rows of the MMA tile)
 
@@ -246,9 +291,13 @@ template <int D>
 constexpr int pitch_bytes() { return D * 2 + 16; }
 template <int D>
 constexpr int stage_bytes() { return 2 * kTilePos * pitch_bytes<D>(); }   // K tile + V tile
-// ring (a warp's record for the merge later overlays its own part of it), Q, the CTA's merged record
-template <int D>
-constexpr int smem_bytes() { return kWarps * 2 * stage_bytes<D>() + kRows * D * 2 + kRows * (D + 2) * 4; }
+// ring (a warp's record for the merge later overlays its own part of it), the CTA's merged record.
+// 4 warps x 2 stages when several CTAs share an SM (large batches: the other CTAs hide the latencies);
+// 8 warps x 3 stages when a launch has at most one CTA per SM (a few sequences): a single warp per
+// scheduler spends ~2900 cycles on a tile (the MMA, ldmatrix and shuffle latencies in a row), so the
+// lone CTA needs two warps per scheduler and 136 KiB of loads in flight to draw its share of HBM.
+template <int D, int STAGES, int WARPS>
+constexpr int smem_bytes() { return WARPS * STAGES * stage_bytes<D>() + kRows * (D + 2) * 4; }
 
 __device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr, bool valid) {
   const int n = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
@@ -282,20 +331,20 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <typename T, int D>
-__global__ void __launch_bounds__(kThreads)
+template <typename T, int D, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc, T* __restrict__ o,
                             const Params p) {
   constexpr bool kIsBf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+  constexpr int kWarps = WARPS, kThreads = WARPS * 32;
   constexpr int PITCH = pitch_bytes<D>();
   constexpr int KSTEPS = D / 16;      // k-steps of Q K^T; pairs of 8-wide output tiles of P V
   constexpr int REC = D + 2;
   constexpr int CHUNKS = D * 2 / 16;  // 16-byte pieces per cache row
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint8_t* ring = smem_raw;                                           // [warp][stage][K | V][16 rows][PITCH]
-  T* q_s = reinterpret_cast<T*>(smem_raw + kWarps * 2 * stage_bytes<D>());   // [16][D], rows beyond heads_here zero
-  float* mine = reinterpret_cast<float*>(q_s + kRows * D);            // [16][REC]
-  constexpr int WARP_FLOATS = 2 * stage_bytes<D>() / 4;              // a warp's ring share, reused for its record [16][REC]
+  float* mine = reinterpret_cast<float*>(smem_raw + kWarps * STAGES * stage_bytes<D>());   // [16][REC]
+  constexpr int WARP_FLOATS = STAGES * stage_bytes<D>() / 4;              // a warp's ring share, reused for its record [16][REC]
   static_assert(kRows * REC <= WARP_FLOATS, "a warp's record must fit into its ring share");
   float* part = reinterpret_cast<float*>(ring);                       // warp w's record at part + w * WARP_FLOATS
 
@@ -306,23 +355,6 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
   const int gr = lane >> 2, tq = lane & 3;   // fragment row group and column pair
   const int h0 = g * p.group + p.head_base;
 
-  for (int i = tid; i < kRows * D; i += kThreads) {
-    const int hh = i / D, dd = i % D;
-    q_s[i] = hh < p.heads_here ? q[(static_cast<int64_t>(b) * p.heads_q + h0 + hh) * D + dd] : softmax::Elem<T>::zero();
-  }
-  __syncthreads();
-  // A fragments of Q for every k-step: a0 (row gr, k 2tq..), a1 (row gr+8, ..), a2 (row gr, k 2tq+8..), a3 (row gr+8, ..)
-  uint32_t qa[KSTEPS][4];
-#pragma unroll
-  for (int kk = 0; kk < KSTEPS; ++kk) {
-    const uint32_t* r0 = reinterpret_cast<const uint32_t*>(q_s + gr * D + kk * 16);
-    const uint32_t* r1 = reinterpret_cast<const uint32_t*>(q_s + (gr + 8) * D + kk * 16);
-    qa[kk][0] = r0[tq];
-    qa[kk][1] = r1[tq];
-    qa[kk][2] = r0[tq + 4];
-    qa[kk][3] = r1[tq + 4];
-  }
-
   const int chunk = ((p.seq_len + static_cast<int>(splits) - 1) / static_cast<int>(splits) + 63) & ~63;
   const int p_begin = static_cast<int>(rank) * chunk;
   const int p_end = min(p.seq_len, p_begin + chunk);
@@ -330,7 +362,7 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
   const int64_t cache_off = (static_cast<int64_t>(b) * p.heads_kv + g) * p.max_seq * D;
   const uint8_t* kbase = reinterpret_cast<const uint8_t*>(kc + cache_off);
   const uint8_t* vbase = reinterpret_cast<const uint8_t*>(vc + cache_off);
-  const uint32_t ring_w = ptx::smem_u32(ring) + warp * 2 * stage_bytes<D>();
+  const uint32_t ring_w = ptx::smem_u32(ring) + warp * STAGES * stage_bytes<D>();
 
   auto prefetch = [&](int tile, int stage) {  // this warp's tile `tile` of the CTA's range into its ring stage
     const int row0 = p_begin + tile * kTilePos;
@@ -353,14 +385,36 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows gr and gr + 8 (this thread's share of the sums)
   const float sl2 = p.scale_log2;
 
-  if (warp < n_tiles) prefetch(warp, 0);
-  cp_async_commit();
-  int stage = 0;
-  for (int t = warp; t < n_tiles; t += kWarps, stage ^= 1) {
-    if (t + kWarps < n_tiles) prefetch(t + kWarps, stage ^ 1);
+  TSD_TRACE(0);
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {  // the first tiles are on their way before anything else is read
+    if (warp + i * kWarps < n_tiles) prefetch(warp + i * kWarps, i);
     cp_async_commit();
-    cp_async_wait<1>();  // everything but the newest group: this tile has landed
+  }
+  // A fragments of Q for every k-step, straight from global memory (all loads independent, rows beyond
+  // heads_here zero): a0 (row gr, k 2tq..), a1 (row gr+8, ..), a2 (row gr, k 2tq+8..), a3 (row gr+8, ..)
+  uint32_t qa[KSTEPS][4];
+  {
+    const uint32_t* r0 = reinterpret_cast<const uint32_t*>(q + (static_cast<int64_t>(b) * p.heads_q + h0 + gr) * D);
+    const uint32_t* r1 = r0 + 8 * (D / 2);
+    const bool ok0 = gr < p.heads_here, ok1 = gr + 8 < p.heads_here;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      qa[kk][0] = ok0 ? __ldg(r0 + kk * 8 + tq) : 0u;
+      qa[kk][1] = ok1 ? __ldg(r1 + kk * 8 + tq) : 0u;
+      qa[kk][2] = ok0 ? __ldg(r0 + kk * 8 + tq + 4) : 0u;
+      qa[kk][3] = ok1 ? __ldg(r1 + kk * 8 + tq + 4) : 0u;
+    }
+  }
+  TSD_TRACE(1);
+  int stage = 0;
+  for (int t = warp; t < n_tiles; t += kWarps, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+    if (t + (STAGES - 1) * kWarps < n_tiles) prefetch(t + (STAGES - 1) * kWarps, stage == 0 ? STAGES - 1 : stage - 1);
+    cp_async_commit();
+    if (t < 16 * kWarps) TSD_TRACE(8 + 2 * (t / kWarps));
+    cp_async_wait<STAGES - 1>();  // everything but the newest STAGES - 1 groups: this tile has landed
     __syncwarp();
+    if (t < 16 * kWarps) TSD_TRACE(9 + 2 * (t / kWarps));
     const uint32_t ks = ring_w + stage * stage_bytes<D>();
     const uint32_t vs = ks + kTilePos * PITCH;
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -417,8 +471,9 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
       mma_16816<kIsBf16>(oacc[2 * jj], pa, vb[0], vb[1]);
       mma_16816<kIsBf16>(oacc[2 * jj + 1], pa, vb[2], vb[3]);
     }
-    __syncwarp();  // the stage is refilled two iterations from now; every lane is done reading it
+    __syncwarp();  // the stage is refilled at the top of the next iteration; every lane is done reading it
   }
+  TSD_TRACE(2);
   cp_async_wait<0>();
   __syncwarp();  // the warp's ring share is free: it now receives the warp's record
   // this thread's share of the row sums -> the whole row's
@@ -465,27 +520,13 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
       mine[hh * REC + D + 1] = ll;
     }
   }
+  TSD_TRACE(3);
   ptx::cluster_sync_all();
-  if (rank == 0) {
-    const uint32_t mine_addr = ptx::smem_u32(mine);
-    for (int i = tid; i < kRows * D; i += kThreads) {
-      const int hh = i / D, dd = i % D;
-      if (hh >= p.heads_here) continue;
-      float mm = -INFINITY;
-      for (uint32_t r = 0; r < splits; ++r)
-        mm = fmaxf(mm, ptx::ld_shared_cluster_f32(ptx::mapa_shared(mine_addr + (hh * REC + D) * 4, r)));
-      float ll = 0.f, oo = 0.f;
-      for (uint32_t r = 0; r < splits; ++r) {
-        const uint32_t base = ptx::mapa_shared(mine_addr + hh * REC * 4, r);
-        const float mr = ptx::ld_shared_cluster_f32(base + D * 4);
-        const float wgt = mr == -INFINITY ? 0.f : ptx::ex2_approx(mr - mm);
-        ll = fmaf(ptx::ld_shared_cluster_f32(base + (D + 1) * 4), wgt, ll);
-        oo = fmaf(ptx::ld_shared_cluster_f32(base + dd * 4), wgt, oo);
-      }
-      softmax::Elem<T>::store1(o + (static_cast<int64_t>(b) * p.heads_q + h0 + hh) * D + dd, oo / ll);
-    }
-  }
+  TSD_TRACE(4);
+  cluster_merge<T, kRows, D, kThreads>(mine, part, rank, splits, p.heads_here, o + (static_cast<int64_t>(b) * p.heads_q + h0) * D);
+  TSD_TRACE(5);
   ptx::cluster_sync_all();  // nobody leaves while its shared memory may still be read
+  TSD_TRACE(6);
 }
 
 }  // namespace mma

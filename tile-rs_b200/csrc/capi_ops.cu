@@ -374,3 +374,9 @@ extern "C" int32_t tsm100_debug_read_attn_trace(long long* out) {
   return cudaMemcpyFromSymbol(out, tsm100::attn::g_attn_trace, sizeof(tsm100::attn::g_attn_trace)) == cudaSuccess ? 0 : 6;
 }
 #endif
+
+#ifdef TSM100_DECODE_TRACE
+extern "C" int32_t tsm100_debug_read_decode_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, tsm100::attn_decode::mma::g_decode_trace, sizeof(tsm100::attn_decode::mma::g_decode_trace)) == cudaSuccess ? 0 : 6;
+}
+#endif

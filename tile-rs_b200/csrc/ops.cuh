@@ -713,7 +713,7 @@ inline int32_t attention_decode_launch(std::string* err, const tsm100_attention_
   return cuda_ok(err, e, "attention_decode_kernel launch");
 }
 
-template <typename T, int D>
+template <typename T, int D, int STAGES, int WARPS>
 inline int32_t attention_decode_mma_launch(std::string* err, const tsm100_attention_decode_desc* d, const T* q, const T* k,
                                            const T* v, T* o, int head_base, int heads_here, int splits, cudaStream_t s) {
   namespace ad = attn_decode;
@@ -727,10 +727,14 @@ inline int32_t attention_decode_mma_launch(std::string* err, const tsm100_attent
   p.head_base = head_base;
   p.heads_here = heads_here;
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
-  auto kern = ad::mma::attention_decode_mma_kernel<T, D>;
-  constexpr int smem = ad::mma::smem_bytes<D>();
+  auto kern = ad::mma::attention_decode_mma_kernel<T, D, STAGES, WARPS>;
+  constexpr int smem = ad::mma::smem_bytes<D, STAGES, WARPS>();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_decode_mma_kernel)");
+  if (splits > ad::kMaxSplits) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_decode_mma_kernel, wide clusters)");
+  }
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -739,12 +743,46 @@ inline int32_t attention_decode_mma_launch(std::string* err, const tsm100_attent
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cfg.blockDim = dim3(ad::mma::kThreads);
+  cfg.blockDim = dim3(WARPS * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cfg.gridDim = dim3(static_cast<unsigned>(static_cast<int64_t>(d->batch) * d->heads_kv * splits));
   e = cudaLaunchKernelEx(&cfg, kern, q, k, v, o, p);
   return cuda_ok(err, e, "attention_decode_mma_kernel launch");
+}
+
+// How many clusters of `size` CTAs of the eight-warp decode kernel the GPU holds at once (asked once per
+// kernel, size and device; 0 if such clusters cannot be placed at all).
+template <typename T, int D>
+inline int decode_lone_clusters(int size) {
+  namespace ad = attn_decode;
+  static int cached[64][2] = {};  // [device][size == 16]: 0 unknown, else count + 1
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  int& slot = cached[dev][size > ad::kMaxSplits ? 1 : 0];
+  if (size != ad::kMaxSplits && size != ad::kMaxSplitsWide) return 0;
+  if (slot == 0) {
+    auto kern = ad::mma::attention_decode_mma_kernel<T, D, 3, 8>;
+    constexpr int smem = ad::mma::smem_bytes<D, 3, 8>();
+    int clusters = 0;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(size);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.blockDim = dim3(8 * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.gridDim = dim3(static_cast<unsigned>(size));
+    const bool ok = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                    cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+                    cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) == cudaSuccess;
+    if (!ok) (void)cudaGetLastError();  // the answer is "none", not an error of the caller's launch
+    slot = (ok ? clusters : 0) + 1;
+  }
+  return slot - 1;
 }
 
 template <typename T, int D>
@@ -768,8 +806,16 @@ inline int32_t attention_decode_typed(std::string* err, const tsm100_attention_d
     // so the GPU is covered about four times before the ranges get shorter than 256 positions
     splits = 1;
     while (splits < attn_decode::kMaxSplits && units * splits < 4ll * sms && d->seq_len / (2 * splits) >= 256) splits *= 2;
+    // a handful of sequences: clusters of 16 if the GPU holds all of them at once (one CTA per SM; a B200
+    // holds 7), so that most SMs take part
+    if (splits == attn_decode::kMaxSplits && d->seq_len / (2 * attn_decode::kMaxSplitsWide) >= 256 &&
+        units <= decode_lone_clusters<T, D>(attn_decode::kMaxSplitsWide))
+      splits = attn_decode::kMaxSplitsWide;
+    // every CTA alone on its SM from start to end: eight warps and a deeper ring, so that it hides its own latencies
+    const bool lone = units * splits <= sms && (splits < attn_decode::kMaxSplits || units <= decode_lone_clusters<T, D>(splits));
     for (int base = 0; base < group && st == TSM100_OK; base += 16)
-      st = attention_decode_mma_launch<T, D>(err, d, qp, kp, vp, op, base, std::min(16, group - base), splits, s);
+      st = lone ? attention_decode_mma_launch<T, D, 3, 8>(err, d, qp, kp, vp, op, base, std::min(16, group - base), splits, s)
+                : attention_decode_mma_launch<T, D, 2, 4>(err, d, qp, kp, vp, op, base, std::min(16, group - base), splits, s);
     return st;
   }
   // groups wider than 8 query heads run in passes of 8 (the cache is then re-read, from L2 when it fits)
@@ -796,7 +842,7 @@ inline int32_t attention_decode(std::string* err, const tsm100_attention_decode_
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
     return op_fail(err, TSM100_ERR_INVALID, "attention_decode: buffers must be 16-byte aligned");
   if (d->batch == 0) return TSM100_OK;
-  if (static_cast<int64_t>(d->batch) * d->heads_kv * attn_decode::kMaxSplits > 0x7fffffff)
+  if (static_cast<int64_t>(d->batch) * d->heads_kv * attn_decode::kMaxSplitsWide > 0x7fffffff)
     return op_fail(err, TSM100_ERR_INVALID, "attention_decode: too many (batch, KV head) units for one launch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool d128 = d->head_dim == 128;
