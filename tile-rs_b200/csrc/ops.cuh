@@ -14,6 +14,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <type_traits>
 
 #include "../../include/tile_sm100.h"
 #include "attention_decode.cuh"
@@ -323,16 +324,19 @@ inline int32_t rope(std::string* err, const tsm100_rope_desc* d, void* x, void* 
   int sms = 0;
   int32_t st = sm_count(err, &sms);
   if (st != TSM100_OK) return st;
-  const int64_t n = tokens * (d->head_dim / 2);
-  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, static_cast<int64_t>(sms) * 8)));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (d->dtype == TSM100_F32)
-    rowops::rope_kernel<float><<<grid, 256, 0, s>>>(static_cast<float*>(x), tokens, d->seq_len, d->heads, d->head_dim, d->start_pos, d->theta);
-  else if (d->dtype == TSM100_BF16)
-    rowops::rope_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(x), tokens, d->seq_len, d->heads, d->head_dim,
-                                                            d->start_pos, d->theta);
-  else
-    rowops::rope_kernel<__half><<<grid, 256, 0, s>>>(static_cast<__half*>(x), tokens, d->seq_len, d->heads, d->head_dim, d->start_pos, d->theta);
+  const int pv = d->dtype == TSM100_F32 ? 4 : 8;  // elements per 16 bytes
+  const bool vec = d->head_dim % pv == 0 && aligned16(x);
+  const int64_t n = tokens * (vec ? d->head_dim / pv : d->head_dim / 2);
+  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, static_cast<int64_t>(sms) * 8)));
+  auto launch = [&](auto* xt) {
+    using T = std::remove_pointer_t<decltype(xt)>;
+    if (vec) rowops::rope_vec_kernel<T><<<grid, 256, 0, s>>>(xt, tokens, d->seq_len, d->heads, d->head_dim, d->start_pos, d->theta);
+    else rowops::rope_kernel<T><<<grid, 256, 0, s>>>(xt, tokens, d->seq_len, d->heads, d->head_dim, d->start_pos, d->theta);
+  };
+  if (d->dtype == TSM100_F32) launch(static_cast<float*>(x));
+  else if (d->dtype == TSM100_BF16) launch(static_cast<__nv_bfloat16*>(x));
+  else launch(static_cast<__half*>(x));
   return cuda_ok(err, cudaGetLastError(), "rope_kernel launch");
 }
 
@@ -342,12 +346,17 @@ inline cudaError_t kv_cache_update_typed(const tsm100_kv_cache_update_desc* d, c
   const bool vec = d->head_dim % PV == 0 && aligned16(src) && aligned16(cache);
   const int64_t n = static_cast<int64_t>(d->batch) * d->seq_len * d->heads * (vec ? d->head_dim / PV : d->head_dim);
   const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, static_cast<int64_t>(sms) * 8)));
-  if (vec)
-    rowops::kv_cache_update_kernel<T, PV><<<grid, 256, 0, s>>>(static_cast<const T*>(src), static_cast<T*>(cache), d->batch, d->seq_len,
-                                                               d->heads, d->head_dim, d->start_pos, d->max_seq);
-  else
-    rowops::kv_cache_update_kernel<T, 1><<<grid, 256, 0, s>>>(static_cast<const T*>(src), static_cast<T*>(cache), d->batch, d->seq_len,
-                                                              d->heads, d->head_dim, d->start_pos, d->max_seq);
+  const bool small = n + static_cast<int64_t>(grid) * 256 < 0xffffffffll;  // the loop index cannot wrap
+  auto launch = [&](auto vec_tag, auto index_tag) {
+    constexpr int V = decltype(vec_tag)::value;
+    using I = decltype(index_tag);
+    rowops::kv_cache_update_kernel<T, V, I><<<grid, 256, 0, s>>>(static_cast<const T*>(src), static_cast<T*>(cache), d->batch,
+                                                                 d->seq_len, d->heads, d->head_dim, d->start_pos, d->max_seq);
+  };
+  if (vec && small) launch(std::integral_constant<int, PV>{}, uint32_t{});
+  else if (vec) launch(std::integral_constant<int, PV>{}, int64_t{});
+  else if (small) launch(std::integral_constant<int, 1>{}, uint32_t{});
+  else launch(std::integral_constant<int, 1>{}, int64_t{});
   return cudaGetLastError();
 }
 

@@ -254,23 +254,71 @@ rope_kernel(T* __restrict__ x, int64_t tokens, int32_t seq_len, int32_t heads, i
   }
 }
 
-// VEC = elements per access (16 bytes when rows allow it, else 1)
-template <typename T, int VEC>
+// The same with 16-byte accesses (head_dim a multiple of the vector, 16-byte aligned buffer): one thread per
+// (batch, token, vector of a head row); its PV/2 angles are computed once and used for every head, and the
+// loads of four heads are in flight together.  Same formula per pair as above.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(T* __restrict__ x, int64_t tokens, int32_t seq_len, int32_t heads, int32_t d, int32_t start_pos, float theta) {
+  constexpr int PV = Elem<T>::kPerVec;
+  constexpr int HU = 4;
+  const int dv = d / PV;
+  const int64_t n = tokens * dv;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < n;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t tok = idx / dv;
+    const int j = static_cast<int>(idx % dv);
+    const int pos = start_pos + static_cast<int>(tok % seq_len);
+    float c[PV / 2], s[PV / 2];
+#pragma unroll
+    for (int e = 0; e < PV / 2; ++e) {
+      const int i = j * (PV / 2) + e;
+      const float freq = 1.0f / powf(theta, 2.0f * static_cast<float>(i) / static_cast<float>(d));
+      const float angle = static_cast<float>(pos) * freq;
+      sincosf(angle, &s[e], &c[e]);
+    }
+    Vec16* p = reinterpret_cast<Vec16*>(x + tok * heads * d) + j;
+    auto rotate = [&](const Vec16& raw) -> Vec16 {
+      float f[PV], r[PV];
+      Elem<T>::unpack(raw, f);
+#pragma unroll
+      for (int e = 0; e < PV / 2; ++e) {
+        const float x0 = f[2 * e], x1 = f[2 * e + 1];
+        r[2 * e] = x0 * c[e] - x1 * s[e];
+        r[2 * e + 1] = x0 * s[e] + x1 * c[e];
+      }
+      return Elem<T>::pack(r);
+    };
+    int h = 0;
+    for (; h + HU <= heads; h += HU) {
+      Vec16 raw[HU];
+#pragma unroll
+      for (int u = 0; u < HU; ++u) raw[u] = p[static_cast<int64_t>(h + u) * dv];
+#pragma unroll
+      for (int u = 0; u < HU; ++u) p[static_cast<int64_t>(h + u) * dv] = rotate(raw[u]);
+    }
+    for (; h < heads; ++h) p[static_cast<int64_t>(h) * dv] = rotate(p[static_cast<int64_t>(h) * dv]);
+  }
+}
+
+// VEC = elements per access (16 bytes when rows allow it, else 1); I = index arithmetic type: 32-bit when the
+// element count allows it (64-bit divisions cost more than the copy)
+template <typename T, int VEC, typename I>
 __global__ void __launch_bounds__(256)
 kv_cache_update_kernel(const T* __restrict__ src, T* __restrict__ cache, int64_t batch, int32_t seq_len, int32_t heads,
                        int32_t d, int32_t start_pos, int32_t max_seq) {
-  const int dv = d / VEC;
-  const int64_t n = batch * seq_len * heads * dv;
-  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < n;
-       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+  const I dv = static_cast<I>(d / VEC);
+  const I n = static_cast<I>(batch * seq_len * heads) * dv;
+  const I stride = static_cast<I>(gridDim.x) * blockDim.x;
+  for (I idx = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x; idx < n; idx += stride) {
     const int dd = static_cast<int>(idx % dv) * VEC;
-    int64_t r = idx / dv;
-    const int h = static_cast<int>(r % heads);
-    r /= heads;
-    const int si = static_cast<int>(r % seq_len);
-    const int64_t b = r / seq_len;
-    const T* s = src + ((b * seq_len + si) * heads + h) * d + dd;
-    T* c = cache + ((b * heads + h) * max_seq + start_pos + si) * d + dd;
+    I r = idx / dv;
+    const I h = r % static_cast<I>(heads);
+    r /= static_cast<I>(heads);
+    const I si = r % static_cast<I>(seq_len);
+    const int64_t b = static_cast<int64_t>(r / static_cast<I>(seq_len));
+    const T* s = src + ((b * seq_len + static_cast<int64_t>(si)) * heads + static_cast<int64_t>(h)) * d + dd;
+    T* c = cache + ((b * heads + static_cast<int64_t>(h)) * max_seq + start_pos + static_cast<int64_t>(si)) * d + dd;
     if (VEC == 1) *c = *s;
     else *reinterpret_cast<Vec16*>(c) = *reinterpret_cast<const Vec16*>(s);
   }
