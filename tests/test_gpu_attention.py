@@ -74,6 +74,43 @@ def test_attention_f32_fp32_pipe(dev, pkg, oracle, causal):
     assert m["rel_max"] <= 1e-5 and m["rel_fro"] <= 1e-5, m
 
 
+@pytest.mark.parametrize("b,hq,hkv,s,d,causal", [(1, 2, 2, 333, 128, False), (1, 4, 2, 333, 128, True), (2, 2, 1, 64, 64, True),
+                                                    (1, 1, 1, 1, 128, True), (1, 2, 2, 700, 64, False), (1, 3, 3, 129, 128, True)])
+def test_attention_f32_tensor_core_three_tf32(dev, pkg, oracle, b, hq, hkv, s, d, causal):
+    """f32 tensors with head_dim 64 / 128 run on tensor cores with three TF32 products per product: same 1e-5 bar
+    as the f32 GEMM, against the f32 oracle and its f64-accumulating variant; ragged last query and key tiles."""
+    capi = pkg.capi
+    q = util.gen_normal(capi, (b, hq, s, d), 441)
+    k = util.gen_normal(capi, (b, hkv, s, d), 442)
+    v = util.gen_normal(capi, (b, hkv, s, d), 443)
+    o = run_attention(dev, capi, q, k, v, capi.F32, causal)
+    assert np.isfinite(o).all()
+    m = oracle.compare(o, oracle.attention_f32(q, k, v, causal))
+    assert m["rel_max"] <= 1e-5 and m["rel_fro"] <= 1e-5, m
+
+
+def test_attention_f32_other_head_dim_fp32_pipe(dev, pkg, oracle):
+    capi = pkg.capi
+    b, hq, hkv, s, d = 1, 2, 1, 70, 80  # head_dim 80 on f32 data: the FP32-pipe kernel
+    q = util.gen_normal(capi, (b, hq, s, d), 451)
+    k = util.gen_normal(capi, (b, hkv, s, d), 452)
+    v = util.gen_normal(capi, (b, hkv, s, d), 453)
+    o = run_attention(dev, capi, q, k, v, capi.F32, True)
+    m = oracle.compare(o, oracle.attention_f32(q, k, v, True))
+    assert m["rel_max"] <= 1e-5 and m["rel_fro"] <= 1e-5, m
+
+
+def test_attention_f32_large_scores(dev, pkg, oracle):
+    """Scores of a few hundred: the running maximum and the rescaling of the accumulator matter."""
+    capi = pkg.capi
+    q = 6.0 * util.gen_normal(capi, (1, 2, 500, 128), 461)
+    k = util.gen_normal(capi, (1, 2, 500, 128), 462)
+    v = util.gen_normal(capi, (1, 2, 500, 128), 463)
+    o = run_attention(dev, capi, q, k, v, capi.F32, False)
+    m = oracle.compare(o, oracle.attention_f32(q, k, v, False))
+    assert m["rel_max"] <= 2e-5 and m["rel_fro"] <= 1e-5, m
+
+
 def test_attention_f16_and_other_head_dim(dev, pkg, oracle):
     capi = pkg.capi
     b, h, s, d = 1, 2, 96, 80  # head_dim 80: FP32-pipe kernel on 16-bit data

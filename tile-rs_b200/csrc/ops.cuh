@@ -20,6 +20,7 @@
 #include "attention_decode.cuh"
 #include "attention_simt.cuh"
 #include "attention_tc.cuh"
+#include "attention_tf32x3.cuh"
 #include "ewise.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
@@ -595,6 +596,34 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
 // ---------------------------------------------------------------------------
 // attention
 // ---------------------------------------------------------------------------
+// f32 tensors with head_dim 64 or 128 and 16-byte aligned rows: tensor cores, three TF32 products per product.
+inline bool attention_tf32x3_ok(const attn_simt::Params& p, const void* q, const void* k, const void* v, const void* o) {
+  return (p.head_dim == 64 || p.head_dim == 128) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) &&
+         p.q_row_stride % 4 == 0 && p.q_head_stride % 4 == 0 && p.kv_head_stride % 4 == 0 && p.o_row_stride % 4 == 0 &&
+         p.o_head_stride % 4 == 0;
+}
+template <int D>
+inline int32_t attention_tf32x3_launch_d(std::string* err, const attn_simt::Params& p, const float* q, const float* k,
+                                         const float* v, float* o, cudaStream_t s) {
+  namespace at = attn_tf32;
+  const int64_t grid = static_cast<int64_t>((p.seq + at::kBM - 1) / at::kBM) * p.batch * p.heads_q;
+  if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many query blocks for one launch");
+  auto kern = at::attention_tf32x3_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, at::smem_bytes<D>());
+  if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_tf32x3_kernel)");
+  kern<<<static_cast<unsigned>(grid), at::kThreads, at::smem_bytes<D>(), s>>>(q, k, v, o, p);
+  return cuda_ok(err, cudaGetLastError(), "attention_tf32x3_kernel launch");
+}
+inline int32_t attention_tf32x3_launch(std::string* err, const attn_simt::Params& p, const void* q, const void* k,
+                                       const void* v, void* o, cudaStream_t s) {
+  const float* qf = static_cast<const float*>(q);
+  const float* kf = static_cast<const float*>(k);
+  const float* vf = static_cast<const float*>(v);
+  float* of = static_cast<float*>(o);
+  return p.head_dim == 128 ? attention_tf32x3_launch_d<128>(err, p, qf, kf, vf, of, s)
+                           : attention_tf32x3_launch_d<64>(err, p, qf, kf, vf, of, s);
+}
+
 template <typename T>
 inline int32_t attention_simt_launch(std::string* err, const tsm100_attention_desc* d, const void* q, const void* k,
                                      const void* v, void* o, cudaStream_t s) {
@@ -602,6 +631,8 @@ inline int32_t attention_simt_launch(std::string* err, const tsm100_attention_de
   attn_simt::Params p{d->seq, d->head_dim, d->heads_q, d->heads_kv, d->batch, d->causal,
                       static_cast<float>(1.0 / std::sqrt(static_cast<double>(d->head_dim))),
                       d->seq, 0, d->head_dim, sd, sd, d->head_dim, sd};
+  if constexpr (std::is_same<T, float>::value)
+    if (attention_tf32x3_ok(p, q, k, v, o)) return attention_tf32x3_launch(err, p, q, k, v, o, s);
   const int64_t rows = static_cast<int64_t>(d->batch) * d->heads_q * d->seq;
   const int64_t grid = (rows + attn_simt::kWarps - 1) / attn_simt::kWarps;
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many query rows for one launch");
@@ -621,6 +652,8 @@ inline int32_t attention_prefill_simt_launch(std::string* err, const tsm100_atte
                       static_cast<float>(1.0 / std::sqrt(static_cast<double>(d->head_dim))),
                       d->start_pos + d->seq_len, d->start_pos, hd, d->head_dim,
                       static_cast<int64_t>(d->max_seq) * d->head_dim, hd, d->head_dim};
+  if constexpr (std::is_same<T, float>::value)
+    if (attention_tf32x3_ok(p, q, k, v, o)) return attention_tf32x3_launch(err, p, q, k, v, o, s);
   const int64_t rows = static_cast<int64_t>(d->heads_q) * d->seq_len;
   const int64_t grid = (rows + attn_simt::kWarps - 1) / attn_simt::kWarps;
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: too many query rows for one launch");
