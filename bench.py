@@ -294,18 +294,21 @@ class GemmWL(Workload):
 class AttentionWL(Workload):
     bound, unit_name, dtype = "tensor", "kv_groups", "bf16"
 
-    def __init__(self, ctx, units, group, seq, causal, name):
+    def __init__(self, ctx, units, group, seq, causal, name, dtype="bf16"):
         super().__init__(ctx, units)
         torch = _torch()
-        self.group, self.seq, self.causal, self.name = group, seq, causal, name
+        self.group, self.seq, self.causal, self.name, self.dtype = group, seq, causal, name, dtype
+        if dtype == "f32":  # three TF32 products per product on the warp-level MMA: compared with the FP32 FMA rate
+            self.bound = "fp32"
         self.work_per_unit = 4.0 * group * seq * seq * 128 * (0.5 if causal else 1.0)
         g = torch.Generator(device=ctx.tdev).manual_seed(401)
-        mk = lambda h: torch.randn(units, h, seq, 128, device=ctx.tdev, generator=g).to(torch.bfloat16)
+        mk = lambda h: torch.randn(units, h, seq, 128, device=ctx.tdev, generator=g).to(torch.float32 if dtype == "f32" else torch.bfloat16)
         self.q, self.k, self.v = mk(group), mk(1), mk(1)
         self.o = torch.empty_like(self.q)
 
     def step(self):
-        self.ctx.dev.attention(self.ctx.pkg.capi.BF16, self.units, self.group, 1, self.seq, 128, self.q.data_ptr(),
+        capi = self.ctx.pkg.capi
+        self.ctx.dev.attention(capi.F32 if self.dtype == "f32" else capi.BF16, self.units, self.group, 1, self.seq, 128, self.q.data_ptr(),
                                self.k.data_ptr(), self.v.data_ptr(), self.o.data_ptr(), causal=self.causal,
                                stream=self.ctx.stream)
 
@@ -351,6 +354,7 @@ def catalogue():
         "attention_noncausal": (256, lambda c, u, f: AttentionWL(c, u, 1, 4096, False, "attention_noncausal")),
         "attention_causal": (256, lambda c, u, f: AttentionWL(c, u, 1, 4096, True, "attention_causal")),
         "attention_gqa_causal": (16, lambda c, u, f: AttentionWL(c, u, 8, 16384, True, "attention_gqa_causal")),
+        "attention_f32_causal": (32, lambda c, u, f: AttentionWL(c, u, 1, 4096, True, "attention_f32_causal", "f32")),
         "rms_norm_f32": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "rms_norm")),
         "reduce_sum_f32": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "reduce_sum")),
         "silu_mul_f32": (SOFTMAX_ROWS, lambda c, u, f: RowOpWL(c, u, "silu_mul")),

@@ -75,7 +75,8 @@ def test_attention_f32_fp32_pipe(dev, pkg, oracle, causal):
 
 
 @pytest.mark.parametrize("b,hq,hkv,s,d,causal", [(1, 2, 2, 333, 128, False), (1, 4, 2, 333, 128, True), (2, 2, 1, 64, 64, True),
-                                                    (1, 1, 1, 1, 128, True), (1, 2, 2, 700, 64, False), (1, 3, 3, 129, 128, True)])
+                                                    (1, 1, 1, 1, 128, True), (1, 2, 2, 700, 64, False), (1, 3, 3, 129, 128, True),
+                                                    (1, 2, 1, 200, 96, True), (2, 2, 2, 150, 32, False)])
 def test_attention_f32_tensor_core_three_tf32(dev, pkg, oracle, b, hq, hkv, s, d, causal):
     """f32 tensors with head_dim 64 / 128 run on tensor cores with three TF32 products per product: same 1e-5 bar
     as the f32 GEMM, against the f32 oracle and its f64-accumulating variant; ragged last query and key tiles."""

@@ -35,7 +35,7 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 2;
 
 template <int D>
-constexpr int pitch() { return D + 4; }  // floats: rows 4 banks apart
+constexpr int pitch() { return D + 4; }  // floats: rows 4 banks apart for D = 32, 64, 96, 128 (D % 32 == 0)
 template <int D>
 constexpr int tile_floats() { return kBN * pitch<D>(); }
 template <int D>

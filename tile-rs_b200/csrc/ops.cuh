@@ -596,9 +596,9 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
 // ---------------------------------------------------------------------------
 // attention
 // ---------------------------------------------------------------------------
-// f32 tensors with head_dim 64 or 128 and 16-byte aligned rows: tensor cores, three TF32 products per product.
+// f32 tensors with head_dim 32, 64, 96 or 128 and 16-byte aligned rows: tensor cores, three TF32 products per product.
 inline bool attention_tf32x3_ok(const attn_simt::Params& p, const void* q, const void* k, const void* v, const void* o) {
-  return (p.head_dim == 64 || p.head_dim == 128) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) &&
+  return (p.head_dim == 32 || p.head_dim == 64 || p.head_dim == 96 || p.head_dim == 128) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) &&
          p.q_row_stride % 4 == 0 && p.q_head_stride % 4 == 0 && p.kv_head_stride % 4 == 0 && p.o_row_stride % 4 == 0 &&
          p.o_head_stride % 4 == 0;
 }
@@ -620,8 +620,12 @@ inline int32_t attention_tf32x3_launch(std::string* err, const attn_simt::Params
   const float* kf = static_cast<const float*>(k);
   const float* vf = static_cast<const float*>(v);
   float* of = static_cast<float*>(o);
-  return p.head_dim == 128 ? attention_tf32x3_launch_d<128>(err, p, qf, kf, vf, of, s)
-                           : attention_tf32x3_launch_d<64>(err, p, qf, kf, vf, of, s);
+  switch (p.head_dim) {
+    case 128: return attention_tf32x3_launch_d<128>(err, p, qf, kf, vf, of, s);
+    case 96: return attention_tf32x3_launch_d<96>(err, p, qf, kf, vf, of, s);
+    case 64: return attention_tf32x3_launch_d<64>(err, p, qf, kf, vf, of, s);
+    default: return attention_tf32x3_launch_d<32>(err, p, qf, kf, vf, of, s);
+  }
 }
 
 template <typename T>
