@@ -90,6 +90,27 @@ def test_attention_f32_tensor_core_three_tf32(dev, pkg, oracle, b, hq, hkv, s, d
     assert m["rel_max"] <= 1e-5 and m["rel_fro"] <= 1e-5, m
 
 
+@pytest.mark.parametrize("b,hq,hkv,s,d,causal", [(1, 4, 2, 300, 64, True), (2, 2, 2, 129, 96, False), (1, 2, 1, 1000, 32, True),
+                                                    (1, 8, 2, 2048, 64, True)])
+def test_attention_bf16_small_head_dims(dev, pkg, oracle, b, hq, hkv, s, d, causal):
+    """16-bit data with head_dim 32 / 64 / 96: the warp-level tensor-core kernel (the inputs are TF32 numbers, so
+    Q K^T is one product and P V two)."""
+    capi = pkg.capi
+    q, k, v = bf16_qkv(capi, b, hq, hkv, s, d, seed=471)
+    o = run_attention(dev, capi, q, k, v, capi.BF16, causal).view(np.uint16)
+    ref32, _ = oracle.attention_bf16(q, k, v, causal)
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(o), ref32)
+
+
+def test_attention_f16_head_dim_64(dev, pkg, oracle):
+    capi = pkg.capi
+    qf, kf, vf = (util.gen_normal(capi, (1, 2, 200, 64), 480 + i) for i in range(3))
+    qh, kh, vh = (util.f32_to_f16_bits(t) for t in (qf, kf, vf))
+    oh = run_attention(dev, capi, qh, kh, vh, capi.F16, True).view(np.float16).astype(np.float32)
+    ref = oracle.attention_f32(*(t.view(np.float16).astype(np.float32) for t in (qh, kh, vh)), True)
+    util.assert_16bit_close(oracle, oh, ref)
+
+
 def test_attention_f32_other_head_dim_fp32_pipe(dev, pkg, oracle):
     capi = pkg.capi
     b, hq, hkv, s, d = 1, 2, 1, 70, 80  # head_dim 80 on f32 data: the FP32-pipe kernel

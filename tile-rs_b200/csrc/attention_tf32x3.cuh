@@ -15,6 +15,9 @@
 // B-fragment loads hit 32 banks); the score tile lives in the accumulator fragments, online
 // max / sum per row, and the accumulator layout of S is used directly as the A operand of
 // P V (the k index of that product is a permutation of the keys, applied to the V loads).
+// 16-bit tensors with head sizes the tcgen05 kernel does not cover (32, 64, 96) use the same kernel:
+// a bf16 or f16 value is a TF32 number already (8 / 11 significant bits), its lo part is zero, so
+// Q K^T is ONE product and P V two (P is f32), still with f32-grade accuracy before the final rounding.
 // Same strided layouts as attention_simt.cuh: plain [batch*heads][seq][d] tensors, or
 // token-major Q / O against a KV cache with a position offset (prefill).
 #pragma once
@@ -34,12 +37,12 @@ constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 2;
 
-template <int D>
-constexpr int pitch() { return D + 4; }  // floats: rows 4 banks apart for D = 32, 64, 96, 128 (D % 32 == 0)
-template <int D>
-constexpr int tile_floats() { return kBN * pitch<D>(); }
-template <int D>
-constexpr int smem_bytes() { return kStages * 2 * tile_floats<D>() * 4; }  // K and V tiles
+template <typename T, int D>
+constexpr int pitch_bytes() { return D * static_cast<int>(sizeof(T)) + 16; }  // rows 4 banks apart for D = 32, 64, 96, 128
+template <typename T, int D>
+constexpr int tile_bytes() { return kBN * pitch_bytes<T, D>(); }
+template <typename T, int D>
+constexpr int smem_bytes() { return kStages * 2 * tile_bytes<T, D>(); }  // K and V tiles
 
 __device__ __forceinline__ void split(float x, uint32_t& hi, uint32_t& lo) {
   hi = __float_as_uint(x) & 0xffffe000u;          // what the tensor core reads of x
@@ -49,25 +52,36 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
   asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// d += a * b with three products, small terms first
-__device__ __forceinline__ void mma_3x(float (&d)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4], float b0, float b1) {
-  uint32_t b0h, b0l, b1h, b1l;
-  split(b0, b0h, b0l);
-  split(b1, b1h, b1l);
-  mma_tf32(d, al, b0h, b1h);
-  mma_tf32(d, ah, b0l, b1l);
-  mma_tf32(d, ah, b0h, b1h);
+// d += a * b, small terms first.  f32 B: three products.  A 16-bit B value (bf16: 8 significant bits, f16: 11)
+// is a TF32 number already, its lo part is zero: two products, or one when A is 16-bit data as well.
+template <bool kExactA, bool kExactB>
+__device__ __forceinline__ void mma_split(float (&d)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4], float b0, float b1) {
+  if (kExactB) {
+    if (!kExactA) mma_tf32(d, al, __float_as_uint(b0), __float_as_uint(b1));
+    mma_tf32(d, ah, __float_as_uint(b0), __float_as_uint(b1));
+  } else {
+    uint32_t b0h, b0l, b1h, b1l;
+    split(b0, b0h, b0l);
+    split(b1, b1h, b1l);
+    mma_tf32(d, al, b0h, b1h);
+    mma_tf32(d, ah, b0l, b1l);
+    mma_tf32(d, ah, b0h, b1h);
+  }
 }
 
-template <int D>
+template <typename T, int D>
 __global__ void __launch_bounds__(kThreads)
-attention_tf32x3_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                        float* __restrict__ o, const Params p) {
+attention_tf32x3_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                        T* __restrict__ o, const Params p) {
   namespace cp = attn_decode::mma;
-  constexpr int PW = pitch<D>();
+  using gemm_simt::from_f32;
+  using gemm_simt::to_f32;
+  constexpr bool kExact = sizeof(T) == 2;  // 16-bit data: every input value is a TF32 number
+  constexpr int PW = pitch_bytes<T, D>() / static_cast<int>(sizeof(T));  // row pitch in elements
   constexpr int KSTEPS = D / 8;   // k-steps of Q K^T; 8-wide output tiles of P V
-  constexpr int CHUNKS = D / 4;   // 16-byte pieces per row
-  extern __shared__ __align__(16) float smem_f[];
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T));
+  constexpr int CHUNKS = D / VEC;  // 16-byte pieces per row
+  extern __shared__ __align__(16) uint8_t smem_f[];
   const uint32_t smem_base = ptx::smem_u32(smem_f);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gr = lane >> 2, tq = lane & 3;
@@ -79,20 +93,20 @@ attention_tf32x3_kernel(const float* __restrict__ q, const float* __restrict__ k
   const int q0 = (p.causal ? q_blocks - 1 - qb_raw : qb_raw) * kBM;
   const int b = static_cast<int>(bh / p.heads_q), h = static_cast<int>(bh % p.heads_q);
   const int64_t kvh = static_cast<int64_t>(b) * p.heads_kv + h / (p.heads_q / p.heads_kv);
-  const float* kb = k + kvh * p.kv_head_stride;
-  const float* vb = v + kvh * p.kv_head_stride;
+  const T* kb = k + kvh * p.kv_head_stride;
+  const T* vb = v + kvh * p.kv_head_stride;
   const int n_all = (p.seq_kv + kBN - 1) / kBN;
   const int n_tiles = p.causal ? min(n_all, (q0 + kBM - 1 + p.q_offset) / kBN + 1) : n_all;
 
   auto prefetch = [&](int tile, int stage) {
-    const uint32_t ks = smem_base + stage * 2 * tile_floats<D>() * 4, vs = ks + tile_floats<D>() * 4;
+    const uint32_t ks = smem_base + stage * 2 * tile_bytes<T, D>(), vs = ks + tile_bytes<T, D>();
     for (int i = tid; i < kBN * CHUNKS; i += kThreads) {
-      const int r = i / CHUNKS, c4 = (i % CHUNKS) * 4;
+      const int r = i / CHUNKS, c4 = (i % CHUNKS) * VEC;
       const int key = tile * kBN + r;
       const bool ok = key < p.seq_kv;  // rows past the end are zero-filled: 0 * V must stay finite
       const int64_t off = ok ? static_cast<int64_t>(key) * D + c4 : 0;
-      cp::cp_async_16(ks + (r * PW + c4) * 4, kb + off, ok);
-      cp::cp_async_16(vs + (r * PW + c4) * 4, vb + off, ok);
+      cp::cp_async_16(ks + (r * PW + c4) * static_cast<int>(sizeof(T)), kb + off, ok);
+      cp::cp_async_16(vs + (r * PW + c4) * static_cast<int>(sizeof(T)), vb + off, ok);
     }
   };
   if (n_tiles > 0) prefetch(0, 0);
@@ -102,15 +116,15 @@ attention_tf32x3_kernel(const float* __restrict__ q, const float* __restrict__ k
   const int r0 = q0 + warp * 16 + gr, r1 = r0 + 8;
   float qa[KSTEPS][4];
   {
-    const float* q_r0 = q + bh * p.q_head_stride + static_cast<int64_t>(r0) * p.q_row_stride;
-    const float* q_r1 = q + bh * p.q_head_stride + static_cast<int64_t>(r1) * p.q_row_stride;
+    const T* q_r0 = q + bh * p.q_head_stride + static_cast<int64_t>(r0) * p.q_row_stride;
+    const T* q_r1 = q + bh * p.q_head_stride + static_cast<int64_t>(r1) * p.q_row_stride;
     const bool ok0 = r0 < p.seq, ok1 = r1 < p.seq;
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk) {
-      qa[kk][0] = ok0 ? __ldg(q_r0 + kk * 8 + tq) : 0.f;
-      qa[kk][1] = ok1 ? __ldg(q_r1 + kk * 8 + tq) : 0.f;
-      qa[kk][2] = ok0 ? __ldg(q_r0 + kk * 8 + tq + 4) : 0.f;
-      qa[kk][3] = ok1 ? __ldg(q_r1 + kk * 8 + tq + 4) : 0.f;
+      qa[kk][0] = ok0 ? to_f32(q_r0[kk * 8 + tq]) : 0.f;
+      qa[kk][1] = ok1 ? to_f32(q_r1[kk * 8 + tq]) : 0.f;
+      qa[kk][2] = ok0 ? to_f32(q_r0[kk * 8 + tq + 4]) : 0.f;
+      qa[kk][3] = ok1 ? to_f32(q_r1[kk * 8 + tq + 4]) : 0.f;
     }
   }
   // last visible key of the two rows
@@ -130,8 +144,8 @@ attention_tf32x3_kernel(const float* __restrict__ q, const float* __restrict__ k
     cp::cp_async_commit();
     cp::cp_async_wait<1>();  // tile t has landed (this thread's copies) ...
     __syncthreads();         // ... and everybody's
-    const float* ks = smem_f + (t & 1) * 2 * tile_floats<D>();
-    const float* vs = ks + tile_floats<D>();
+    const T* ks = reinterpret_cast<const T*>(smem_f + (t & 1) * 2 * tile_bytes<T, D>());
+    const T* vs = reinterpret_cast<const T*>(smem_f + (t & 1) * 2 * tile_bytes<T, D>() + tile_bytes<T, D>());
 
     // S = Q K^T for 16 rows x 64 keys: b0 (k tq, key gr), b1 (k tq+4, key gr) of every 8-key group
     float s[kBN / 8][4];
@@ -143,11 +157,14 @@ attention_tf32x3_kernel(const float* __restrict__ q, const float* __restrict__ k
     for (int kk = 0; kk < KSTEPS; ++kk) {
       uint32_t ah[4], al[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) split(qa[kk][e], ah[e], al[e]);
+      for (int e = 0; e < 4; ++e) {
+        if (kExact) ah[e] = __float_as_uint(qa[kk][e]), al[e] = 0u;
+        else split(qa[kk][e], ah[e], al[e]);
+      }
 #pragma unroll
       for (int n = 0; n < kBN / 8; ++n) {
-        const float* kr = ks + (n * 8 + gr) * PW + kk * 8 + tq;
-        mma_3x(s[n], ah, al, kr[0], kr[4]);
+        const T* kr = ks + (n * 8 + gr) * PW + kk * 8 + tq;
+        mma_split<kExact, kExact>(s[n], ah, al, to_f32(kr[0]), to_f32(kr[4]));
       }
     }
     // scale to log2 units, mask, row maxima (c0, c1: row gr, keys 2tq, 2tq+1; c2, c3: row gr+8)
@@ -200,9 +217,9 @@ attention_tf32x3_kernel(const float* __restrict__ q, const float* __restrict__ k
       split(s[n][2], ah[1], al[1]);
       split(s[n][1], ah[2], al[2]);
       split(s[n][3], ah[3], al[3]);
-      const float* vr = vs + (n * 8 + 2 * tq) * PW + gr;
+      const T* vr = vs + (n * 8 + 2 * tq) * PW + gr;
 #pragma unroll
-      for (int i = 0; i < KSTEPS; ++i) mma_3x(oacc[i], ah, al, vr[i * 8], vr[PW + i * 8]);
+      for (int i = 0; i < KSTEPS; ++i) mma_split<false, kExact>(oacc[i], ah, al, to_f32(vr[i * 8]), to_f32(vr[PW + i * 8]));
     }
     __syncthreads();  // the stage is refilled at the top of the next iteration
   }
@@ -213,12 +230,18 @@ attention_tf32x3_kernel(const float* __restrict__ q, const float* __restrict__ k
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
-  float* o_r0 = o + bh * p.o_head_stride + static_cast<int64_t>(r0) * p.o_row_stride + 2 * tq;
-  float* o_r1 = o + bh * p.o_head_stride + static_cast<int64_t>(r1) * p.o_row_stride + 2 * tq;
+  T* o_r0 = o + bh * p.o_head_stride + static_cast<int64_t>(r0) * p.o_row_stride + 2 * tq;
+  T* o_r1 = o + bh * p.o_head_stride + static_cast<int64_t>(r1) * p.o_row_stride + 2 * tq;
 #pragma unroll
   for (int i = 0; i < KSTEPS; ++i) {
-    if (r0 < p.seq) *reinterpret_cast<float2*>(o_r0 + i * 8) = make_float2(oacc[i][0] * inv0, oacc[i][1] * inv0);
-    if (r1 < p.seq) *reinterpret_cast<float2*>(o_r1 + i * 8) = make_float2(oacc[i][2] * inv1, oacc[i][3] * inv1);
+    if (r0 < p.seq) {
+      o_r0[i * 8] = from_f32<T>(oacc[i][0] * inv0);
+      o_r0[i * 8 + 1] = from_f32<T>(oacc[i][1] * inv0);
+    }
+    if (r1 < p.seq) {
+      o_r1[i * 8] = from_f32<T>(oacc[i][2] * inv1);
+      o_r1[i * 8 + 1] = from_f32<T>(oacc[i][3] * inv1);
+    }
   }
 }
 

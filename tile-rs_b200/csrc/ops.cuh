@@ -596,35 +596,41 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
 // ---------------------------------------------------------------------------
 // attention
 // ---------------------------------------------------------------------------
-// f32 tensors with head_dim 32, 64, 96 or 128 and 16-byte aligned rows: tensor cores, three TF32 products per product.
+// Head dims 32, 64, 96 (and 128 for f32) with 16-byte aligned rows: the warp-level tensor-core kernel (f32: three
+// TF32 products per product; 16-bit data, whose values are TF32 numbers already: one for Q K^T, two for P V).
+template <typename T>
 inline bool attention_tf32x3_ok(const attn_simt::Params& p, const void* q, const void* k, const void* v, const void* o) {
-  return (p.head_dim == 32 || p.head_dim == 64 || p.head_dim == 96 || p.head_dim == 128) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) &&
-         p.q_row_stride % 4 == 0 && p.q_head_stride % 4 == 0 && p.kv_head_stride % 4 == 0 && p.o_row_stride % 4 == 0 &&
-         p.o_head_stride % 4 == 0;
+  constexpr int64_t vec = 16 / static_cast<int64_t>(sizeof(T));
+  const bool dim_ok = p.head_dim == 32 || p.head_dim == 64 || p.head_dim == 96 || (sizeof(T) == 4 && p.head_dim == 128);
+  return dim_ok && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && p.q_row_stride % vec == 0 &&
+         p.q_head_stride % vec == 0 && p.kv_head_stride % vec == 0 && p.o_row_stride % vec == 0 && p.o_head_stride % vec == 0;
 }
-template <int D>
-inline int32_t attention_tf32x3_launch_d(std::string* err, const attn_simt::Params& p, const float* q, const float* k,
-                                         const float* v, float* o, cudaStream_t s) {
+template <typename T, int D>
+inline int32_t attention_tf32x3_launch_d(std::string* err, const attn_simt::Params& p, const T* q, const T* k,
+                                         const T* v, T* o, cudaStream_t s) {
   namespace at = attn_tf32;
   const int64_t grid = static_cast<int64_t>((p.seq + at::kBM - 1) / at::kBM) * p.batch * p.heads_q;
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many query blocks for one launch");
-  auto kern = at::attention_tf32x3_kernel<D>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, at::smem_bytes<D>());
+  auto kern = at::attention_tf32x3_kernel<T, D>;
+  constexpr int smem = at::smem_bytes<T, D>();
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_tf32x3_kernel)");
-  kern<<<static_cast<unsigned>(grid), at::kThreads, at::smem_bytes<D>(), s>>>(q, k, v, o, p);
+  kern<<<static_cast<unsigned>(grid), at::kThreads, smem, s>>>(q, k, v, o, p);
   return cuda_ok(err, cudaGetLastError(), "attention_tf32x3_kernel launch");
 }
+template <typename T>
 inline int32_t attention_tf32x3_launch(std::string* err, const attn_simt::Params& p, const void* q, const void* k,
                                        const void* v, void* o, cudaStream_t s) {
-  const float* qf = static_cast<const float*>(q);
-  const float* kf = static_cast<const float*>(k);
-  const float* vf = static_cast<const float*>(v);
-  float* of = static_cast<float*>(o);
+  const T* qf = static_cast<const T*>(q);
+  const T* kf = static_cast<const T*>(k);
+  const T* vf = static_cast<const T*>(v);
+  T* of = static_cast<T*>(o);
+  if constexpr (sizeof(T) == 4)
+    if (p.head_dim == 128) return attention_tf32x3_launch_d<T, 128>(err, p, qf, kf, vf, of, s);
   switch (p.head_dim) {
-    case 128: return attention_tf32x3_launch_d<128>(err, p, qf, kf, vf, of, s);
-    case 96: return attention_tf32x3_launch_d<96>(err, p, qf, kf, vf, of, s);
-    case 64: return attention_tf32x3_launch_d<64>(err, p, qf, kf, vf, of, s);
-    default: return attention_tf32x3_launch_d<32>(err, p, qf, kf, vf, of, s);
+    case 96: return attention_tf32x3_launch_d<T, 96>(err, p, qf, kf, vf, of, s);
+    case 64: return attention_tf32x3_launch_d<T, 64>(err, p, qf, kf, vf, of, s);
+    default: return attention_tf32x3_launch_d<T, 32>(err, p, qf, kf, vf, of, s);
   }
 }
 
@@ -635,8 +641,7 @@ inline int32_t attention_simt_launch(std::string* err, const tsm100_attention_de
   attn_simt::Params p{d->seq, d->head_dim, d->heads_q, d->heads_kv, d->batch, d->causal,
                       static_cast<float>(1.0 / std::sqrt(static_cast<double>(d->head_dim))),
                       d->seq, 0, d->head_dim, sd, sd, d->head_dim, sd};
-  if constexpr (std::is_same<T, float>::value)
-    if (attention_tf32x3_ok(p, q, k, v, o)) return attention_tf32x3_launch(err, p, q, k, v, o, s);
+  if (attention_tf32x3_ok<T>(p, q, k, v, o)) return attention_tf32x3_launch<T>(err, p, q, k, v, o, s);
   const int64_t rows = static_cast<int64_t>(d->batch) * d->heads_q * d->seq;
   const int64_t grid = (rows + attn_simt::kWarps - 1) / attn_simt::kWarps;
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many query rows for one launch");
@@ -656,8 +661,7 @@ inline int32_t attention_prefill_simt_launch(std::string* err, const tsm100_atte
                       static_cast<float>(1.0 / std::sqrt(static_cast<double>(d->head_dim))),
                       d->start_pos + d->seq_len, d->start_pos, hd, d->head_dim,
                       static_cast<int64_t>(d->max_seq) * d->head_dim, hd, d->head_dim};
-  if constexpr (std::is_same<T, float>::value)
-    if (attention_tf32x3_ok(p, q, k, v, o)) return attention_tf32x3_launch(err, p, q, k, v, o, s);
+  if (attention_tf32x3_ok<T>(p, q, k, v, o)) return attention_tf32x3_launch<T>(err, p, q, k, v, o, s);
   const int64_t rows = static_cast<int64_t>(d->heads_q) * d->seq_len;
   const int64_t grid = (rows + attn_simt::kWarps - 1) / attn_simt::kWarps;
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: too many query rows for one launch");
