@@ -9,10 +9,11 @@
 // the truncation of lo are below 2^-21 of |a||b|, the size of f32 rounding itself.
 //
 // 64 x 64 output tile per CTA, 4 warps of 32 x 32 (2 x 4 mma.sync.m16n8k8.tf32 tiles), 32-deep
-// K slices through a three-stage cp.async ring; rows padded so that fragment loads are
+// K slices through a three- or four-stage cp.async ring; rows padded so that fragment loads are
 // conflict-free.  A CTA cluster may split K (the 512^3 configuration has only 64 output tiles
 // for 148 SMs): every CTA of a cluster accumulates its share of K and the partial tiles are
-// added through distributed shared memory in rank order, so the result does not depend on timing.
+// added through distributed shared memory in rank order (every CTA its share of the tile), so the result
+// does not depend on timing.
 // Needs 16-byte aligned rows: K % 4 == 0, and N % 4 == 0 for row-major B.
 #pragma once
 
@@ -23,7 +24,8 @@ namespace tsm100 {
 namespace gemm_tf32x3 {
 
 constexpr int kBM = 64, kBN = 64, kBK = 32;
-constexpr int kStages = 3;
+constexpr int kStages = 3;       // large problems (several CTAs per SM)
+constexpr int kStagesSplit = 4;  // K split over a cluster: few slices per CTA, all of them in flight at once
 constexpr int kThreads = 128;
 constexpr int kPitchA = kBK + 4;   // floats: rows 4 banks apart -> A fragment loads hit 32 banks
 constexpr int kPitchB = kBN + 8;   // row-major B [K][N]: rows 8 banks apart
@@ -31,7 +33,7 @@ constexpr int kPitchBT = kBK + 4;  // B stored [N][K]: same pattern as A
 constexpr int kABytes = kBM * kPitchA * 4;
 constexpr int kBBytes = (kBK * kPitchB > kBN * kPitchBT ? kBK * kPitchB : kBN * kPitchBT) * 4;
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kSmemBytes = kStages * kStageBytes;   // 55296: the 64 x 64 f32 tile for the cluster sum (16 KiB) overlays it
+constexpr int kSmemBytes = kStagesSplit * kStageBytes;   // the most a launch asks for; the 64 x 64 f32 tile for the cluster sum (16 KiB) overlays the ring
 constexpr int kMaxSplit = 4;
 
 struct Params {
@@ -48,7 +50,7 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool kBTransposed>
+template <bool kBTransposed, int STAGES = kStages>
 __global__ void __launch_bounds__(kThreads)
 gemm_tf32x3_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c, const Params p) {
   namespace cp = attn_decode::mma;
@@ -101,17 +103,17 @@ gemm_tf32x3_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
       for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
 
 #pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < n_slices) prefetch(s, s);
     cp::cp_async_commit();
   }
   for (int s = 0; s < n_slices; ++s) {
-    cp::cp_async_wait<kStages - 2>();  // slice s has landed (for this thread's copies)
-    __syncthreads();                   // ... for everybody's; and the stage refilled below is no longer read
-    if (s + kStages - 1 < n_slices) prefetch(s + kStages - 1, (s + kStages - 1) % kStages);
+    cp::cp_async_wait<STAGES - 2>();  // slice s has landed (for this thread's copies)
+    __syncthreads();                  // ... for everybody's; and the stage refilled below is no longer read
+    if (s + STAGES - 1 < n_slices) prefetch(s + STAGES - 1, (s + STAGES - 1) % STAGES);
     cp::cp_async_commit();
-    const float* as = reinterpret_cast<const float*>(smem + (s % kStages) * kStageBytes);
-    const float* bs = reinterpret_cast<const float*>(smem + (s % kStages) * kStageBytes + kABytes);
+    const float* as = reinterpret_cast<const float*>(smem + (s % STAGES) * kStageBytes);
+    const float* bs = reinterpret_cast<const float*>(smem + (s % STAGES) * kStageBytes + kABytes);
 #pragma unroll
     for (int kk = 0; kk < kBK / 8; ++kk) {
       uint32_t ah[2][4], al[2][4], bh[4][2], bl[4][2];
@@ -166,14 +168,27 @@ gemm_tf32x3_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
         tile_s[(r + 8) * kBN + cc + 1] = acc[i][j][3];
       }
     ptx::cluster_sync_all();
-    if (rank == 0) {
+    {
+      // every CTA adds its share of the tile (pairs of columns; N is even), all its remote loads in flight
+      // together, ranks in rank order: a single CTA walking the whole tile spent more time here than in the MMAs
       float* cb = c + static_cast<int64_t>(bz) * p.m * p.n;
-      for (int i = tid; i < kBM * kBN; i += kThreads) {
-        const int r = i / kBN, cc = i % kBN;
+      const int per = kBM * kBN / 2 / static_cast<int>(splits);  // column pairs per rank
+      for (int i = static_cast<int>(rank) * per + tid; i < (static_cast<int>(rank) + 1) * per; i += kThreads) {
+        const int r = (2 * i) / kBN, cc = (2 * i) % kBN;
         if (m0 + r >= p.m || n0 + cc >= p.n) continue;
-        float v = tile_s[i];
-        for (uint32_t q = 1; q < splits; ++q) v += ptx::ld_shared_cluster_f32(ptx::mapa_shared(smem_base + i * 4, q));
-        cb[static_cast<int64_t>(m0 + r) * p.n + n0 + cc] = v;
+        float2 part[kMaxSplit];
+#pragma unroll
+        for (int q = 0; q < kMaxSplit; ++q)
+          part[q] = q < static_cast<int>(splits) ? ptx::ld_shared_cluster_f32x2(ptx::mapa_shared(smem_base + i * 8, static_cast<uint32_t>(q)))
+                                                  : make_float2(0.f, 0.f);
+        float2 v = part[0];
+#pragma unroll
+        for (int q = 1; q < kMaxSplit; ++q)
+          if (q < static_cast<int>(splits)) {
+            v.x += part[q].x;
+            v.y += part[q].y;
+          }
+        *reinterpret_cast<float2*>(cb + static_cast<int64_t>(m0 + r) * p.n + n0 + cc) = v;
       }
     }
     ptx::cluster_sync_all();  // nobody leaves while its shared memory may still be read

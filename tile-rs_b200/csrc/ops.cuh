@@ -414,9 +414,10 @@ inline int32_t gemm_tf32x3_launch(std::string* err, const tsm100_gemm_desc* d, c
   if (st != TSM100_OK) return st;
   const int64_t tiles = ((d->m + g::kBM - 1) / g::kBM) * ((d->n + g::kBN - 1) / g::kBN) * d->batch;
   if (tiles * g::kMaxSplit > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "gemm: too many tiles for one launch");
-  // fewer tiles than SMs: a cluster splits K, as long as every CTA keeps at least four 32-deep slices
+  // fewer tiles than SMs: a cluster splits K while all CTAs still fit the GPU at once (two per SM) and every CTA
+  // keeps at least four 32-deep slices
   int splits = 1;
-  while (splits < g::kMaxSplit && tiles * splits * 2 <= sms && d->k / (2 * splits) >= 4 * g::kBK) splits *= 2;
+  while (splits < g::kMaxSplit && tiles * splits * 2 <= 2 * sms && d->k / (2 * splits) >= 4 * g::kBK) splits *= 2;
   g::Params p;
   p.m = static_cast<int32_t>(d->m);
   p.n = static_cast<int32_t>(d->n);
@@ -432,21 +433,20 @@ inline int32_t gemm_tf32x3_launch(std::string* err, const tsm100_gemm_desc* d, c
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cfg.blockDim = dim3(g::kThreads);
-  cfg.dynamicSmemBytes = g::kSmemBytes;
+  const int stages = splits > 1 ? g::kStagesSplit : g::kStages;
+  cfg.dynamicSmemBytes = static_cast<size_t>(stages) * g::kStageBytes;
   cfg.stream = s;
   cfg.gridDim = dim3(static_cast<unsigned>(tiles * splits));
+  auto launch = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), p);
+  };
   cudaError_t e;
-  if (d->b_transposed) {
-    auto kern = g::gemm_tf32x3_kernel<true>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
-    if (e == cudaSuccess)
-      e = cudaLaunchKernelEx(&cfg, kern, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), p);
-  } else {
-    auto kern = g::gemm_tf32x3_kernel<false>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
-    if (e == cudaSuccess)
-      e = cudaLaunchKernelEx(&cfg, kern, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), p);
-  }
+  if (d->b_transposed)
+    e = splits > 1 ? launch(g::gemm_tf32x3_kernel<true, g::kStagesSplit>) : launch(g::gemm_tf32x3_kernel<true, g::kStages>);
+  else
+    e = splits > 1 ? launch(g::gemm_tf32x3_kernel<false, g::kStagesSplit>) : launch(g::gemm_tf32x3_kernel<false, g::kStages>);
   return cuda_ok(err, e, "gemm_tf32x3_kernel launch");
 }
 

@@ -256,6 +256,11 @@ __device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
   return v;
 }
+__device__ __forceinline__ float2 ld_shared_cluster_f32x2(uint32_t cluster_addr) {  // 8-byte aligned
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(cluster_addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ uint32_t cluster_nctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
