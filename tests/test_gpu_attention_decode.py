@@ -23,7 +23,8 @@ def run_decode(dev, capi, q, k, v, seq_len, dtype):
 # (batch, heads_q, heads_kv, seq_len, max_seq, head_dim): group sizes 1, 2, 3 (padded to 4), 8 and 12 (two passes);
 # ranges that end inside a warp's slots; one position; long caches that are split over a cluster
 CASES = [(1, 1, 1, 1, 8, 64), (2, 4, 4, 33, 40, 128), (1, 8, 4, 100, 128, 64), (2, 6, 2, 257, 300, 128), (1, 16, 2, 1000, 1024, 128),
-         (1, 24, 2, 515, 600, 64), (3, 8, 1, 4096, 4096, 128), (1, 2, 2, 20000, 20480, 128), (1, 8, 1, 16384, 16384, 64)]
+         (1, 24, 2, 515, 600, 64), (3, 8, 1, 4096, 4096, 128), (1, 2, 2, 20000, 20480, 128), (1, 8, 1, 16384, 16384, 64),
+         (2, 10, 2, 77, 80, 128), (1, 40, 2, 1029, 1100, 64)]  # f32 groups of 5 and 20 (two passes): tensor cores, three TF32 products
 
 
 @pytest.mark.parametrize("b,hq,hkv,n,max_seq,d", CASES)

@@ -530,5 +530,225 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
 }
 
 }  // namespace mma
+// ===========================================================================
+// f32 caches on tensor cores, for groups of several query heads (one head per cache is served as
+// well by the FP32-pipe kernel above).  The same structure as the 16-bit kernel: the heads of a
+// group are the M = 16 rows, a warp streams its own tiles of 8 positions through a cp.async ring,
+// online softmax on the accumulator fragments, warp records merged through shared memory and the
+// CTAs of the cluster through distributed shared memory.  The arithmetic keeps f32 accuracy (the
+// oracle is matched to 1e-5): mma.sync.m16n8k8.tf32 with every operand split into hi + lo and three
+// products per product, as in gemm_tf32x3.cuh.  B fragments are plain 32-bit loads from rows padded
+// by 16 bytes (32 banks); the accumulator fragment of S is the A fragment of P V with the k index
+// tq -> position 2tq, tq + 4 -> position 2tq + 1, applied to the V row addresses.
+// ===========================================================================
+namespace tf32 {
+
+constexpr int kTilePos = 8;
+constexpr int kRows = 16;
+
+template <int D>
+constexpr int pitch_words() { return D + 4; }
+template <int D>
+constexpr int stage_bytes() { return 2 * kTilePos * pitch_words<D>() * 4; }  // K tile + V tile
+template <int D, int STAGES, int WARPS>
+constexpr int smem_bytes() { return WARPS * STAGES * stage_bytes<D>() + kRows * (D + 2) * 4; }
+
+__device__ __forceinline__ void split(float x, uint32_t& hi, uint32_t& lo) {
+  hi = __float_as_uint(x) & 0xffffe000u;          // what the tensor core reads of x
+  lo = __float_as_uint(x - __uint_as_float(hi));  // exact; the tensor core reads its top 11 bits
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_3x(float (&d)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4], float b0, float b1) {
+  uint32_t b0h, b0l, b1h, b1l;
+  split(b0, b0h, b0l);
+  split(b1, b1h, b1l);
+  mma_tf32(d, al, b0h, b1h);  // small terms first
+  mma_tf32(d, ah, b0l, b1l);
+  mma_tf32(d, ah, b0h, b1h);
+}
+
+template <int D, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_tf32_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
+                             float* __restrict__ o, const Params p) {
+  namespace cp = mma;  // cp.async helpers
+  constexpr int kWarps = WARPS, kThreads = WARPS * 32;
+  constexpr int PW = pitch_words<D>();
+  constexpr int KSTEPS = D / 8;      // k-steps of Q K^T; 8-wide output tiles of P V
+  constexpr int REC = D + 2;
+  constexpr int CHUNKS = D / 4;      // 16-byte pieces per cache row
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  uint8_t* ring = smem_raw;                                           // [warp][stage][K | V][8 rows][PW floats]
+  float* mine = reinterpret_cast<float*>(smem_raw + kWarps * STAGES * stage_bytes<D>());   // [16][REC]
+  constexpr int WARP_FLOATS = STAGES * stage_bytes<D>() / 4;          // a warp's ring share, reused for its record [16][REC]
+  static_assert(kRows * REC <= WARP_FLOATS, "a warp's record must fit into its ring share");
+  float* part = reinterpret_cast<float*>(ring);                       // warp w's record at part + w * WARP_FLOATS
+
+  const uint32_t rank = ptx::cluster_ctarank(), splits = ptx::cluster_nctarank();
+  const int unit = blockIdx.x / splits;
+  const int b = unit / p.heads_kv, g = unit % p.heads_kv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gr = lane >> 2, tq = lane & 3;   // fragment row group and column pair
+  const int h0 = g * p.group + p.head_base;
+
+  const int chunk = ((p.seq_len + static_cast<int>(splits) - 1) / static_cast<int>(splits) + 63) & ~63;
+  const int p_begin = static_cast<int>(rank) * chunk;
+  const int p_end = min(p.seq_len, p_begin + chunk);
+  const int n_tiles = p_end > p_begin ? (p_end - p_begin + kTilePos - 1) / kTilePos : 0;
+  const int64_t cache_off = (static_cast<int64_t>(b) * p.heads_kv + g) * p.max_seq * D;
+  const float* kbase = kc + cache_off;
+  const float* vbase = vc + cache_off;
+  const uint32_t ring_w = ptx::smem_u32(ring) + warp * STAGES * stage_bytes<D>();
+
+  auto prefetch = [&](int tile, int stage) {  // this warp's tile `tile` of the CTA's range into its ring stage
+    const int row0 = p_begin + tile * kTilePos;
+    const uint32_t dst = ring_w + stage * stage_bytes<D>();
+#pragma unroll
+    for (int c = lane; c < kTilePos * CHUNKS; c += 32) {
+      const int r = c / CHUNKS, cc = c % CHUNKS;
+      const bool ok = row0 + r < p_end;  // rows past the range are zero-filled: they carry no weight, and 0 * V stays finite
+      const int64_t src = (static_cast<int64_t>(ok ? row0 + r : p_begin)) * D + cc * 4;
+      cp::cp_async_16(dst + (r * PW + cc * 4) * 4, kbase + src, ok);
+      cp::cp_async_16(dst + ((kTilePos + r) * PW + cc * 4) * 4, vbase + src, ok);
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {  // the first tiles are on their way before anything else is read
+    if (warp + i * kWarps < n_tiles) prefetch(warp + i * kWarps, i);
+    cp::cp_async_commit();
+  }
+  // A fragments of Q (rows beyond heads_here zero): a0 (row gr, k tq), a1 (row gr+8, k tq), a2 (row gr, k tq+4), a3 (row gr+8, k tq+4)
+  float qa[KSTEPS][4];
+  {
+    const float* r0 = q + (static_cast<int64_t>(b) * p.heads_q + h0 + gr) * D;
+    const float* r1 = r0 + 8 * D;
+    const bool ok0 = gr < p.heads_here, ok1 = gr + 8 < p.heads_here;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      qa[kk][0] = ok0 ? __ldg(r0 + kk * 8 + tq) : 0.f;
+      qa[kk][1] = ok1 ? __ldg(r1 + kk * 8 + tq) : 0.f;
+      qa[kk][2] = ok0 ? __ldg(r0 + kk * 8 + tq + 4) : 0.f;
+      qa[kk][3] = ok1 ? __ldg(r1 + kk * 8 + tq + 4) : 0.f;
+    }
+  }
+
+  float oacc[KSTEPS][4];
+#pragma unroll
+  for (int j = 0; j < KSTEPS; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oacc[j][e] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows gr and gr + 8 (this thread's share of the sums)
+  const float sl2 = p.scale_log2;
+
+  int stage = 0;
+  for (int t = warp; t < n_tiles; t += kWarps, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+    if (t + (STAGES - 1) * kWarps < n_tiles) prefetch(t + (STAGES - 1) * kWarps, stage == 0 ? STAGES - 1 : stage - 1);
+    cp::cp_async_commit();
+    cp::cp_async_wait<STAGES - 1>();  // everything but the newest STAGES - 1 groups: this tile has landed
+    __syncwarp();
+    const float* ks = reinterpret_cast<const float*>(ring + warp * STAGES * stage_bytes<D>() + stage * stage_bytes<D>());
+    const float* vs = ks + kTilePos * PW;
+    float s[4] = {0.f, 0.f, 0.f, 0.f};  // (row gr, pos 2tq), (gr, 2tq+1), (gr+8, 2tq), (gr+8, 2tq+1)
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      uint32_t ah[4], al[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) split(qa[kk][e], ah[e], al[e]);
+      const float* kr = ks + gr * PW + kk * 8 + tq;  // b0 (k tq, position gr), b1 (k tq+4, position gr)
+      mma_3x(s, ah, al, kr[0], kr[4]);
+    }
+    // scale to log2 units; positions past the end of the range carry no weight
+    const int pos = p_begin + t * kTilePos + 2 * tq;
+    s[0] = pos < p_end ? s[0] * sl2 : -INFINITY;
+    s[1] = pos + 1 < p_end ? s[1] * sl2 : -INFINITY;
+    s[2] = pos < p_end ? s[2] * sl2 : -INFINITY;
+    s[3] = pos + 1 < p_end ? s[3] * sl2 : -INFINITY;
+    float t0 = fmaxf(s[0], s[1]), t1 = fmaxf(s[2], s[3]);
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+    const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);  // finite: a tile has at least one valid position
+    const float a0 = ptx::ex2_approx(m0 - n0), a1 = ptx::ex2_approx(m1 - n1);  // first tile: 2^(-inf) = 0
+    m0 = n0;
+    m1 = n1;
+    const float p0 = ptx::ex2_approx(s[0] - n0), p1 = ptx::ex2_approx(s[1] - n0);
+    const float p2 = ptx::ex2_approx(s[2] - n1), p3 = ptx::ex2_approx(s[3] - n1);
+    l0 = fmaf(l0, a0, p0 + p1);
+    l1 = fmaf(l1, a1, p2 + p3);
+    if (__any_sync(0xffffffffu, a0 != 1.0f || a1 != 1.0f)) {  // a maximum moved somewhere in the warp: rescale
+#pragma unroll
+      for (int j = 0; j < KSTEPS; ++j) {
+        oacc[j][0] *= a0;
+        oacc[j][1] *= a0;
+        oacc[j][2] *= a1;
+        oacc[j][3] *= a1;
+      }
+    }
+    // O += P V: a0 (row gr, k tq -> position 2tq), a1 (row gr+8, same), a2 (row gr, k tq+4 -> position 2tq+1), a3
+    uint32_t ah[4], al[4];
+    split(p0, ah[0], al[0]);
+    split(p2, ah[1], al[1]);
+    split(p1, ah[2], al[2]);
+    split(p3, ah[3], al[3]);
+    const float* vr = vs + 2 * tq * PW + gr;  // b0 (position 2tq, d 8j + gr), b1 (position 2tq + 1, d 8j + gr)
+#pragma unroll
+    for (int j = 0; j < KSTEPS; ++j) mma_3x(oacc[j], ah, al, vr[j * 8], vr[PW + j * 8]);
+    __syncwarp();  // the stage is refilled at the top of the next iteration; every lane is done reading it
+  }
+  cp::cp_async_wait<0>();
+  __syncwarp();  // the warp's ring share is free: it now receives the warp's record
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+  // warp records -> shared memory: row r of warp w at part[w * WARP_FLOATS + r * REC]: O[D], max, sum
+  {
+    float* r0 = part + warp * WARP_FLOATS + gr * REC;
+    float* r1 = part + warp * WARP_FLOATS + (gr + 8) * REC;
+#pragma unroll
+    for (int j = 0; j < KSTEPS; ++j) {
+      r0[j * 8 + 2 * tq] = oacc[j][0];
+      r0[j * 8 + 2 * tq + 1] = oacc[j][1];
+      r1[j * 8 + 2 * tq] = oacc[j][2];
+      r1[j * 8 + 2 * tq + 1] = oacc[j][3];
+    }
+    if (tq == 0) {
+      r0[D] = m0;
+      r0[D + 1] = l0;
+      r1[D] = m1;
+      r1[D + 1] = l1;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < kRows * D; i += kThreads) {
+    const int hh = i / D, dd = i % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, part[w * WARP_FLOATS + hh * REC + D]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float* rec = part + w * WARP_FLOATS + hh * REC;
+      const float wgt = rec[D] == -INFINITY ? 0.f : ptx::ex2_approx(rec[D] - mm);  // a warp without tiles carries no weight
+      ll = fmaf(rec[D + 1], wgt, ll);
+      oo = fmaf(rec[dd], wgt, oo);
+    }
+    mine[hh * REC + dd] = oo;
+    if (dd == 0) {
+      mine[hh * REC + D] = mm;
+      mine[hh * REC + D + 1] = ll;
+    }
+  }
+  ptx::cluster_sync_all();
+  cluster_merge<float, kRows, D, kThreads>(mine, part, rank, splits, p.heads_here, o + (static_cast<int64_t>(b) * p.heads_q + h0) * D);
+  ptx::cluster_sync_all();  // nobody leaves while its shared memory may still be read
+}
+
+}  // namespace tf32
 }  // namespace attn_decode
 }  // namespace tsm100

@@ -763,6 +763,19 @@ inline int32_t attention_decode_launch(std::string* err, const tsm100_attention_
   return cuda_ok(err, e, "attention_decode_kernel launch");
 }
 
+// The tensor-core decode kernel for an element type: mma.sync on 16-bit caches, three TF32 products on f32 caches.
+template <typename T, int D, int STAGES, int WARPS>
+struct DecodeTc {
+  static auto kernel() {
+    if constexpr (sizeof(T) == 4) return attn_decode::tf32::attention_decode_tf32_kernel<D, STAGES, WARPS>;
+    else return attn_decode::mma::attention_decode_mma_kernel<T, D, STAGES, WARPS>;
+  }
+  static constexpr int smem() {
+    if constexpr (sizeof(T) == 4) return attn_decode::tf32::smem_bytes<D, STAGES, WARPS>();
+    else return attn_decode::mma::smem_bytes<D, STAGES, WARPS>();
+  }
+};
+
 template <typename T, int D, int STAGES, int WARPS>
 inline int32_t attention_decode_mma_launch(std::string* err, const tsm100_attention_decode_desc* d, const T* q, const T* k,
                                            const T* v, T* o, int head_base, int heads_here, int splits, cudaStream_t s) {
@@ -777,8 +790,8 @@ inline int32_t attention_decode_mma_launch(std::string* err, const tsm100_attent
   p.head_base = head_base;
   p.heads_here = heads_here;
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
-  auto kern = ad::mma::attention_decode_mma_kernel<T, D, STAGES, WARPS>;
-  constexpr int smem = ad::mma::smem_bytes<D, STAGES, WARPS>();
+  auto kern = DecodeTc<T, D, STAGES, WARPS>::kernel();
+  constexpr int smem = DecodeTc<T, D, STAGES, WARPS>::smem();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_decode_mma_kernel)");
   if (splits > ad::kMaxSplits) {
@@ -812,8 +825,8 @@ inline int decode_lone_clusters(int size) {
   int& slot = cached[dev][size > ad::kMaxSplits ? 1 : 0];
   if (size != ad::kMaxSplits && size != ad::kMaxSplitsWide) return 0;
   if (slot == 0) {
-    auto kern = ad::mma::attention_decode_mma_kernel<T, D, 3, 8>;
-    constexpr int smem = ad::mma::smem_bytes<D, 3, 8>();
+    auto kern = DecodeTc<T, D, 3, 8>::kernel();
+    constexpr int smem = DecodeTc<T, D, 3, 8>::smem();
     int clusters = 0;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
@@ -835,6 +848,10 @@ inline int decode_lone_clusters(int size) {
   return slot - 1;
 }
 
+// f32 caches: from this many query heads per cache on, the tensor-core kernel (three TF32 products) is faster than
+// the FP32-pipe kernel, whose instruction count grows with the heads while the cache row is read once either way
+constexpr int kDecodeF32TensorCoreGroup = 5;
+
 template <typename T, int D>
 inline int32_t attention_decode_typed(std::string* err, const tsm100_attention_decode_desc* d, const void* q, const void* k,
                                       const void* v, void* o, cudaStream_t s) {
@@ -851,9 +868,9 @@ inline int32_t attention_decode_typed(std::string* err, const tsm100_attention_d
   const T* kp = static_cast<const T*>(k);
   const T* vp = static_cast<const T*>(v);
   T* op = static_cast<T*>(o);
-  if constexpr (sizeof(T) == 2) {
-    // 16-bit storage: tensor cores, up to 16 query heads of a group per pass; 4 warps x 16 positions per CTA,
-    // so the GPU is covered about four times before the ranges get shorter than 256 positions
+  if (sizeof(T) == 2 || group >= kDecodeF32TensorCoreGroup) {
+    // 16-bit storage, or f32 with several query heads per cache: tensor cores, up to 16 query heads of a group per
+    // pass; 4 warps per CTA, so the GPU is covered about four times before the ranges get shorter than 256 positions
     splits = 1;
     while (splits < attn_decode::kMaxSplits && units * splits < 4ll * sms && d->seq_len / (2 * splits) >= 256) splits *= 2;
     // a handful of sequences: clusters of 16 if the GPU holds all of them at once (one CTA per SM; a B200
