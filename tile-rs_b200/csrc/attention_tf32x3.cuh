@@ -69,6 +69,34 @@ __device__ __forceinline__ void mma_split(float (&d)[4], const uint32_t (&ah)[4]
   }
 }
 
+// The same for N independent accumulators that share A: the products are issued term by term across the group,
+// so that an MMA never waits for the one just before it (which writes the same accumulator).
+template <bool kExactA, bool kExactB, int N>
+__device__ __forceinline__ void mma_split_group(float (*d)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4],
+                                                const float (&b0)[N], const float (&b1)[N]) {
+  if (kExactB) {
+    if (!kExactA) {
+#pragma unroll
+      for (int n = 0; n < N; ++n) mma_tf32(d[n], al, __float_as_uint(b0[n]), __float_as_uint(b1[n]));
+    }
+#pragma unroll
+    for (int n = 0; n < N; ++n) mma_tf32(d[n], ah, __float_as_uint(b0[n]), __float_as_uint(b1[n]));
+  } else {
+    uint32_t b0h[N], b0l[N], b1h[N], b1l[N];
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+      split(b0[n], b0h[n], b0l[n]);
+      split(b1[n], b1h[n], b1l[n]);
+    }
+#pragma unroll
+    for (int n = 0; n < N; ++n) mma_tf32(d[n], al, b0h[n], b1h[n]);  // small terms first
+#pragma unroll
+    for (int n = 0; n < N; ++n) mma_tf32(d[n], ah, b0l[n], b1l[n]);
+#pragma unroll
+    for (int n = 0; n < N; ++n) mma_tf32(d[n], ah, b0h[n], b1h[n]);
+  }
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads)
 attention_tf32x3_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
@@ -161,11 +189,14 @@ attention_tf32x3_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
         if (kExact) ah[e] = __float_as_uint(qa[kk][e]), al[e] = 0u;
         else split(qa[kk][e], ah[e], al[e]);
       }
+      float kv0[kBN / 8], kv1[kBN / 8];
 #pragma unroll
       for (int n = 0; n < kBN / 8; ++n) {
         const T* kr = ks + (n * 8 + gr) * PW + kk * 8 + tq;
-        mma_split<kExact, kExact>(s[n], ah, al, to_f32(kr[0]), to_f32(kr[4]));
+        kv0[n] = to_f32(kr[0]);
+        kv1[n] = to_f32(kr[4]);
       }
+      mma_split_group<kExact, kExact, kBN / 8>(s, ah, al, kv0, kv1);
     }
     // scale to log2 units, mask, row maxima (c0, c1: row gr, keys 2tq, 2tq+1; c2, c3: row gr+8)
     const int key0 = t * kBN + 2 * tq;
@@ -218,8 +249,17 @@ attention_tf32x3_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
       split(s[n][1], ah[2], al[2]);
       split(s[n][3], ah[3], al[3]);
       const T* vr = vs + (n * 8 + 2 * tq) * PW + gr;
+      constexpr int G = KSTEPS % 8 == 0 ? 8 : 4;  // output tiles per group of independent accumulators
 #pragma unroll
-      for (int i = 0; i < KSTEPS; ++i) mma_split<false, kExact>(oacc[i], ah, al, to_f32(vr[i * 8]), to_f32(vr[PW + i * 8]));
+      for (int i0 = 0; i0 < KSTEPS; i0 += G) {
+        float vv0[G], vv1[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+          vv0[i] = to_f32(vr[(i0 + i) * 8]);
+          vv1[i] = to_f32(vr[PW + (i0 + i) * 8]);
+        }
+        mma_split_group<false, kExact, G>(oacc + i0, ah, al, vv0, vv1);
+      }
     }
     __syncthreads();  // the stage is refilled at the top of the next iteration
   }
