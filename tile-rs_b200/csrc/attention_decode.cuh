@@ -561,15 +561,6 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
   asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void mma_3x(float (&d)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4], float b0, float b1) {
-  uint32_t b0h, b0l, b1h, b1l;
-  split(b0, b0h, b0l);
-  split(b1, b1h, b1l);
-  mma_tf32(d, al, b0h, b1h);  // small terms first
-  mma_tf32(d, ah, b0l, b1l);
-  mma_tf32(d, ah, b0h, b1h);
-}
-
 template <int D, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_tf32_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
@@ -651,15 +642,34 @@ attention_decode_tf32_kernel(const float* __restrict__ q, const float* __restric
     __syncwarp();
     const float* ks = reinterpret_cast<const float*>(ring + warp * STAGES * stage_bytes<D>() + stage * stage_bytes<D>());
     const float* vs = ks + kTilePos * PW;
-    float s[4] = {0.f, 0.f, 0.f, 0.f};  // (row gr, pos 2tq), (gr, 2tq+1), (gr+8, 2tq), (gr+8, 2tq+1)
+    // Four partial sums (k-steps 4c, 4c+1, 4c+2, 4c+3), their products issued term by term across the four, so
+    // that an MMA never waits for the one just before it; (row gr, pos 2tq), (gr, 2tq+1), (gr+8, 2tq), (gr+8, 2tq+1)
+    float sp[4][4];
 #pragma unroll
-    for (int kk = 0; kk < KSTEPS; ++kk) {
-      uint32_t ah[4], al[4];
+    for (int c = 0; c < 4; ++c)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) split(qa[kk][e], ah[e], al[e]);
-      const float* kr = ks + gr * PW + kk * 8 + tq;  // b0 (k tq, position gr), b1 (k tq+4, position gr)
-      mma_3x(s, ah, al, kr[0], kr[4]);
+      for (int e = 0; e < 4; ++e) sp[c][e] = 0.f;
+#pragma unroll
+    for (int k4 = 0; k4 < KSTEPS; k4 += 4) {
+      uint32_t ah[4][4], al[4][4], b0h[4], b0l[4], b1h[4], b1l[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split(qa[k4 + c][e], ah[c][e], al[c][e]);
+        const float* kr = ks + gr * PW + (k4 + c) * 8 + tq;  // b0 (k tq, position gr), b1 (k tq+4, position gr)
+        split(kr[0], b0h[c], b0l[c]);
+        split(kr[4], b1h[c], b1l[c]);
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) mma_tf32(sp[c], al[c], b0h[c], b1h[c]);  // small terms first
+#pragma unroll
+      for (int c = 0; c < 4; ++c) mma_tf32(sp[c], ah[c], b0l[c], b1l[c]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) mma_tf32(sp[c], ah[c], b0h[c], b1h[c]);
     }
+    float s[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[e] = (sp[0][e] + sp[1][e]) + (sp[2][e] + sp[3][e]);
     // scale to log2 units; positions past the end of the range carry no weight
     const int pos = p_begin + t * kTilePos + 2 * tq;
     s[0] = pos < p_end ? s[0] * sl2 : -INFINITY;
@@ -696,7 +706,20 @@ attention_decode_tf32_kernel(const float* __restrict__ q, const float* __restric
     split(p3, ah[3], al[3]);
     const float* vr = vs + 2 * tq * PW + gr;  // b0 (position 2tq, d 8j + gr), b1 (position 2tq + 1, d 8j + gr)
 #pragma unroll
-    for (int j = 0; j < KSTEPS; ++j) mma_3x(oacc[j], ah, al, vr[j * 8], vr[PW + j * 8]);
+    for (int j0 = 0; j0 < KSTEPS; j0 += 8) {  // eight independent accumulators at a time, term by term
+      uint32_t b0h[8], b0l[8], b1h[8], b1l[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        split(vr[(j0 + j) * 8], b0h[j], b0l[j]);
+        split(vr[PW + (j0 + j) * 8], b1h[j], b1l[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mma_tf32(oacc[j0 + j], al, b0h[j], b1h[j]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mma_tf32(oacc[j0 + j], ah, b0l[j], b1l[j]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mma_tf32(oacc[j0 + j], ah, b0h[j], b1h[j]);
+    }
     __syncwarp();  // the stage is refilled at the top of the next iteration; every lane is done reading it
   }
   cp::cp_async_wait<0>();
