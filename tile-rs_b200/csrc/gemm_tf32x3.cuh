@@ -141,14 +141,20 @@ gemm_tf32x3_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
         split_tf32(v0, bh[j][0], bl[j][0]);
         split_tf32(v1, bh[j][1], bl[j][1]);
       }
+      // small terms first; term by term across the eight accumulators, so that an MMA never waits for the one
+      // just before it (which would write the same accumulator)
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {  // small terms first
-          mma_tf32(acc[i][j], al[i], bh[j][0], bh[j][1]);
-          mma_tf32(acc[i][j], ah[i], bl[j][0], bl[j][1]);
-          mma_tf32(acc[i][j], ah[i], bh[j][0], bh[j][1]);
-        }
+        for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], al[i], bh[j][0], bh[j][1]);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ah[i], bl[j][0], bl[j][1]);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_tf32(acc[i][j], ah[i], bh[j][0], bh[j][1]);
     }
   }
   cp::cp_async_wait<0>();
