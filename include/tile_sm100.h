@@ -229,7 +229,10 @@ int32_t tsm100_gemm_static_scratch(const tsm100_gemm_desc* desc, const void* a, 
  * __tile_attention_gqa_* as the NVIDIA emitter defines it
  * (mlir_to_gpu.rs:1624-1711): kv_head = h / (heads_q/heads_kv), always causal
  * there.  Replaces mlir_to_gpu.rs:1976-1979 (unhandled) and :1624-1711.
- * 16-bit Q/K/V use tensor cores with f32 softmax statistics. */
+ * 16-bit Q/K/V use tensor cores with f32 softmax statistics (head_dim 128: tcgen05; 32 / 64 / 96: warp-level
+ * MMA); f32 Q/K/V with head_dim 32 / 64 / 96 / 128 use tensor cores with three TF32 products per product
+ * (results agree with an f32 evaluation to 1e-5).  Other head sizes, or rows that do not start on 16-byte
+ * boundaries: FP32 pipe. */
 typedef struct {
   int32_t dtype; /* TSM100_BF16 | TSM100_F16 | TSM100_F32 */
   int32_t causal;
@@ -279,7 +282,8 @@ int32_t tsm100_kv_cache_update(tsm100_device_t dev, const tsm100_kv_cache_update
  * the caches [heads_kv][max_seq][head_dim], kv head = h / (heads_q / heads_kv).
  * __tile_attention_prefill_f32 (tile.rs:2134-2136; wrapper :3062-3074); arithmetic of
  * crates/rustc_codegen_tile/src/mlir_to_msl.rs:10928-11010 without that lowering's limit of 256 cache positions
- * (its `threadgroup float scores[256]`).  head_dim 128 in 16 bit runs on tensor cores. */
+ * (its `threadgroup float scores[256]`).  The same kernels as tsm100_attention serve it (tensor cores for
+ * head_dim 128 in 16 bit and for head_dim 32 / 64 / 96 / 128 in f32 and 32 / 64 / 96 in 16 bit). */
 typedef struct {
   int32_t dtype;
   int32_t heads_q;
