@@ -439,6 +439,7 @@ NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per full-size la
     "reduce_sum_f32": 4 * (268.5e6 + 3.2e6),
     "silu_mul_f32": 4 * (536.9e6 + 229.3e6),
     "attention_decode_bf16": 4 * (537.0e6 + 4.6e6),
+    "attention_f32_causal": 2 * (100.9e6 + 16.8e6),  # captured on 16 of 32 heads, scaled by heads
 }
 
 
