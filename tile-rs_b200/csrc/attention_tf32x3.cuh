@@ -97,8 +97,9 @@ __device__ __forceinline__ void mma_split_group(float (*d)[4], const uint32_t (&
   }
 }
 
+// 16-bit data with head_dim <= 64 needs few enough registers for two CTAs per SM (16 warps hide each other's latencies)
 template <typename T, int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (sizeof(T) == 2 && D <= 64) ? 2 : 1)
 attention_tf32x3_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                         T* __restrict__ o, const Params p) {
   namespace cp = attn_decode::mma;
