@@ -291,13 +291,14 @@ template <int D>
 constexpr int pitch_bytes() { return D * 2 + 16; }
 template <int D>
 constexpr int stage_bytes() { return 2 * kTilePos * pitch_bytes<D>(); }   // K tile + V tile
-// ring (a warp's record for the merge later overlays its own part of it), the CTA's merged record.
+// ring (a warp's record for the merge later overlays its own part of it, the CTA's merged record the rest of warp 0's):
+// without a separate record three 4-warp CTAs fit one SM.
 // 4 warps x 2 stages when several CTAs share an SM (large batches: the other CTAs hide the latencies);
 // 8 warps x 3 stages when a launch has at most one CTA per SM (a few sequences): a single warp per
 // scheduler spends ~2900 cycles on a tile (the MMA, ldmatrix and shuffle latencies in a row), so the
 // lone CTA needs two warps per scheduler and 136 KiB of loads in flight to draw its share of HBM.
 template <int D, int STAGES, int WARPS>
-constexpr int smem_bytes() { return WARPS * STAGES * stage_bytes<D>() + kRows * (D + 2) * 4; }
+constexpr int smem_bytes() { return WARPS * STAGES * stage_bytes<D>(); }
 
 __device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr, bool valid) {
   const int n = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
@@ -343,10 +344,10 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
   constexpr int CHUNKS = D * 2 / 16;  // 16-byte pieces per cache row
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint8_t* ring = smem_raw;                                           // [warp][stage][K | V][16 rows][PITCH]
-  float* mine = reinterpret_cast<float*>(smem_raw + kWarps * STAGES * stage_bytes<D>());   // [16][REC]
   constexpr int WARP_FLOATS = STAGES * stage_bytes<D>() / 4;              // a warp's ring share, reused for its record [16][REC]
-  static_assert(kRows * REC <= WARP_FLOATS, "a warp's record must fit into its ring share");
+  static_assert(2 * kRows * REC <= WARP_FLOATS, "a warp's record and the CTA's merged record must fit into a ring share");
   float* part = reinterpret_cast<float*>(ring);                       // warp w's record at part + w * WARP_FLOATS
+  float* mine = part + kRows * REC;                                   // the CTA's merged record [16][REC], behind warp 0's
 
   const uint32_t rank = ptx::cluster_ctarank(), splits = ptx::cluster_nctarank();
   const int unit = blockIdx.x / splits;
@@ -551,7 +552,7 @@ constexpr int pitch_words() { return D + 4; }
 template <int D>
 constexpr int stage_bytes() { return 2 * kTilePos * pitch_words<D>() * 4; }  // K tile + V tile
 template <int D, int STAGES, int WARPS>
-constexpr int smem_bytes() { return WARPS * STAGES * stage_bytes<D>() + kRows * (D + 2) * 4; }
+constexpr int smem_bytes() { return WARPS * STAGES * stage_bytes<D>(); }
 
 __device__ __forceinline__ void split(float x, uint32_t& hi, uint32_t& lo) {
   hi = __float_as_uint(x) & 0xffffe000u;          // what the tensor core reads of x
@@ -573,10 +574,10 @@ attention_decode_tf32_kernel(const float* __restrict__ q, const float* __restric
   constexpr int CHUNKS = D / 4;      // 16-byte pieces per cache row
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint8_t* ring = smem_raw;                                           // [warp][stage][K | V][8 rows][PW floats]
-  float* mine = reinterpret_cast<float*>(smem_raw + kWarps * STAGES * stage_bytes<D>());   // [16][REC]
   constexpr int WARP_FLOATS = STAGES * stage_bytes<D>() / 4;          // a warp's ring share, reused for its record [16][REC]
-  static_assert(kRows * REC <= WARP_FLOATS, "a warp's record must fit into its ring share");
+  static_assert(2 * kRows * REC <= WARP_FLOATS, "a warp's record and the CTA's merged record must fit into a ring share");
   float* part = reinterpret_cast<float*>(ring);                       // warp w's record at part + w * WARP_FLOATS
+  float* mine = part + kRows * REC;                                   // the CTA's merged record [16][REC], behind warp 0's
 
   const uint32_t rank = ptx::cluster_ctarank(), splits = ptx::cluster_nctarank();
   const int unit = blockIdx.x / splits;
