@@ -79,6 +79,17 @@ int32_t tsm100_device_sm_count(tsm100_device_t dev, int32_t* sms);
  * check_cu (crates/tile_hal/src/cuda.rs:124-130) sees driver codes only. */
 int32_t tsm100_device_status(tsm100_device_t dev, void* stream, uint32_t* status);
 
+/* Lets one bounded device-side wait run out on purpose: a one-CTA kernel waits up to
+ * `limit_us` microseconds on a barrier nobody arrives at, gives up, records
+ * 0x1000|63 in the device's status word and returns normally (no trap, no fault, no
+ * unbounded spin).  The call itself returns TSM100_OK once that kernel has finished;
+ * the next tsm100_stream_synchronize / tsm100_device_status on the device then
+ * reports the timeout exactly as it would for a stuck pipeline, and clears it.
+ * observed[0] = how many of the kernel's two waiting threads left through the failure
+ * path (2), observed[1] = how long the first one waited, in microseconds.  May be
+ * NULL.  No counterpart in the reference, which has no device-side error channel. */
+int32_t tsm100_selftest_wait_timeout(tsm100_device_t dev, uint32_t limit_us, uint32_t* observed, void* stream);
+
 /* ---- streams and events: crates/tile_hal/src/stream.rs:7-10, cuda.rs:134-166 */
 /* A stream is a raw cudaStream_t carried as void*; NULL is the default stream,
  * so a stream made by another runtime in the same process can be passed. */
@@ -186,13 +197,19 @@ int32_t tsm100_silu_mul(tsm100_device_t dev, const tsm100_silu_mul_desc* desc, c
  * comment) and :1584-1622.  16-bit inputs accumulate in f32 on the tensor
  * cores; out_dtype is the input dtype or TSM100_F32.  `batch` independent
  * problems are stored back to back (the per-block tile stride of
- * #[tile_kernel], tile_std_macros/src/lib.rs:237-254). */
+ * #[tile_kernel], tile_std_macros/src/lib.rs:237-254).
+ * lda / ldb / ldc are row pitches in elements; 0 means "packed" (K for A; N, or K
+ * when b_transposed, for B; N for C), which is the only layout the tile
+ * intrinsics know.  A non-zero pitch lets a column block of a larger row-major
+ * matrix be an operand or the result in place (the N-column split of one large
+ * GEMM across GPUs); problems of a batch are then rows * pitch apart. */
 typedef struct {
   int32_t dtype;     /* element type of A and B */
   int32_t out_dtype; /* element type of C */
   int32_t b_transposed;
   int32_t batch;
   int64_t m, n, k;
+  int64_t lda, ldb, ldc; /* 0 = packed */
 } tsm100_gemm_desc;
 int32_t tsm100_gemm(tsm100_device_t dev, const tsm100_gemm_desc* desc, const void* a, const void* b,
                     void* c, void* stream);
@@ -334,6 +351,54 @@ int32_t tsm100_attention_host(tsm100_device_t dev, const tsm100_attention_desc* 
  * per-block tile of #[tile_kernel] (tile_std_macros/src/lib.rs:237-254). */
 int32_t tsm100_shard_range(int64_t units, int32_t world, int32_t rank, int64_t* first, int64_t* count);
 
+/* ---- multi-GPU launcher --------------------------------------------------- */
+/* One problem, described once with HOST buffers, run on a list of devices of this
+ * machine.  The reference can drive one GPU per process (crates/tile_hal/src/cuda.rs:321-327:
+ * one cuCtxCreate, no cuCtxSetCurrent; crates/tile_hal/src/backend.rs:95-112); the path has
+ * no exchange step, so the launcher deals the problem's independent units out with
+ * tsm100_shard_range and gives every device a host thread, a stream and a workspace of its
+ * own.  No peer access, no collective.  Units: softmax rows; GEMM problems of a batch, or,
+ * for batch == 1, N columns in blocks of 256 (device g computes C[:, first:first+count) from
+ * all of A and its columns of B, read from and written into the caller's row-major matrices
+ * in place); attention (batch, KV head) groups. */
+enum { TSM100_OP_SOFTMAX = 0, TSM100_OP_GEMM = 1, TSM100_OP_ATTENTION = 2 };
+typedef struct {
+  int32_t op;         /* TSM100_OP_* */
+  const void* desc;   /* tsm100_softmax_desc | tsm100_gemm_desc | tsm100_attention_desc of the WHOLE problem */
+  const void* in[3];  /* host buffers: x | a, b | q, k, v (page-locked ones copy asynchronously) */
+  void* out;          /* host buffer:  y | c | o */
+  int32_t launches;   /* kernel launches per device on its resident shard, timed together (< 1 means 1) */
+  int32_t timeout_ms; /* limit for each device's whole part; 0 = none */
+} tsm100_multi_job;
+typedef struct {
+  int32_t ordinal;
+  int32_t status;         /* TSM100_* of this device's part */
+  int64_t first, count;   /* its shard, in units */
+  float upload_ms;        /* CUDA-event times on the device's stream ... */
+  float kernel_ms;        /* ... per launch */
+  float download_ms;
+  float total_ms;         /* host clock around everything the device's thread did */
+  uint32_t device_status; /* the kernels' status word (0, or 0x1000|site) */
+  char message[160];      /* names the device when status != TSM100_OK */
+} tsm100_multi_report;
+/* The shard device `index` of `n` gets: contiguous, whole granules, the first ones one larger. */
+int32_t tsm100_multi_plan(const tsm100_multi_job* job, int32_t n, int32_t index, int64_t* first, int64_t* count);
+/* Runs the job on devices ordinals[0..n) and fills reports[0..n).  Returns TSM100_OK, or the
+ * status of the first device that failed, with a message that names its ordinal.  A device
+ * past timeout_ms is reported as TSM100_ERR_TIMEOUT; the call still returns only after that
+ * device has drained, because its copies target the caller's buffers (every device-side wait
+ * of the kernels is itself bounded, so it does drain).  Device workspaces are kept between
+ * runs; tsm100_multi_release frees them. */
+int32_t tsm100_multi_run(const tsm100_multi_job* job, const int32_t* ordinals, int32_t n, tsm100_multi_report* reports);
+/* The same scheduling (split, one thread per device, clock watching, reports) around a
+ * caller-supplied per-device function; NULL selects the built-in CUDA one.  This is how
+ * the launcher's failure handling is tested on machines without GPUs. */
+typedef int32_t (*tsm100_multi_worker_fn)(void* user, const tsm100_multi_job* job, int32_t ordinal, int64_t first,
+                                          int64_t count, tsm100_multi_report* report);
+int32_t tsm100_multi_run_with(const tsm100_multi_job* job, const int32_t* ordinals, int32_t n,
+                              tsm100_multi_report* reports, tsm100_multi_worker_fn worker, void* user);
+int32_t tsm100_multi_release(void);
+
 /* ---- cuda_sm100 CodegenTarget ------------------------------------------ */
 /* CodegenTarget::emit for the target named "cuda_sm100"
  * (crates/tile_codegen/src/target.rs:57-65; supersedes convert_mlir_to_gpu,
@@ -369,6 +434,9 @@ const char* tsm100_target_ext(void);  /* EmitOut.ext        -> "cu"         */
  *   outliers: element i := value where SplitMix64(s ^ i*golden) % period == 0 */
 int32_t tsm100_fill_uniform_f32(float* dst, int64_t n, uint64_t seed, int64_t first_index);
 int32_t tsm100_fill_normal_f32(float* dst, int64_t n, uint64_t seed, int64_t first_index, double sigma);
+/* The normal stream of tsm100_fill_normal_f32, times `factor` in f32, rounded to bf16 (RNE): the same bits as
+ * fill + scale + f32_to_bf16 without the f32 buffer. */
+int32_t tsm100_fill_normal_bf16(uint16_t* dst, int64_t n, uint64_t seed, int64_t first_index, double sigma, float factor);
 int32_t tsm100_plant_outliers_f32(float* dst, int64_t n, uint64_t seed, int64_t first_index,
                                   uint32_t period, float value);
 int32_t tsm100_scale_f32(float* dst, int64_t n, float factor);

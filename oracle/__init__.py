@@ -36,6 +36,8 @@ def lib() -> C.CDLL:
     if _LIB is None:
         h = C.CDLL(str(build()))
         h.orc_num_threads.restype = C.c_int
+        h.orc_set_num_threads.argtypes = [C.c_int]
+        h.orc_set_num_threads.restype = None
         h.orc_gemm_f32.argtypes = [_vp, _vp, _vp, _i64, _i64, _i64, C.c_int]
         h.orc_gemm_f64acc.argtypes = [_vp, _vp, _vp, _i64, _i64, _i64, C.c_int]
         h.orc_gemm_bf16.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _i64, C.c_int]
@@ -68,6 +70,12 @@ def lib() -> C.CDLL:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int) -> int:
+    """Sets the OpenMP thread count of the calling thread's parallel regions; returns what is then in force."""
+    lib().orc_set_num_threads(int(n))
+    return num_threads()
 
 
 def _p(a: np.ndarray) -> int:

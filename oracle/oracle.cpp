@@ -160,6 +160,16 @@ int orc_num_threads(void) {
 #endif
 }
 
+// Sets the number of OpenMP threads the functions below use (launchers such as torchrun
+// export OMP_NUM_THREADS=1, which would otherwise make a "CPU baseline" single-threaded).
+void orc_set_num_threads(int n) {
+#if defined(_OPENMP)
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 void orc_bf16_to_f32(const uint16_t* src, float* dst, int64_t n) {
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; ++i) dst[i] = bf16_to_f32(src[i]);

@@ -52,7 +52,7 @@ def test_no_device_is_an_error_not_a_fallback(pkg):
 
 
 def test_shard_range(pkg):
-    sh = pkg.shard
+    sh = pkg.launcher
     for units in (0, 1, 7, 16, 64, 65536, 100003):
         for world in (1, 2, 3, 4, 8):
             parts = [sh.shard_range(units, world, r) for r in range(world)]
@@ -65,13 +65,11 @@ def test_shard_range(pkg):
     with pytest.raises(ValueError):
         sh.shard_range(8, 4, 4)
     # the configurations' partitions on an 8-GPU box
-    assert [sh.softmax_rows(65536, 8, r).count for r in range(8)] == [8192] * 8
-    assert [sh.gemm_batches(64, 8, r).count for r in range(8)] == [8] * 8
-    assert [sh.gemm_n_columns(8192, 8, r).count for r in range(8)] == [1024] * 8
-    assert [sh.attention_groups(8, 32, 8, r).count for r in range(8)] == [32] * 8
-    assert [(s.first, s.count) for s in (sh.attention_groups(2, 8, 8, r) for r in range(8))] == [(2 * r, 2) for r in range(8)]
-    cols = [sh.gemm_n_columns(1000, 3, r) for r in range(3)]
-    assert cols[0].first == 0 and cols[-1].stop == 1000 and all(c.first % 256 == 0 for c in cols)
+    assert [sh.shard_range(65536, 8, r).count for r in range(8)] == [8192] * 8     # softmax rows
+    assert [sh.shard_range(64, 8, r).count for r in range(8)] == [8] * 8           # GEMM problems of the batch
+    assert [sh.shard_range(8 * 32, 8, r).count for r in range(8)] == [32] * 8      # (batch, head) groups
+    assert [(s.first, s.count) for s in (sh.shard_range(2 * 8, 8, r) for r in range(8))] == [(2 * r, 2) for r in range(8)]
+    # (the N-column split of one large GEMM is a launcher plan: tests/test_launcher.py)
 
 
 def _splitmix(z):
@@ -110,6 +108,10 @@ def test_generator_matches_its_definition_and_golden(pkg):
     hot = util.plant_outliers(capi, np.zeros(2000, np.float32), 202).nonzero()[0]
     assert np.array_equal(hot, g["outliers_202"])
     assert np.array_equal(hot, np.array([i for i in range(2000) if _draw(202, i) % 100 == 0]))
+    # the bf16 form is the same stream, scaled and rounded once
+    direct = np.empty(33, np.uint16)
+    assert capi.lib().tsm100_fill_normal_bf16(direct.ctypes.data, direct.size, 201, 17, 3.0, 0.5) == 0
+    assert np.array_equal(direct, util.to_bf16(capi, util.gen_normal(capi, (33,), 201, 3.0, first=17) * np.float32(0.5)))
     big = util.gen_normal(capi, (200000,), 7)
     assert abs(big.mean()) < 0.01 and abs(big.std() - 1.0) < 0.01
 

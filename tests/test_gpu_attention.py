@@ -191,3 +191,46 @@ def test_attention_host_path(dev, pkg, oracle):
                        causal=True)
     ref32, _ = oracle.attention_bf16(q, k, v, True)
     util.assert_16bit_close(oracle, oracle.bf16_to_f32(o), ref32)
+
+
+def _sampled_heads_check(dev, pkg, oracle, batch, hq, hkv, seq, causal, heads, what):
+    """Runs the full configuration on device-generated bf16 N(0,1) data (per-head scales as the GQA configuration
+    has them) and checks sampled (batch, head) x query-row blocks against the oracle: the head and batch indexing
+    of the timed launches, which small cases cannot reach."""
+    capi = pkg.capi
+    g = torch.Generator(device="cuda:0").manual_seed(401)
+    mk = lambda h: torch.randn(batch, h, seq, 128, device="cuda:0", generator=g)
+    q, k, v = mk(hq), mk(hkv), mk(hkv)
+    if hq != hkv:  # one scale per query head and per KV head, uniform in [0.5, 2)
+        q *= (torch.rand(1, hq, 1, 1, device="cuda:0", generator=g) * 1.5 + 0.5)
+        skv = torch.rand(1, hkv, 1, 1, device="cuda:0", generator=g) * 1.5 + 0.5
+        k *= skv
+        v *= skv
+    q, k, v = (t.to(torch.bfloat16).contiguous() for t in (q, k, v))
+    o = torch.full_like(q, float("nan"))
+    dev.attention(capi.BF16, batch, hq, hkv, seq, 128, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                  causal=causal, stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    assert dev.status() == 0
+    assert not torch.isnan(o.float()).any()
+    bits = lambda t: t.view(torch.int16).cpu().numpy().view(np.uint16)
+    group = hq // hkv
+    over = 0
+    for (b, h) in heads:
+        qh, kh, vh = bits(q[b, h][None, None]), bits(k[b, h // group][None, None]), bits(v[b, h // group][None, None])
+        for row0 in (0, seq // 2 - 32, seq - 64):
+            ref32, _ = oracle.attention_bf16(qh, kh, vh, causal, q_row0=row0, q_rows=64)
+            got = oracle.bf16_to_f32(bits(o[b, h, row0:row0 + 64][None, None]))
+            m = util.assert_16bit_close(oracle, got, ref32, (what, b, h, row0))
+            over += m["over_2e-2"]
+    print(f"[parity] {what}: {len(heads)} heads x 3 row blocks, elements over 2e-2: {over}")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_b8_h32_s4096_head_indexing(dev, pkg, oracle, causal):
+    _sampled_heads_check(dev, pkg, oracle, 8, 32, 32, 4096, causal, [(0, 0), (0, 31), (3, 17), (7, 31)],
+                         f"b8 h32 s4096 causal={causal}")
+
+
+def test_attention_gqa_b2_64_8_s16384_head_indexing(dev, pkg, oracle):
+    _sampled_heads_check(dev, pkg, oracle, 2, 64, 8, 16384, True, [(0, 0), (0, 63), (1, 9), (1, 56)], "gqa b2 64/8 s16384")

@@ -160,3 +160,87 @@ def test_gemm_host_path(dev, pkg, oracle):
     dev.gemm_host(capi.BF16, m, n, k, a.ctypes.data, b.ctypes.data, c.ctypes.data)
     ref32, _ = oracle.gemm_bf16(a, b)
     util.assert_16bit_close(oracle, oracle.bf16_to_f32(c), ref32)
+
+
+@pytest.mark.parametrize("dtype,m,n,k,n0,nb,bt", [
+    ("bf16", 512, 1024, 256, 256, 512, False),   # CTA-pair kernel on a column block of a wider matrix
+    ("bf16", 512, 1024, 256, 512, 256, True),    # B stored [N, K]: the block is a row range of it, C still pitched
+    ("bf16", 96, 768, 128, 256, 256, False),     # single-CTA tensor-core kernel
+    ("bf16", 50, 60, 20, 10, 30, False),         # FP32-pipe kernel (pitches not 16-byte multiples)
+    ("f32", 256, 768, 128, 256, 256, False),     # three-TF32 kernel
+    ("f32", 64, 512, 2048, 128, 64, True),       # the same with a cluster splitting K
+    ("f32", 33, 50, 17, 7, 21, False),           # FP32 pipe
+])
+def test_gemm_column_block_in_place(dev, pkg, oracle, dtype, m, n, k, n0, nb, bt):
+    """C[:, n0:n0+nb] = A * B[:, n0:n0+nb] with B and C addressed inside their full row-major matrices through
+    ldb / ldc (the N-column split of one large GEMM); every other column of C keeps its sentinel."""
+    capi = pkg.capi
+    sigma = k ** -0.25
+    a32 = util.gen_normal(capi, (m, k), 350, sigma)
+    b32 = util.gen_normal(capi, (n, k) if bt else (k, n), 351, sigma)
+    if dtype == "bf16":
+        a, b, code, tdt, es = util.to_bf16(capi, a32), util.to_bf16(capi, b32), capi.BF16, torch.int16, 2
+    else:
+        a, b, code, tdt, es = a32, b32, capi.F32, torch.float32, 4
+    ad, bd = util.dev_tensor(torch, a), util.dev_tensor(torch, b)
+    sentinel = 12345 if tdt == torch.int16 else 777.0
+    cd = torch.full((m, n), sentinel, dtype=tdt, device="cuda:0")
+    b_ptr = bd.data_ptr() + (n0 * k * es if bt else n0 * es)  # rows n0.. of [N, K], or columns n0.. of [K, N]
+    dev.gemm(code, m, nb, k, ad.data_ptr(), b_ptr, cd.data_ptr() + n0 * es, b_transposed=bt,
+             ldb=(k if bt else n), ldc=n, stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    assert dev.status() == 0
+    c = cd.cpu().numpy()
+    blk = np.ascontiguousarray(b[n0:n0 + nb] if bt else b[:, n0:n0 + nb])
+    if dtype == "bf16":
+        ref32, _ = oracle.gemm_bf16(a, blk, b_transposed=bt)
+        util.assert_16bit_close(oracle, oracle.bf16_to_f32(np.ascontiguousarray(c[:, n0:n0 + nb]).view(np.uint16)), ref32)
+    else:
+        mt = oracle.compare(np.ascontiguousarray(c[:, n0:n0 + nb]), oracle.gemm_f32(a, blk, b_transposed=bt, f64_acc=True))
+        assert mt["rel_max"] <= util.F32_REL and mt["rel_fro"] <= util.F32_REL, mt
+    outside = np.concatenate([c[:, :n0].ravel(), c[:, n0 + nb:].ravel()])
+    assert (outside == sentinel).all()
+    with pytest.raises(pkg.hal.KernelError, match="pitch"):
+        dev.gemm(code, m, nb, k, ad.data_ptr(), b_ptr, cd.data_ptr(), ldc=nb - 1)
+
+
+def test_gemm_host_pitched(dev, pkg, oracle):
+    """tsm100_gemm_host on a column block of host matrices (what the launcher's N-column split does per device)."""
+    capi = pkg.capi
+    m, n, k, n0, nb = 640, 1024, 512, 512, 256
+    a = util.to_bf16(capi, util.gen_normal(capi, (m, k), 360, k ** -0.25))
+    b = util.to_bf16(capi, util.gen_normal(capi, (k, n), 361, k ** -0.25))
+    c = np.full((m, n), 12345, np.uint16)
+    dev.gemm_host(capi.BF16, m, nb, k, a.ctypes.data, b.ctypes.data + n0 * 2, c.ctypes.data + n0 * 2, ldb=n, ldc=n)
+    ref32, _ = oracle.gemm_bf16(a, np.ascontiguousarray(b[:, n0:n0 + nb]))
+    util.assert_16bit_close(oracle, oracle.bf16_to_f32(np.ascontiguousarray(c[:, n0:n0 + nb])), ref32)
+    assert (c[:, :n0] == 12345).all() and (c[:, n0 + nb:] == 12345).all()
+
+
+def test_gemm_bf16_batched_64x4096_strides(dev, pkg, oracle):
+    """The batched configuration at full size (64 problems of 4096^3, 6 GiB): problem i is problem 0 with A scaled by
+    2^(i-32) and B by 2^((7i mod 64)-32) - exact in bf16 and in the f32 accumulation - so C_i must equal
+    2^(a_i+b_i) * C_0 bit for bit; reading or writing any problem at a wrong batch offset breaks that.
+    Problem 0 itself is checked against the oracle on sampled rows."""
+    capi = pkg.capi
+    n, batch = 4096, 64
+    sigma = n ** -0.25
+    a0 = util.to_bf16(capi, util.gen_normal(capi, (n, n), 310, sigma))
+    b0 = util.to_bf16(capi, util.gen_normal(capi, (n, n), 311, sigma))
+    a0d, b0d = util.dev_tensor(torch, a0).view(torch.bfloat16), util.dev_tensor(torch, b0).view(torch.bfloat16)
+    ea = torch.arange(batch, device="cuda:0") - 32
+    eb = (torch.arange(batch, device="cuda:0") * 7) % 64 - 32
+    ad = (a0d[None] * torch.pow(2.0, ea.float())[:, None, None].to(torch.bfloat16)).contiguous()
+    bd = (b0d[None] * torch.pow(2.0, eb.float())[:, None, None].to(torch.bfloat16)).contiguous()
+    cd = torch.empty((batch, n, n), dtype=torch.bfloat16, device="cuda:0")
+    dev.gemm(capi.BF16, n, n, n, ad.data_ptr(), bd.data_ptr(), cd.data_ptr(), batch=batch, stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    assert dev.status() == 0
+    i0 = int(torch.nonzero((ea + eb) == 0)[0])  # a problem whose scales cancel: C_i0 == C_unscaled
+    base = cd[i0].float()
+    for i in range(batch):
+        assert torch.equal(cd[i].float(), base * float(2.0 ** int(ea[i] + eb[i]))), i
+    rows = np.array([0, 129, 2047, 4095])
+    got = oracle.bf16_to_f32(cd[i0].view(torch.int16)[torch.from_numpy(rows).to("cuda:0")].cpu().numpy().view(np.uint16))
+    ref32, _ = oracle.gemm_bf16(np.ascontiguousarray(a0[rows]), b0)
+    util.assert_16bit_close(oracle, got, ref32, "64 x 4096^3, problem with unit scale", report=True)

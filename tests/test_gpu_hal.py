@@ -217,3 +217,59 @@ def test_launch_with_tile_kernel_descriptor(dev, pkg, oracle, tmp_path):
         launcher.launch_described(k, pkg.hal.LaunchGrid.blocks_(blocks + 1), [xb, yb], s)  # buffers too small for ten tiles
     with pytest.raises(pkg.hal.KernelError, match="takes 2 buffers"):
         launcher.launch_described(k, pkg.hal.LaunchGrid.blocks_(blocks), [xb], s)
+
+
+def test_emitted_causal_chain_module_launches(dev, pkg, oracle, tmp_path):
+    """matmul_transposed -> scale -> causal_mask -> softmax -> matmul is recognised as ONE fused causal attention;
+    the emitted module is launched, one (batch, head) per block, and matches the oracle's causal attention."""
+    seq, dim, blocks = 256, 64, 5
+    out, so = _module(pkg, tmp_path, F.causal_chain("causal_attention", seq, dim), "causal")
+    assert out.meta.kernel_names == ["causal_attention"]
+    launcher = dev.create_launcher()
+    launcher.load(so, pkg.hal.KernelMode.Matrix)
+    s = dev.create_stream()
+    q, k, v = (util.gen_normal(pkg.capi, (blocks, 1, seq, dim), 410 + i) for i in range(3))
+    qb, kb, vb = (dev.alloc_from_slice(t, s) for t in (q, k, v))
+    ob = dev.alloc(q.size, np.float32)
+    launcher.launch("causal_attention", pkg.hal.LaunchGrid.blocks_(blocks),
+                    [qb.as_raw_ptr(), kb.as_raw_ptr(), vb.as_raw_ptr(), ob.as_raw_mut_ptr()], s)
+    o = ob.copy_to_host(s).reshape(q.shape)
+    assert dev.status(s) == 0
+    m = oracle.compare(o, oracle.attention_f32(q, k, v, True))
+    assert m["rel_max"] <= util.F32_REL and m["rel_fro"] <= util.F32_REL, m
+    # and without the mask the same chain is plain attention
+    out2, so2 = _module(pkg, tmp_path, F.causal_chain("plain_attention", seq, dim, mask=False), "plain")
+    l2 = dev.create_launcher()
+    l2.load(so2, pkg.hal.KernelMode.Matrix)
+    l2.launch("plain_attention", pkg.hal.LaunchGrid.blocks_(blocks),
+              [qb.as_raw_ptr(), kb.as_raw_ptr(), vb.as_raw_ptr(), ob.as_raw_mut_ptr()], s)
+    o2 = ob.copy_to_host(s).reshape(q.shape)
+    m = oracle.compare(o2, oracle.attention_f32(q, k, v, False))
+    assert m["rel_max"] <= util.F32_REL and m["rel_fro"] <= util.F32_REL, m
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_survivable(dev, pkg):
+    """A one-CTA kernel waits 2 ms on a barrier nobody arrives at.  The wait gives up on its own: the kernel
+    returns normally, the status word carries 0x1000 | site, the next synchronise raises the timeout error and
+    clears the word, and the device goes on working.  Nothing traps, faults or spins without a limit."""
+    import ctypes as C
+    capi = pkg.capi
+    assert dev.status() == 0
+    seen = (C.c_uint32 * 2)()
+    pkg.hal.check(capi.lib().tsm100_selftest_wait_timeout(dev._h, 2000, seen, None))
+    assert seen[0] == 2             # both waiting threads left through the failure path
+    assert 2000 <= seen[1] < 200000  # the first one after its 2 ms limit, not after the library's 2 s
+    with pytest.raises(pkg.hal.RuntimeError_, match="0x103f"):
+        pkg.hal.check(capi.lib().tsm100_stream_synchronize(dev._h, None))
+    pkg.hal.check(capi.lib().tsm100_stream_synchronize(dev._h, None))  # reported once, then clear
+    # a second expiry is reported through tsm100_device_status, and a real kernel runs right after it
+    pkg.hal.check(capi.lib().tsm100_selftest_wait_timeout(dev._h, 1000, None, None))
+    assert dev.status() == 0x1000 | 63
+    assert dev.status() == 0
+    x = util.softmax_input(capi, 64, 4096)
+    xd = util.dev_tensor(torch, x)
+    yd = torch.empty_like(xd)
+    dev.softmax(capi.F32, 64, 4096, xd.data_ptr(), yd.data_ptr(), stream=util.cur_stream(torch))
+    torch.cuda.synchronize()
+    assert dev.status() == 0
+    assert float((yd.sum(dim=1) - 1).abs().max()) < 1e-5

@@ -6,7 +6,8 @@ fused attention — behind the reference's two plugin seams.
               KernelLauncher / BackendSelector / HalError) over that ABI
 * ``codegen`` host-side mirror of ``tile_codegen`` (CodegenTarget / TargetRegistry)
               with the ``cuda_sm100`` target
-* ``shard``   the multi-GPU partition rules (rows, batches, N-column blocks, KV groups)
+* ``launcher`` the multi-GPU launcher (``tsm100_multi_run``) and the shard rule it and the
+              process-per-GPU form share
 * ``build``   nvcc recipe for ``libtile_sm100.so``
 
 The directory name carries a hyphen, so it is imported under the module name
@@ -14,6 +15,6 @@ The directory name carries a hyphen, so it is imported under the module name
 fallback anywhere in this package: compute calls fail with ``HalError`` when no
 CUDA device is present.
 """
-from . import build, capi, codegen, hal, shard  # noqa: F401
+from . import build, capi, codegen, hal, launcher  # noqa: F401
 
-__all__ = ["build", "capi", "codegen", "hal", "shard"]
+__all__ = ["build", "capi", "codegen", "hal", "launcher"]

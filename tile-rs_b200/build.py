@@ -21,7 +21,7 @@ INCLUDE = PKG_DIR.parent / "include"
 BUILD_DIR = PKG_DIR / "_build"
 LIB_PATH = PKG_DIR / "libtile_sm100.so"
 
-CUDA_SOURCES = ["runtime.cu", "capi_ops.cu"]
+CUDA_SOURCES = ["runtime.cu", "capi_ops.cu", "multi.cu"]
 CXX_SOURCES = ["inputs.cpp", "emit.cpp"]
 
 NVCC_FLAGS = [

@@ -25,7 +25,7 @@ class SoftmaxDesc(C.Structure):
 
 class GemmDesc(C.Structure):
     _fields_ = [("dtype", c_i32), ("out_dtype", c_i32), ("b_transposed", c_i32), ("batch", c_i32),
-                ("m", c_i64), ("n", c_i64), ("k", c_i64)]
+                ("m", c_i64), ("n", c_i64), ("k", c_i64), ("lda", c_i64), ("ldb", c_i64), ("ldc", c_i64)]
 
 
 class RmsNormDesc(C.Structure):
@@ -68,7 +68,22 @@ class AttentionDesc(C.Structure):
                 ("heads_kv", c_i32), ("seq", c_i32), ("head_dim", c_i32)]
 
 
+OP_SOFTMAX, OP_GEMM, OP_ATTENTION = 0, 1, 2
+
+
+class MultiJob(C.Structure):
+    _fields_ = [("op", c_i32), ("desc", c_vp), ("inputs", c_vp * 3), ("out", c_vp), ("launches", c_i32),
+                ("timeout_ms", c_i32)]
+
+
+class MultiReport(C.Structure):
+    _fields_ = [("ordinal", c_i32), ("status", c_i32), ("first", c_i64), ("count", c_i64), ("upload_ms", C.c_float),
+                ("kernel_ms", C.c_float), ("download_ms", C.c_float), ("total_ms", C.c_float), ("device_status", c_u32),
+                ("message", C.c_char * 160)]
+
+
 P = C.POINTER
+MULTI_WORKER_FN = C.CFUNCTYPE(c_i32, c_vp, P(MultiJob), c_i32, c_i64, c_i64, P(MultiReport))
 # name -> (restype, argtypes); every symbol the header declares
 PROTOTYPES = {
     "tsm100_version": (c_i32, []),
@@ -81,6 +96,7 @@ PROTOTYPES = {
     "tsm100_mem_info": (c_i32, [c_vp, P(c_sz), P(c_sz)]),
     "tsm100_device_sm_count": (c_i32, [c_vp, P(c_i32)]),
     "tsm100_device_status": (c_i32, [c_vp, c_vp, P(c_u32)]),
+    "tsm100_selftest_wait_timeout": (c_i32, [c_vp, c_u32, P(c_u32), c_vp]),
     "tsm100_stream_create": (c_i32, [c_vp, P(c_vp)]),
     "tsm100_stream_destroy": (c_i32, [c_vp, c_vp]),
     "tsm100_stream_synchronize": (c_i32, [c_vp, c_vp]),
@@ -115,12 +131,17 @@ PROTOTYPES = {
     "tsm100_gemm_host": (c_i32, [c_vp, P(GemmDesc), c_vp, c_vp, c_vp]),
     "tsm100_attention_host": (c_i32, [c_vp, P(AttentionDesc), c_vp, c_vp, c_vp, c_vp]),
     "tsm100_shard_range": (c_i32, [c_i64, c_i32, c_i32, P(c_i64), P(c_i64)]),
+    "tsm100_multi_plan": (c_i32, [P(MultiJob), c_i32, c_i32, P(c_i64), P(c_i64)]),
+    "tsm100_multi_run": (c_i32, [P(MultiJob), P(c_i32), c_i32, P(MultiReport)]),
+    "tsm100_multi_run_with": (c_i32, [P(MultiJob), P(c_i32), c_i32, P(MultiReport), MULTI_WORKER_FN, c_vp]),
+    "tsm100_multi_release": (c_i32, []),
     "tsm100_emit": (c_i32, [C.c_char_p, c_sz, C.c_char_p, c_sz, P(c_sz), C.c_char_p, c_sz, P(c_sz)]),
     "tsm100_emit_descriptors": (c_i32, [C.c_char_p, c_sz, C.c_char_p, c_sz, P(c_sz)]),
     "tsm100_target_name": (C.c_char_p, []),
     "tsm100_target_ext": (C.c_char_p, []),
     "tsm100_fill_uniform_f32": (c_i32, [c_vp, c_i64, c_u64, c_i64]),
     "tsm100_fill_normal_f32": (c_i32, [c_vp, c_i64, c_u64, c_i64, C.c_double]),
+    "tsm100_fill_normal_bf16": (c_i32, [c_vp, c_i64, c_u64, c_i64, C.c_double, C.c_float]),
     "tsm100_plant_outliers_f32": (c_i32, [c_vp, c_i64, c_u64, c_i64, c_u32, C.c_float]),
     "tsm100_scale_f32": (c_i32, [c_vp, c_i64, C.c_float]),
     "tsm100_f32_to_bf16": (c_i32, [c_vp, c_vp, c_i64]),

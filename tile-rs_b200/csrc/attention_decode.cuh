@@ -275,14 +275,6 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ kc, const
 // the A fragments.
 // ===========================================================================
 namespace mma {
-#ifdef TSM100_DECODE_TRACE
-// Development aid (never compiled into the library): clock stamps of thread 0 of CTA 0.
-__device__ long long g_decode_trace[64];
-#define TSD_TRACE(k) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_decode_trace[k] = clock64(); } while (0)
-#else
-#define TSD_TRACE(k) do { } while (0)
-#endif
-
 // warps per CTA: 4 for large launches (several CTAs per SM), 8 when a launch has at most one CTA per SM
 constexpr int kTilePos = 16;   // positions per tile
 constexpr int kRows = 16;      // query heads per pass (rows of the MMA tile)
@@ -386,7 +378,6 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows gr and gr + 8 (this thread's share of the sums)
   const float sl2 = p.scale_log2;
 
-  TSD_TRACE(0);
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {  // the first tiles are on their way before anything else is read
     if (warp + i * kWarps < n_tiles) prefetch(warp + i * kWarps, i);
@@ -407,15 +398,12 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
       qa[kk][3] = ok1 ? __ldg(r1 + kk * 8 + tq + 4) : 0u;
     }
   }
-  TSD_TRACE(1);
   int stage = 0;
   for (int t = warp; t < n_tiles; t += kWarps, stage = stage + 1 == STAGES ? 0 : stage + 1) {
     if (t + (STAGES - 1) * kWarps < n_tiles) prefetch(t + (STAGES - 1) * kWarps, stage == 0 ? STAGES - 1 : stage - 1);
     cp_async_commit();
-    if (t < 16 * kWarps) TSD_TRACE(8 + 2 * (t / kWarps));
     cp_async_wait<STAGES - 1>();  // everything but the newest STAGES - 1 groups: this tile has landed
     __syncwarp();
-    if (t < 16 * kWarps) TSD_TRACE(9 + 2 * (t / kWarps));
     const uint32_t ks = ring_w + stage * stage_bytes<D>();
     const uint32_t vs = ks + kTilePos * PITCH;
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -474,7 +462,6 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
     }
     __syncwarp();  // the stage is refilled at the top of the next iteration; every lane is done reading it
   }
-  TSD_TRACE(2);
   cp_async_wait<0>();
   __syncwarp();  // the warp's ring share is free: it now receives the warp's record
   // this thread's share of the row sums -> the whole row's
@@ -521,13 +508,9 @@ attention_decode_mma_kernel(const T* __restrict__ q, const T* __restrict__ kc, c
       mine[hh * REC + D + 1] = ll;
     }
   }
-  TSD_TRACE(3);
   ptx::cluster_sync_all();
-  TSD_TRACE(4);
   cluster_merge<T, kRows, D, kThreads>(mine, part, rank, splits, p.heads_here, o + (static_cast<int64_t>(b) * p.heads_q + h0) * D);
-  TSD_TRACE(5);
   ptx::cluster_sync_all();  // nobody leaves while its shared memory may still be read
-  TSD_TRACE(6);
 }
 
 }  // namespace mma

@@ -49,10 +49,7 @@ constexpr int kHalfBytes = kTileBytes / 2; // one 128-row x 64-column swizzled h
 constexpr int kRing = 5;
 constexpr int kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-#ifndef TSM100_POLY_PAIRS
-#define TSM100_POLY_PAIRS 2
-#endif
-constexpr int kPolyPairs = TSM100_POLY_PAIRS;  // of every 8 pairs of exponentials, how many avoid MUFU
+constexpr int kPolyPairs = 2;  // of every 8 pairs of exponentials, how many avoid MUFU
 
 struct alignas(8) Barriers {
   uint64_t q_full;
@@ -80,19 +77,6 @@ struct Params {
   int32_t seq_kv, q_offset;
   int64_t o_row_stride, o_head_stride;
 };
-
-#ifdef TSM100_TRACE
-// Development aid (never compiled into the library): per-step clock stamps of CTA 0.
-__device__ long long g_attn_trace[3 * 64 * 8];
-#define TSM_TRACE(role, j, slot)                                                                  \
-  do {                                                                                            \
-    if (blockIdx.x == 0 && (j) < 64) g_attn_trace[((role) * 64 + (j)) * 8 + (slot)] = clock64(); \
-  } while (0)
-#else
-#define TSM_TRACE(role, j, slot) \
-  do {                           \
-  } while (0)
-#endif
 
 template <bool kIsBf16>
 __device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
@@ -267,31 +251,23 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       // PV_g(j) in this (in-order) stream, so overwriting S_g never overtakes the read of P_g.
       for (int j = 0; j < n_b && ok; ++j) {
         const int k_idx = 2 * j, v_idx = 2 * j + 1;
-        TSM_TRACE(1, j, 0);
         if (j < n_a) {
           if (!(ok = wait_kv(k_idx))) break;
-          TSM_TRACE(1, j, 1);
           issue_qk(0, k_idx);
         }
         if (j >= 1) {  // PV_B(j-1): last reader of V_{j-1}
           if (!(ok = wait_kv(v_idx - 2))) break;
-          TSM_TRACE(1, j, 2);
           if (!(ok = wait_p(1, j - 1))) break;
-          TSM_TRACE(1, j, 3);
           issue_pv(1, v_idx - 2, j - 1 > 0);
           if (ptx::elect_one_sync()) ptx::tcgen05_commit(&bars->kv_empty[(v_idx - 2) % kRing]);
         }
         if (j >= n_a && !(ok = wait_kv(k_idx))) break;  // otherwise already waited for before QK_A
-        TSM_TRACE(1, j, 4);
         issue_qk(1, k_idx);  // last reader of K_j
         if (ptx::elect_one_sync()) ptx::tcgen05_commit(&bars->kv_empty[k_idx % kRing]);
         if (j < n_a) {
           if (!(ok = wait_kv(v_idx))) break;
-          TSM_TRACE(1, j, 5);
           if (!(ok = wait_p(0, j))) break;
-          TSM_TRACE(1, j, 6);
           issue_pv(0, v_idx, j > 0);
-          TSM_TRACE(1, j, 7);
         }
       }
       if (ok) {
@@ -321,23 +297,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     float m_used = -INFINITY;  // running max in raw score units
     float l = 0.f;
     bool alive = true;
-    const bool tracer = (threadIdx.x & 127) == 0;
     for (int j = 0; j < n_g; ++j) {
-      if (tracer) TSM_TRACE(g * 2, j, 0);
       bool ready = ptx::mbar_wait(&bars->s_full[g], j & 1u, abort_flag, p.status, 16 + g);
       if (!__all_sync(0xffffffffu, ready)) {
         alive = false;
         break;
       }
       ptx::tcgen05_fence_after_thread_sync();
-      if (tracer) TSM_TRACE(g * 2, j, 1);
-#ifdef TSM100_DEBUG_SKIP_SOFTMAX
-      if (j >= 0) {  // development aid: hand the tile straight back, to time the MMA pipeline alone
-        ptx::tcgen05_fence_before_thread_sync();
-        ptx::mbar_arrive(&bars->p_ready[g]);
-        continue;
-      }
-#endif
       const int col0 = j * kBKV;
       const bool masked = col0 + kBKV - 1 > limit;
 
@@ -346,7 +312,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
       for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32b_x32(ts + c * 32, v[c]);
       ptx::tmem_ld_wait();
-      if (tracer) TSM_TRACE(g * 2, j, 2);
 
       float mx = -INFINITY;
       if (masked) {
@@ -367,7 +332,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
       const float m_new = fmaxf(m_used, mx);
-      if (tracer) TSM_TRACE(g * 2, j, 3);
       if (j == 0) {
         m_used = m_new;
       } else {
@@ -432,11 +396,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       ptx::unpack_f32x2(lsum[0], l4[0], l4[1]);
       ptx::unpack_f32x2(lsum[1], l4[2], l4[3]);
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      if (tracer) TSM_TRACE(g * 2, j, 4);
       ptx::tmem_st_wait();
       ptx::tcgen05_fence_before_thread_sync();  // P stores (and O rescale) ordered before the arrive
       ptx::mbar_arrive(&bars->p_ready[g]);
-      if (tracer) TSM_TRACE(g * 2, j, 5);
     }
 
     if (alive && n_g > 0) {

@@ -7,6 +7,7 @@
 
 #include "common.hpp"
 #include "ops.cuh"
+#include "selftest.cuh"
 
 using namespace tsm100;
 
@@ -51,6 +52,18 @@ int32_t sync_pipe(tsm100_device_t dev) {
 }
 
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// `rows` rows of `width` bytes between buffers with row pitches dpitch / spitch: one plain copy when both are packed.
+int32_t copy_rows(void* dst, size_t dpitch, const void* src, size_t spitch, size_t width, int64_t rows, cudaMemcpyKind kind,
+                  cudaStream_t s) {
+  if (rows <= 0 || width == 0) return TSM100_OK;
+  if (dpitch == width && spitch == width) {
+    TSM_CUDA(cudaMemcpyAsync(dst, src, width * static_cast<size_t>(rows), kind, s), TSM100_ERR_MEMORY);
+  } else {
+    TSM_CUDA(cudaMemcpy2DAsync(dst, dpitch, src, spitch, width, static_cast<size_t>(rows), kind, s), TSM100_ERR_MEMORY);
+  }
+  return TSM100_OK;
+}
 
 }  // namespace
 
@@ -132,6 +145,30 @@ int32_t tsm100_attention_prefill(tsm100_device_t dev, const tsm100_attention_pre
   return finish(ops::attention_prefill(&err, desc, q, k_cache, v_cache, o, dev->status, stream), err);
 }
 
+int32_t tsm100_selftest_wait_timeout(tsm100_device_t dev, uint32_t limit_us, uint32_t* observed_host, void* stream) {
+  int32_t st = use_device(dev);
+  if (st != TSM100_OK) return st;
+  if (limit_us == 0 || limit_us > 1000000u) return fail(TSM100_ERR_INVALID, "selftest_wait_timeout: limit must be 1 .. 1000000 us");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint32_t* observed = nullptr;
+  TSM_CUDA(cudaMalloc(reinterpret_cast<void**>(&observed), 2 * sizeof(uint32_t)), TSM100_ERR_MEMORY);
+  cudaError_t e = cudaMemsetAsync(observed, 0, 2 * sizeof(uint32_t), s);
+  if (e == cudaSuccess) {
+    selftest::wait_timeout_kernel<<<1, 64, 0, s>>>(dev->status, static_cast<unsigned long long>(limit_us) * 1000ull, observed);
+    e = cudaGetLastError();
+  }
+  uint32_t host[2] = {0, 0};
+  if (e == cudaSuccess) e = cudaMemcpyAsync(host, observed, sizeof host, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  cudaFree(observed);
+  if (e != cudaSuccess) return check_cuda(e, TSM100_ERR_LAUNCH, "selftest_wait_timeout");
+  if (observed_host) {
+    observed_host[0] = host[0];
+    observed_host[1] = host[1];
+  }
+  return TSM100_OK;
+}
+
 // ---------------------------------------------------------------------------
 // host-memory operators
 // ---------------------------------------------------------------------------
@@ -175,23 +212,32 @@ int32_t tsm100_gemm_host(tsm100_device_t dev, const tsm100_gemm_desc* desc, cons
   if (!desc || !ops::dtype_valid(desc->dtype) || !ops::dtype_valid(desc->out_dtype) || desc->m < 0 || desc->n < 0 ||
       desc->k < 0 || desc->batch < 0)
     return fail(TSM100_ERR_INVALID, "gemm_host: bad descriptor");
+  const ops::GemmPitch ld = ops::gemm_pitch(desc);  // pitches of the HOST matrices; the device copies are packed
+  const int64_t b_rows = desc->b_transposed ? desc->n : desc->k, b_cols = desc->b_transposed ? desc->k : desc->n;
+  if (ld.lda < desc->k || ld.ldb < b_cols || ld.ldc < desc->n)
+    return fail(TSM100_ERR_INVALID, "gemm_host: a row pitch (lda, ldb, ldc) is shorter than its row");
   if (desc->m == 0 || desc->n == 0 || desc->batch == 0) return TSM100_OK;
   if (!a || !b || !c) return fail(TSM100_ERR_INVALID, "gemm_host: null buffer");
   std::lock_guard<std::mutex> lock(dev->mu);
   const size_t es = ops::dtype_size(desc->dtype), os = ops::dtype_size(desc->out_dtype);
-  const size_t b_bytes = round_up(static_cast<size_t>(desc->k) * desc->n * es, 256);
+  const size_t a_row = static_cast<size_t>(desc->k) * es, b_row = static_cast<size_t>(b_cols) * es,
+               c_row = static_cast<size_t>(desc->n) * os;
+  const size_t b_bytes = round_up(static_cast<size_t>(b_rows) * b_row, 256);
+  tsm100_gemm_desc packed = *desc;
+  packed.lda = packed.ldb = packed.ldc = 0;
   std::string err;
   if (desc->batch == 1) {
     // B stays resident; A and C stream through in row blocks.
-    int64_t rows_per_chunk = std::max<int64_t>(128, (16ll << 20) / std::max<int64_t>(1, desc->k * static_cast<int64_t>(es)));
+    int64_t rows_per_chunk = std::max<int64_t>(128, (16ll << 20) / std::max<int64_t>(1, static_cast<int64_t>(a_row)));
     rows_per_chunk = std::min<int64_t>(desc->m, (rows_per_chunk + 127) / 128 * 128);
-    const size_t a_chunk = round_up(static_cast<size_t>(rows_per_chunk) * desc->k * es, 256);
-    const size_t c_chunk = round_up(static_cast<size_t>(rows_per_chunk) * desc->n * os, 256);
+    const size_t a_chunk = round_up(static_cast<size_t>(rows_per_chunk) * a_row, 256);
+    const size_t c_chunk = round_up(static_cast<size_t>(rows_per_chunk) * c_row, 256);
     st = ensure_pipe(dev, b_bytes + (a_chunk + c_chunk) * HostPipe::kSlots);
     if (st != TSM100_OK) return st;
     HostPipe& p = dev->pipe;
     char* db = static_cast<char*>(p.dev_buf);
-    TSM_CUDA(cudaMemcpyAsync(db, b, static_cast<size_t>(desc->k) * desc->n * es, cudaMemcpyHostToDevice, p.stream[0]), TSM100_ERR_MEMORY);
+    st = copy_rows(db, b_row, b, static_cast<size_t>(ld.ldb) * es, b_row, b_rows, cudaMemcpyHostToDevice, p.stream[0]);
+    if (st != TSM100_OK) return st;
     TSM_CUDA(cudaEventRecord(p.done[0], p.stream[0]), TSM100_ERR_STREAM);
     int64_t row = 0;
     for (int i = 0; row < desc->m; ++i, row += rows_per_chunk) {
@@ -199,40 +245,47 @@ int32_t tsm100_gemm_host(tsm100_device_t dev, const tsm100_gemm_desc* desc, cons
       cudaStream_t s = p.stream[slot];
       char* da = db + b_bytes + static_cast<size_t>(slot) * (a_chunk + c_chunk);
       char* dc = da + a_chunk;
-      tsm100_gemm_desc d = *desc;
+      tsm100_gemm_desc d = packed;
       d.m = std::min<int64_t>(rows_per_chunk, desc->m - row);
-      TSM_CUDA(cudaMemcpyAsync(da, static_cast<const char*>(a) + static_cast<size_t>(row) * desc->k * es,
-                               static_cast<size_t>(d.m) * desc->k * es, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
+      st = copy_rows(da, a_row, static_cast<const char*>(a) + static_cast<size_t>(row) * ld.lda * es,
+                     static_cast<size_t>(ld.lda) * es, a_row, d.m, cudaMemcpyHostToDevice, s);
+      if (st != TSM100_OK) return st;
       TSM_CUDA(cudaStreamWaitEvent(s, p.done[0], 0), TSM100_ERR_STREAM);
       st = ops::gemm(&err, &d, da, db, dc, dev->status, s);
       if (st != TSM100_OK) return finish(st, err);
-      TSM_CUDA(cudaMemcpyAsync(static_cast<char*>(c) + static_cast<size_t>(row) * desc->n * os, dc,
-                               static_cast<size_t>(d.m) * desc->n * os, cudaMemcpyDeviceToHost, s), TSM100_ERR_MEMORY);
+      st = copy_rows(static_cast<char*>(c) + static_cast<size_t>(row) * ld.ldc * os, static_cast<size_t>(ld.ldc) * os, dc, c_row,
+                     c_row, d.m, cudaMemcpyDeviceToHost, s);
+      if (st != TSM100_OK) return st;
     }
     return sync_pipe(dev);
   }
   // batched: one problem per slot
-  const size_t a_bytes = round_up(static_cast<size_t>(desc->m) * desc->k * es, 256);
-  const size_t c_bytes = round_up(static_cast<size_t>(desc->m) * desc->n * os, 256);
+  const size_t a_bytes = round_up(static_cast<size_t>(desc->m) * a_row, 256);
+  const size_t c_bytes = round_up(static_cast<size_t>(desc->m) * c_row, 256);
   const size_t unit = a_bytes + b_bytes + c_bytes;
   st = ensure_pipe(dev, unit * HostPipe::kSlots);
   if (st != TSM100_OK) return st;
   HostPipe& p = dev->pipe;
+  const size_t a_host = static_cast<size_t>(desc->m) * ld.lda * es, b_host = static_cast<size_t>(b_rows) * ld.ldb * es,
+               c_host = static_cast<size_t>(desc->m) * ld.ldc * os;
+  packed.batch = 1;
   for (int i = 0; i < desc->batch; ++i) {
     const int slot = i % HostPipe::kSlots;
     cudaStream_t s = p.stream[slot];
     char* da = static_cast<char*>(p.dev_buf) + static_cast<size_t>(slot) * unit;
     char* db = da + a_bytes;
     char* dc = db + b_bytes;
-    const size_t an = static_cast<size_t>(desc->m) * desc->k * es, bn = static_cast<size_t>(desc->k) * desc->n * es,
-                 cn = static_cast<size_t>(desc->m) * desc->n * os;
-    tsm100_gemm_desc d = *desc;
-    d.batch = 1;
-    TSM_CUDA(cudaMemcpyAsync(da, static_cast<const char*>(a) + i * an, an, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
-    TSM_CUDA(cudaMemcpyAsync(db, static_cast<const char*>(b) + i * bn, bn, cudaMemcpyHostToDevice, s), TSM100_ERR_MEMORY);
-    st = ops::gemm(&err, &d, da, db, dc, dev->status, s);
+    st = copy_rows(da, a_row, static_cast<const char*>(a) + i * a_host, static_cast<size_t>(ld.lda) * es, a_row, desc->m,
+                   cudaMemcpyHostToDevice, s);
+    if (st == TSM100_OK)
+      st = copy_rows(db, b_row, static_cast<const char*>(b) + i * b_host, static_cast<size_t>(ld.ldb) * es, b_row, b_rows,
+                     cudaMemcpyHostToDevice, s);
+    if (st != TSM100_OK) return st;
+    st = ops::gemm(&err, &packed, da, db, dc, dev->status, s);
     if (st != TSM100_OK) return finish(st, err);
-    TSM_CUDA(cudaMemcpyAsync(static_cast<char*>(c) + i * cn, dc, cn, cudaMemcpyDeviceToHost, s), TSM100_ERR_MEMORY);
+    st = copy_rows(static_cast<char*>(c) + i * c_host, static_cast<size_t>(ld.ldc) * os, dc, c_row, c_row, desc->m,
+                   cudaMemcpyDeviceToHost, s);
+    if (st != TSM100_OK) return st;
   }
   return sync_pipe(dev);
 }
@@ -334,8 +387,10 @@ size_t gemm_tc_scratch_bytes(const tsm100_gemm_desc*) { return sizeof(uint32_t);
 
 // The shapes the tensor-core kernel takes (the same conditions under which tsm100_gemm picks it).
 bool gemm_tc_takes(const tsm100_gemm_desc* d, const void* a, const void* b, const void* c) {
+  const ops::GemmPitch ld = ops::gemm_pitch(d);
   return d->dtype != TSM100_F32 && ops::aligned16(a) && ops::aligned16(b) && ops::aligned16(c) && d->k % 8 == 0 &&
          (d->b_transposed || d->n % 8 == 0) && (d->n * ops::dtype_size(d->out_dtype)) % 16 == 0 &&
+         ld.lda % 8 == 0 && ld.ldb % 8 == 0 && (ld.ldc * ops::dtype_size(d->out_dtype)) % 16 == 0 &&
          (static_cast<int64_t>((d->m + 127) / 128) * ((d->n + 255) / 256) * d->batch < 0x7fffffff);
 }
 
@@ -368,15 +423,3 @@ extern "C" int32_t tsm100_gemm_static_scratch(const tsm100_gemm_desc* desc, cons
     TSM_CUDA(cudaMemcpyAsync(status_host, scratch, sizeof(uint32_t), cudaMemcpyDeviceToHost, s), TSM100_ERR_RUNTIME);
   return TSM100_OK;
 }
-
-#ifdef TSM100_TRACE
-extern "C" int32_t tsm100_debug_read_attn_trace(long long* out) {
-  return cudaMemcpyFromSymbol(out, tsm100::attn::g_attn_trace, sizeof(tsm100::attn::g_attn_trace)) == cudaSuccess ? 0 : 6;
-}
-#endif
-
-#ifdef TSM100_DECODE_TRACE
-extern "C" int32_t tsm100_debug_read_decode_trace(long long* out) {
-  return cudaMemcpyFromSymbol(out, tsm100::attn_decode::mma::g_decode_trace, sizeof(tsm100::attn_decode::mma::g_decode_trace)) == cudaSuccess ? 0 : 6;
-}
-#endif

@@ -985,7 +985,7 @@ Kernel lower(const Func& f) {
       k.op = "gemm";
       sum << "__tile_matmul" << (bt ? "_transposed" : "") << " " << prod->m << " x " << prod->k << " x " << prod->n << ", "
           << dt_name(a.dtype) << " in, " << dt_name(out_dt) << " out, one problem per block";
-      body << "  tsm100_gemm_desc d;\n  d.dtype = " << dt_enum(a.dtype) << ";\n  d.out_dtype = " << dt_enum(out_dt)
+      body << "  tsm100_gemm_desc d = {};\n  d.dtype = " << dt_enum(a.dtype) << ";\n  d.out_dtype = " << dt_enum(out_dt)
            << ";\n  d.b_transposed = " << (bt ? 1 : 0) << ";\n  d.batch = static_cast<int32_t>(blocks);\n  d.m = " << prod->m
            << ";\n  d.n = " << prod->n << ";\n  d.k = " << prod->k << ";\n"
            << "  st = tsm100::ops::gemm(&msg, &d, args[" << a.arg << "], args[" << b.arg << "], args[" << store_arg

@@ -34,6 +34,7 @@ __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2hal
 struct Params {
   int32_t m, n, k, batch;
   int32_t b_transposed;
+  int64_t lda, ldb, ldc;  // row pitches in elements (>= the row length); problems of a batch are rows * pitch apart
 };
 
 template <typename InT, typename OutT, int BM, int BN, int BK, int TM, int TN>
@@ -46,9 +47,9 @@ gemm_simt_kernel(const InT* __restrict__ a, const InT* __restrict__ b, OutT* __r
   const int tx = tid % (BN / TN), ty = tid / (BN / TN);
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int64_t bz = blockIdx.z;
-  const InT* ab = a + bz * static_cast<int64_t>(p.m) * p.k;
-  const InT* bb = b + bz * static_cast<int64_t>(p.k) * p.n;
-  OutT* cb = c + bz * static_cast<int64_t>(p.m) * p.n;
+  const InT* ab = a + bz * static_cast<int64_t>(p.m) * p.lda;
+  const InT* bb = b + bz * static_cast<int64_t>(p.b_transposed ? p.n : p.k) * p.ldb;
+  OutT* cb = c + bz * static_cast<int64_t>(p.m) * p.ldc;
 
   float acc[TM][TN];
 #pragma unroll
@@ -61,19 +62,19 @@ gemm_simt_kernel(const InT* __restrict__ a, const InT* __restrict__ b, OutT* __r
     for (int e = tid; e < BM * BK; e += THREADS) {
       const int r = e / BK, kk = e % BK;
       const int gr = m0 + r, gk = k0 + kk;
-      sa[kk][r] = (gr < p.m && gk < p.k) ? to_f32(ab[static_cast<int64_t>(gr) * p.k + gk]) : 0.f;
+      sa[kk][r] = (gr < p.m && gk < p.k) ? to_f32(ab[static_cast<int64_t>(gr) * p.lda + gk]) : 0.f;
     }
     if (!p.b_transposed) {
       for (int e = tid; e < BK * BN; e += THREADS) {
         const int kk = e / BN, cidx = e % BN;
         const int gk = k0 + kk, gc = n0 + cidx;
-        sb[kk][cidx] = (gk < p.k && gc < p.n) ? to_f32(bb[static_cast<int64_t>(gk) * p.n + gc]) : 0.f;
+        sb[kk][cidx] = (gk < p.k && gc < p.n) ? to_f32(bb[static_cast<int64_t>(gk) * p.ldb + gc]) : 0.f;
       }
     } else {
       for (int e = tid; e < BK * BN; e += THREADS) {
         const int cidx = e / BK, kk = e % BK;
         const int gk = k0 + kk, gc = n0 + cidx;
-        sb[kk][cidx] = (gk < p.k && gc < p.n) ? to_f32(bb[static_cast<int64_t>(gc) * p.k + gk]) : 0.f;
+        sb[kk][cidx] = (gk < p.k && gc < p.n) ? to_f32(bb[static_cast<int64_t>(gc) * p.ldb + gk]) : 0.f;
       }
     }
     __syncthreads();
@@ -98,7 +99,7 @@ gemm_simt_kernel(const InT* __restrict__ a, const InT* __restrict__ b, OutT* __r
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
       const int gc = n0 + tx + j * (BN / TN);
-      if (gc < p.n) cb[static_cast<int64_t>(gr) * p.n + gc] = from_f32<OutT>(acc[i][j]);
+      if (gc < p.n) cb[static_cast<int64_t>(gr) * p.ldc + gc] = from_f32<OutT>(acc[i][j]);
     }
   }
 }

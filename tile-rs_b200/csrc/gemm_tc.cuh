@@ -57,6 +57,7 @@ struct Params {
   int32_t m, n, k, batch;
   int32_t m_blocks, n_blocks;
   int64_t c_batch_stride;  // elements
+  int64_t ldc;             // row pitch of C in elements
   uint32_t* status;
 };
 
@@ -259,7 +260,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (!__all_sync(0xffffffffu, ready)) break;
       ptx::tcgen05_fence_after_thread_sync();
       const int row = mb * kBM + quad * 32 + lane;
-      OutT* crow = c + static_cast<int64_t>(b) * p.c_batch_stride + static_cast<int64_t>(row) * p.n;
+      OutT* crow = c + static_cast<int64_t>(b) * p.c_batch_stride + static_cast<int64_t>(row) * p.ldc;
 #pragma unroll 1
       for (int cc = 0; cc < kBN / 32; ++cc) {
         uint32_t v[32];

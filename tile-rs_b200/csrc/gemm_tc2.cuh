@@ -34,10 +34,7 @@ constexpr int kABytes = kCtaM * kBK * 2;  // 16 KiB
 constexpr int kBBytes = kCtaN * kBK * 2;  // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 512;
-#ifndef TSM100_GEMM_GROUP_M
-#define TSM100_GEMM_GROUP_M 8
-#endif
-constexpr int kGroupM = TSM100_GEMM_GROUP_M;  // pair tiles per band: the band's rows of A stay in L2 while B streams
+constexpr int kGroupM = 8;  // pair tiles per band: the band's rows of A stay in L2 while B streams
 
 struct alignas(8) Barriers {
   uint64_t full[kStages];      // used in the leader: both CTAs' bytes of a stage have landed
@@ -195,7 +192,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (!__all_sync(0xffffffffu, ready)) break;
       ptx::tcgen05_fence_after_thread_sync();
       const int row = mb * kPairM + static_cast<int>(rank) * kCtaM + quad * 32 + lane;
-      OutT* crow = c + static_cast<int64_t>(b) * p.c_batch_stride + static_cast<int64_t>(row) * p.n;
+      OutT* crow = c + static_cast<int64_t>(b) * p.c_batch_stride + static_cast<int64_t>(row) * p.ldc;
 #pragma unroll 1
       for (int cc = 0; cc < kBN / 32; ++cc) {
         uint32_t v[32];

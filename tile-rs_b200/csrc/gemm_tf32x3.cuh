@@ -39,6 +39,7 @@ constexpr int kMaxSplit = 4;
 struct Params {
   int32_t m, n, k, batch;
   int32_t k_per_cta;  // K range of one CTA of a cluster, a multiple of kBK
+  int64_t lda, ldb, ldc;  // row pitches in elements (multiples of 4, 4 and 2); problems of a batch are rows * pitch apart
 };
 
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
@@ -67,8 +68,8 @@ gemm_tf32x3_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
   const int k_begin = static_cast<int>(rank) * p.k_per_cta;
   const int k_end = min(p.k, k_begin + p.k_per_cta);
   const int n_slices = k_end > k_begin ? (k_end - k_begin + kBK - 1) / kBK : 0;
-  const float* ab = a + static_cast<int64_t>(bz) * p.m * p.k;
-  const float* bb = b + static_cast<int64_t>(bz) * p.k * p.n;
+  const float* ab = a + static_cast<int64_t>(bz) * p.m * p.lda;
+  const float* bb = b + static_cast<int64_t>(bz) * (kBTransposed ? p.n : p.k) * p.ldb;
 
   auto prefetch = [&](int slice, int stage) {
     const int k0 = k_begin + slice * kBK;
@@ -77,19 +78,19 @@ gemm_tf32x3_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
     for (int i = tid; i < kBM * (kBK / 4); i += kThreads) {
       const int r = i / (kBK / 4), c4 = (i % (kBK / 4)) * 4;
       const bool ok = m0 + r < p.m && k0 + c4 < k_end;  // K % 4 == 0: a piece is inside or outside as a whole
-      cp::cp_async_16(as + (r * kPitchA + c4) * 4, ab + (ok ? static_cast<int64_t>(m0 + r) * p.k + k0 + c4 : 0), ok);
+      cp::cp_async_16(as + (r * kPitchA + c4) * 4, ab + (ok ? static_cast<int64_t>(m0 + r) * p.lda + k0 + c4 : 0), ok);
     }
     if (kBTransposed) {  // B stored [N][K]
       for (int i = tid; i < kBN * (kBK / 4); i += kThreads) {
         const int r = i / (kBK / 4), c4 = (i % (kBK / 4)) * 4;
         const bool ok = n0 + r < p.n && k0 + c4 < k_end;
-        cp::cp_async_16(bs + (r * kPitchBT + c4) * 4, bb + (ok ? static_cast<int64_t>(n0 + r) * p.k + k0 + c4 : 0), ok);
+        cp::cp_async_16(bs + (r * kPitchBT + c4) * 4, bb + (ok ? static_cast<int64_t>(n0 + r) * p.ldb + k0 + c4 : 0), ok);
       }
     } else {             // B stored [K][N]
       for (int i = tid; i < kBK * (kBN / 4); i += kThreads) {
         const int r = i / (kBN / 4), c4 = (i % (kBN / 4)) * 4;
         const bool ok = k0 + r < k_end && n0 + c4 < p.n;  // N % 4 == 0
-        cp::cp_async_16(bs + (r * kPitchB + c4) * 4, bb + (ok ? static_cast<int64_t>(k0 + r) * p.n + n0 + c4 : 0), ok);
+        cp::cp_async_16(bs + (r * kPitchB + c4) * 4, bb + (ok ? static_cast<int64_t>(k0 + r) * p.ldb + n0 + c4 : 0), ok);
       }
     }
   };
@@ -177,7 +178,7 @@ gemm_tf32x3_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
     {
       // every CTA adds its share of the tile (pairs of columns; N is even), all its remote loads in flight
       // together, ranks in rank order: a single CTA walking the whole tile spent more time here than in the MMAs
-      float* cb = c + static_cast<int64_t>(bz) * p.m * p.n;
+      float* cb = c + static_cast<int64_t>(bz) * p.m * p.ldc;
       const int per = kBM * kBN / 2 / static_cast<int>(splits);  // column pairs per rank
       for (int i = static_cast<int>(rank) * per + tid; i < (static_cast<int>(rank) + 1) * per; i += kThreads) {
         const int r = (2 * i) / kBN, cc = (2 * i) % kBN;
@@ -194,21 +195,21 @@ gemm_tf32x3_kernel(const float* __restrict__ a, const float* __restrict__ b, flo
             v.x += part[q].x;
             v.y += part[q].y;
           }
-        *reinterpret_cast<float2*>(cb + static_cast<int64_t>(m0 + r) * p.n + n0 + cc) = v;
+        *reinterpret_cast<float2*>(cb + static_cast<int64_t>(m0 + r) * p.ldc + n0 + cc) = v;
       }
     }
     ptx::cluster_sync_all();  // nobody leaves while its shared memory may still be read
     return;
   }
-  float* cb = c + static_cast<int64_t>(bz) * p.m * p.n;
+  float* cb = c + static_cast<int64_t>(bz) * p.m * p.ldc;
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int r = m0 + wm + i * 16 + g, cc = n0 + wn + j * 8 + 2 * t;  // N % 4 == 0 and cc even: cc + 1 < n when cc < n
       if (cc < p.n) {
-        if (r < p.m) *reinterpret_cast<float2*>(cb + static_cast<int64_t>(r) * p.n + cc) = make_float2(acc[i][j][0], acc[i][j][1]);
-        if (r + 8 < p.m) *reinterpret_cast<float2*>(cb + static_cast<int64_t>(r + 8) * p.n + cc) = make_float2(acc[i][j][2], acc[i][j][3]);
+        if (r < p.m) *reinterpret_cast<float2*>(cb + static_cast<int64_t>(r) * p.ldc + cc) = make_float2(acc[i][j][0], acc[i][j][1]);
+        if (r + 8 < p.m) *reinterpret_cast<float2*>(cb + static_cast<int64_t>(r + 8) * p.ldc + cc) = make_float2(acc[i][j][2], acc[i][j][3]);
       }
     }
 }

@@ -28,6 +28,24 @@ inline uint16_t f32_to_bf16_rne(float f) {
   return static_cast<uint16_t>(u >> 16);
 }
 
+// Both members of the Box-Muller pair (2p, 2p+1) come from one log / sqrt; a chunk of the index
+// range is walked pair by pair, with the ragged first and last elements handled alone.
+template <typename Store>
+void fill_normal(int64_t n, uint64_t seed, int64_t first_index, double sigma, Store store) {
+  const double two_pi = 6.283185307179586476925286766559;
+  const int64_t p_lo = first_index >> 1, p_hi = (first_index + n + 1) >> 1;  // pairs that overlap the range
+#pragma omp parallel for schedule(static)
+  for (int64_t p = p_lo; p < p_hi; ++p) {
+    const uint64_t pair = static_cast<uint64_t>(p);
+    const double u1 = (static_cast<double>(draw(seed, 2 * pair) >> 40) + 1.0) * (1.0 / 16777216.0);  // (0, 1]
+    const double u2 = static_cast<double>(draw(seed, 2 * pair + 1) >> 40) * (1.0 / 16777216.0);       // [0, 1)
+    const double rad = std::sqrt(-2.0 * std::log(u1)) * sigma;
+    const int64_t i0 = 2 * p - first_index, i1 = i0 + 1;
+    if (i0 >= 0 && i0 < n) store(i0, static_cast<float>(rad * std::cos(two_pi * u2)));
+    if (i1 >= 0 && i1 < n) store(i1, static_cast<float>(rad * std::sin(two_pi * u2)));
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -43,18 +61,14 @@ int32_t tsm100_fill_uniform_f32(float* dst, int64_t n, uint64_t seed, int64_t fi
 }
 
 int32_t tsm100_fill_normal_f32(float* dst, int64_t n, uint64_t seed, int64_t first_index, double sigma) {
-  if (n < 0 || (n > 0 && !dst)) return TSM100_ERR_INVALID;
-  const double two_pi = 6.283185307179586476925286766559;
-#pragma omp parallel for schedule(static)
-  for (int64_t i = 0; i < n; ++i) {
-    const uint64_t gi = static_cast<uint64_t>(first_index + i);
-    const uint64_t pair = gi >> 1;
-    const double u1 = (static_cast<double>(draw(seed, 2 * pair) >> 40) + 1.0) * (1.0 / 16777216.0);  // (0, 1]
-    const double u2 = static_cast<double>(draw(seed, 2 * pair + 1) >> 40) * (1.0 / 16777216.0);       // [0, 1)
-    const double rad = std::sqrt(-2.0 * std::log(u1));
-    const double z = (gi & 1) ? rad * std::sin(two_pi * u2) : rad * std::cos(two_pi * u2);
-    dst[i] = static_cast<float>(z * sigma);
-  }
+  if (n < 0 || first_index < 0 || (n > 0 && !dst)) return TSM100_ERR_INVALID;
+  fill_normal(n, seed, first_index, sigma, [dst](int64_t i, float v) { dst[i] = v; });
+  return TSM100_OK;
+}
+
+int32_t tsm100_fill_normal_bf16(uint16_t* dst, int64_t n, uint64_t seed, int64_t first_index, double sigma, float factor) {
+  if (n < 0 || first_index < 0 || (n > 0 && !dst)) return TSM100_ERR_INVALID;
+  fill_normal(n, seed, first_index, sigma, [dst, factor](int64_t i, float v) { dst[i] = f32_to_bf16_rne(v * factor); });
   return TSM100_OK;
 }
 

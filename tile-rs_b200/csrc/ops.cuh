@@ -13,7 +13,11 @@
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
+#include <tuple>
 #include <type_traits>
 
 #include "../../include/tile_sm100.h"
@@ -49,6 +53,81 @@ inline bool dtype_valid(int32_t dtype) { return dtype == TSM100_F32 || dtype == 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------------------
+// per-(kernel, device) facts: asked of the CUDA runtime once, then remembered
+// ---------------------------------------------------------------------------
+// cudaFuncSetAttribute and the occupancy queries cost a few microseconds each, which is as long as
+// a small launch itself; their answers depend on the kernel and the device only.
+struct KernelFacts {
+  std::mutex mu;
+  std::map<std::tuple<const void*, int, int>, int> value;  // (kernel, device, what) -> answer
+};
+inline KernelFacts& kernel_facts() {
+  static KernelFacts f;
+  return f;
+}
+enum { kFactSmemSet = 1, kFactNonPortableSet = 2, kFactBlocksPerSm = 3, kFactClusters = 4 };
+
+// `compute` returns (ok, answer); an answer is remembered only when ok.
+template <typename F>
+inline bool kernel_fact(const void* kern, int what, int* answer, F compute) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+  KernelFacts& f = kernel_facts();
+  const auto key = std::make_tuple(kern, dev, what);
+  {
+    std::lock_guard<std::mutex> lock(f.mu);
+    auto it = f.value.find(key);
+    if (it != f.value.end()) {
+      *answer = it->second;
+      return true;
+    }
+  }
+  if (!compute(answer)) return false;
+  std::lock_guard<std::mutex> lock(f.mu);
+  f.value[key] = *answer;
+  return true;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize, set once per kernel and device.
+template <typename K>
+inline cudaError_t set_dyn_smem_once(K kern, int bytes) {
+  cudaError_t e = cudaSuccess;
+  int unused = 0;
+  kernel_fact(reinterpret_cast<const void*>(kern), kFactSmemSet, &unused, [&](int* out) {
+    e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern), cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    *out = bytes;
+    return e == cudaSuccess;
+  });
+  return e;
+}
+template <typename K>
+inline cudaError_t allow_wide_clusters_once(K kern) {
+  cudaError_t e = cudaSuccess;
+  int unused = 0;
+  kernel_fact(reinterpret_cast<const void*>(kern), kFactNonPortableSet, &unused, [&](int* out) {
+    e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern), cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    *out = 1;
+    return e == cudaSuccess;
+  });
+  return e;
+}
+// Resident CTAs per SM of a kernel launched with `threads` threads and no dynamic shared memory (at least 1).
+template <typename K>
+inline int blocks_per_sm(K kern, int threads) {
+  int per_sm = 1;
+  kernel_fact(reinterpret_cast<const void*>(kern), kFactBlocksPerSm + (threads << 8), &per_sm, [&](int* out) {
+    int n = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, 0) != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    *out = n;
+    return true;
+  });
+  return per_sm < 1 ? 1 : per_sm;
+}
+
+// ---------------------------------------------------------------------------
 // tensor maps
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -69,30 +148,70 @@ inline int32_t encode_fn(std::string* err, EncodeTiledFn* out) {
   return TSM100_OK;
 }
 
-// 16-bit elements, dims (x contiguous, y, z), strides in elements, box (box_x, box_y, 1),
-// 128-byte swizzle, out-of-range elements read as zero.
-inline int32_t make_tmap_16bit_3d(std::string* err, CUtensorMap* out, const void* base, uint64_t dim_x,
-                                  uint64_t dim_y, uint64_t dim_z, uint64_t stride_y, uint64_t stride_z,
-                                  uint32_t box_x, uint32_t box_y, bool is_bf16) {
+// A map is a pure function of its arguments, and a repeated launch (same pointers, same shape) asks for the same
+// ones again: each thread keeps the last few it encoded.
+struct TmapKey {
+  const void* base;
+  uint64_t dim[3], stride[2];
+  uint32_t box[2];
+  int32_t dtype;
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used = false;
+};
+
+// dims (x contiguous, y, z), strides in elements of `elem_bytes`, box (box_x, box_y, 1), 128-byte swizzle,
+// out-of-range elements read as zero.
+inline int32_t make_tmap_3d(std::string* err, CUtensorMap* out, const void* base, uint64_t dim_x, uint64_t dim_y,
+                            uint64_t dim_z, uint64_t stride_y, uint64_t stride_z, uint32_t box_x, uint32_t box_y,
+                            CUtensorMapDataType dtype, uint32_t elem_bytes) {
+  constexpr int kSlots = 16;
+  static thread_local TmapSlot cache[kSlots];
+  static thread_local int next = 0;
+  TmapKey key;
+  std::memset(&key, 0, sizeof key);
+  key.base = base;
+  key.dim[0] = dim_x, key.dim[1] = dim_y, key.dim[2] = dim_z;
+  key.stride[0] = stride_y, key.stride[1] = stride_z;
+  key.box[0] = box_x, key.box[1] = box_y;
+  key.dtype = static_cast<int32_t>(dtype);
+  for (int i = 0; i < kSlots; ++i)
+    if (cache[i].used && std::memcmp(&cache[i].key, &key, sizeof key) == 0) {
+      *out = cache[i].map;
+      return TSM100_OK;
+    }
   EncodeTiledFn fn;
   int32_t st = encode_fn(err, &fn);
   if (st != TSM100_OK) return st;
   cuuint64_t dims[3] = {dim_x, dim_y, dim_z};
-  cuuint64_t strides[2] = {stride_y * 2, stride_z * 2};  // bytes; dimension 0 is contiguous
+  cuuint64_t strides[2] = {stride_y * elem_bytes, stride_z * elem_bytes};  // bytes; dimension 0 is contiguous
   cuuint32_t box[3] = {box_x, box_y, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   if ((strides[0] & 15u) || (strides[1] & 15u) || !aligned16(base))
     return op_fail(err, TSM100_ERR_INVALID, "tensor map needs a 16-byte aligned base and 16-byte-multiple strides");
-  CUresult r = fn(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(out, dtype, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char buf[96];
     snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed: CUresult %d", static_cast<int>(r));
     return op_fail(err, TSM100_ERR_LAUNCH, buf);
   }
+  TmapSlot& slot = cache[next];
+  next = (next + 1) % kSlots;
+  slot.key = key;
+  slot.map = *out;
+  slot.used = true;
   return TSM100_OK;
+}
+
+// 16-bit elements (bf16 or f16).
+inline int32_t make_tmap_16bit_3d(std::string* err, CUtensorMap* out, const void* base, uint64_t dim_x,
+                                  uint64_t dim_y, uint64_t dim_z, uint64_t stride_y, uint64_t stride_z,
+                                  uint32_t box_x, uint32_t box_y, bool is_bf16) {
+  return make_tmap_3d(err, out, base, dim_x, dim_y, dim_z, stride_y, stride_z, box_x, box_y,
+                      is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2);
 }
 
 inline int32_t sm_count(std::string* err, int* sms) {
@@ -144,8 +263,7 @@ inline int32_t softmax_typed(std::string* err, const T* x, T* y, int64_t rows, i
     const int32_t c = static_cast<int32_t>(cols);
     // persistent CTAs: exactly as many as are resident at once, each striding over the rows
     auto launch = [&](auto kern, int threads) {
-      int per_sm = 1;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+      const int per_sm = blocks_per_sm(kern, threads);
       const unsigned grid = static_cast<unsigned>(std::min<int64_t>(rows, static_cast<int64_t>(sms_cta) * per_sm));
       kern<<<grid, threads, 0, s>>>(x, y, rows, c);
     };
@@ -162,7 +280,7 @@ inline int32_t softmax_typed(std::string* err, const T* x, T* y, int64_t rows, i
     constexpr int THREADS = 512;
     const size_t smem = static_cast<size_t>(cols) * sizeof(float);
     auto kern = softmax::softmax_rows_block<T, THREADS>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    e = set_dyn_smem_once(kern, static_cast<int>(kMaxBlockCols * sizeof(float)));  // the most this path ever asks for
     if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(softmax_rows_block)");
     const int per_sm = static_cast<int>(std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / (smem + 1024))));
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(rows, static_cast<int64_t>(sms) * per_sm));
@@ -206,8 +324,7 @@ inline int32_t row_op_typed(std::string* err, const T* x, T* y, int64_t rows, in
   if (st != TSM100_OK) return st;
   // persistent CTAs: exactly as many as are resident at once, each striding over the rows
   auto launch = [&](auto kern, int threads, int rows_per_cta) {
-    int per_sm = 1;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    const int per_sm = blocks_per_sm(kern, threads);
     const int64_t want = (rows + rows_per_cta - 1) / rows_per_cta;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(want, static_cast<int64_t>(sms) * per_sm));
     kern<<<grid, threads, 0, s>>>(x, y, rows, static_cast<int32_t>(cols), eps);
@@ -271,13 +388,7 @@ inline int32_t silu_mul_typed(std::string* err, const T* gate, const T* up, T* y
   namespace ro = rowops;
   constexpr int PV = softmax::Elem<T>::kPerVec;
   // 16-bit data: twice the elements per byte, so twice the threads keep the same bytes in flight (measured: 5.87 -> 6.16 TB/s)
-#ifndef TSM100_SILU16_UNROLL
-#define TSM100_SILU16_UNROLL 4
-#endif
-#ifndef TSM100_SILU16_THREADS
-#define TSM100_SILU16_THREADS 512
-#endif
-  constexpr int THREADS = sizeof(T) == 2 ? TSM100_SILU16_THREADS : 256, UNROLL = sizeof(T) == 2 ? TSM100_SILU16_UNROLL : 4;
+  constexpr int THREADS = sizeof(T) == 2 ? 512 : 256, UNROLL = 4;
   int sms = 0;
   int32_t st = sm_count(err, &sms);
   if (st != TSM100_OK) return st;
@@ -389,11 +500,19 @@ inline int32_t kv_cache_update(std::string* err, const tsm100_kv_cache_update_de
 // ---------------------------------------------------------------------------
 // GEMM
 // ---------------------------------------------------------------------------
+// Row pitches of A, B and C in elements: the descriptor's value, or the row length when it is 0.
+struct GemmPitch {
+  int64_t lda, ldb, ldc;
+};
+inline GemmPitch gemm_pitch(const tsm100_gemm_desc* d) {
+  return {d->lda ? d->lda : d->k, d->ldb ? d->ldb : (d->b_transposed ? d->k : d->n), d->ldc ? d->ldc : d->n};
+}
 template <typename InT, typename OutT>
 inline int32_t gemm_simt_launch(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
                                 cudaStream_t s) {
+  const GemmPitch ld = gemm_pitch(d);
   gemm_simt::Params p{static_cast<int32_t>(d->m), static_cast<int32_t>(d->n), static_cast<int32_t>(d->k), d->batch,
-                      d->b_transposed};
+                      d->b_transposed, ld.lda, ld.ldb, ld.ldc};
   int sms = 0;
   int32_t st = sm_count(err, &sms);
   if (st != TSM100_OK) return st;
@@ -431,6 +550,8 @@ inline int32_t gemm_tf32x3_launch(std::string* err, const tsm100_gemm_desc* d, c
   p.k = static_cast<int32_t>(d->k);
   p.batch = d->batch;
   p.k_per_cta = static_cast<int32_t>(((d->k + splits - 1) / splits + g::kBK - 1) / g::kBK * g::kBK);
+  const GemmPitch ld = gemm_pitch(d);
+  p.lda = ld.lda, p.ldb = ld.ldb, p.ldc = ld.ldc;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -445,7 +566,7 @@ inline int32_t gemm_tf32x3_launch(std::string* err, const tsm100_gemm_desc* d, c
   cfg.stream = s;
   cfg.gridDim = dim3(static_cast<unsigned>(tiles * splits));
   auto launch = [&](auto kern) -> cudaError_t {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
+    cudaError_t e = set_dyn_smem_once(kern, g::kSmemBytes);
     if (e != cudaSuccess) return e;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), p);
   };
@@ -463,12 +584,14 @@ inline int32_t gemm_tc_launch(std::string* err, const tsm100_gemm_desc* d, const
   namespace g = gemm_tc;
   CUtensorMap ta, tb;
   const uint64_t M = d->m, N = d->n, K = d->k, B = d->batch;
-  int32_t st = make_tmap_16bit_3d(err, &ta, a, K, M, B, K, M * K, g::kBK, g::kBM, kBf16);
+  const GemmPitch ld = gemm_pitch(d);
+  const uint64_t lda = ld.lda, ldb = ld.ldb;
+  int32_t st = make_tmap_16bit_3d(err, &ta, a, K, M, B, lda, M * lda, g::kBK, g::kBM, kBf16);
   if (st != TSM100_OK) return st;
   if (kBT)
-    st = make_tmap_16bit_3d(err, &tb, b, K, N, B, K, N * K, g::kBK, g::kBN, kBf16);
+    st = make_tmap_16bit_3d(err, &tb, b, K, N, B, ldb, N * ldb, g::kBK, g::kBN, kBf16);
   else
-    st = make_tmap_16bit_3d(err, &tb, b, N, K, B, N, K * N, 64, g::kBK, kBf16);
+    st = make_tmap_16bit_3d(err, &tb, b, N, K, B, ldb, K * ldb, 64, g::kBK, kBf16);
   if (st != TSM100_OK) return st;
   g::Params p;
   p.m = static_cast<int32_t>(M);
@@ -477,14 +600,15 @@ inline int32_t gemm_tc_launch(std::string* err, const tsm100_gemm_desc* d, const
   p.batch = d->batch;
   p.m_blocks = static_cast<int32_t>((M + g::kBM - 1) / g::kBM);
   p.n_blocks = static_cast<int32_t>((N + g::kBN - 1) / g::kBN);
-  p.c_batch_stride = static_cast<int64_t>(M * N);
+  p.c_batch_stride = static_cast<int64_t>(M) * ld.ldc;
+  p.ldc = ld.ldc;
   p.status = status;
   int sms = 0;
   st = sm_count(err, &sms);
   if (st != TSM100_OK) return st;
   const int64_t tiles = static_cast<int64_t>(p.m_blocks) * p.n_blocks * p.batch;
   auto kern = g::gemm_tc_kernel<OutT, kBT, kBf16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
+  cudaError_t e = set_dyn_smem_once(kern, g::kSmemBytes);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(gemm_tc_kernel)");
   const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sms));
   kern<<<grid, g::kThreads, g::kSmemBytes, s>>>(ta, tb, static_cast<OutT*>(c), p);
@@ -498,12 +622,14 @@ inline int32_t gemm_tc2_launch(std::string* err, const tsm100_gemm_desc* d, cons
   namespace g = gemm_tc2;
   CUtensorMap ta, tb;
   const uint64_t M = d->m, N = d->n, K = d->k, B = d->batch;
-  int32_t st = make_tmap_16bit_3d(err, &ta, a, K, M, B, K, M * K, g::kBK, g::kCtaM, kBf16);
+  const GemmPitch ld = gemm_pitch(d);
+  const uint64_t lda = ld.lda, ldb = ld.ldb;
+  int32_t st = make_tmap_16bit_3d(err, &ta, a, K, M, B, lda, M * lda, g::kBK, g::kCtaM, kBf16);
   if (st != TSM100_OK) return st;
   if (kBT)
-    st = make_tmap_16bit_3d(err, &tb, b, K, N, B, K, N * K, g::kBK, g::kCtaN, kBf16);
+    st = make_tmap_16bit_3d(err, &tb, b, K, N, B, ldb, N * ldb, g::kBK, g::kCtaN, kBf16);
   else
-    st = make_tmap_16bit_3d(err, &tb, b, N, K, B, N, K * N, 64, g::kBK, kBf16);
+    st = make_tmap_16bit_3d(err, &tb, b, N, K, B, ldb, K * ldb, 64, g::kBK, kBf16);
   if (st != TSM100_OK) return st;
   gemm_tc::Params p;
   p.m = static_cast<int32_t>(M);
@@ -512,10 +638,11 @@ inline int32_t gemm_tc2_launch(std::string* err, const tsm100_gemm_desc* d, cons
   p.batch = d->batch;
   p.m_blocks = static_cast<int32_t>((M + g::kPairM - 1) / g::kPairM);
   p.n_blocks = static_cast<int32_t>((N + g::kBN - 1) / g::kBN);
-  p.c_batch_stride = static_cast<int64_t>(M * N);
+  p.c_batch_stride = static_cast<int64_t>(M) * ld.ldc;
+  p.ldc = ld.ldc;
   p.status = status;
   auto kern = g::gemm_tc2_kernel<OutT, kBT, kBf16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g::kSmemBytes);
+  cudaError_t e = set_dyn_smem_once(kern, g::kSmemBytes);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(gemm_tc2_kernel)");
   int sms = 0;
   st = sm_count(err, &sms);
@@ -532,12 +659,16 @@ inline int32_t gemm_tc2_launch(std::string* err, const tsm100_gemm_desc* d, cons
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1));
-  int max_clusters = 0;
-  e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
-  if (e != cudaSuccess || max_clusters < 1) {
-    cudaGetLastError();
-    max_clusters = sms / 2;
-  }
+  int max_clusters = sms / 2;  // how many pairs the GPU holds at once: asked once per kernel and device
+  kernel_fact(reinterpret_cast<const void*>(kern), kFactClusters, &max_clusters, [&](int* out) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    *out = n;
+    return true;
+  });
   const int64_t tiles = static_cast<int64_t>(p.m_blocks) * p.n_blocks * p.batch;
   const int64_t pairs = std::min<int64_t>(tiles, std::min<int64_t>(max_clusters, sms / 2));
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
@@ -558,16 +689,20 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
     return op_fail(err, TSM100_ERR_INVALID, "gemm: f32 inputs produce f32 output");
   if (d->dtype != TSM100_F32 && d->out_dtype != TSM100_F32 && d->out_dtype != d->dtype)
     return op_fail(err, TSM100_ERR_INVALID, "gemm: 16-bit inputs produce the same 16-bit type or f32");
+  const GemmPitch ld = gemm_pitch(d);
+  if (ld.lda < d->k || ld.ldb < (d->b_transposed ? d->k : d->n) || ld.ldc < d->n)
+    return op_fail(err, TSM100_ERR_INVALID, "gemm: a row pitch (lda, ldb, ldc) is shorter than its row");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (d->m == 0 || d->n == 0 || d->batch == 0) return TSM100_OK;
   if (d->k == 0) {  // empty contraction: C = 0 (linalg.fill)
-    const size_t bytes = static_cast<size_t>(d->batch) * d->m * d->n * dtype_size(d->out_dtype);
-    return cuda_ok(err, cudaMemsetAsync(c, 0, bytes, s), "cudaMemsetAsync");
+    const size_t os = dtype_size(d->out_dtype);
+    return cuda_ok(err, cudaMemset2DAsync(c, static_cast<size_t>(ld.ldc) * os, 0, static_cast<size_t>(d->n) * os,
+                                          static_cast<size_t>(d->batch) * d->m, s), "cudaMemset2DAsync");
   }
   if (d->dtype == TSM100_F32) {
     // rows that start on 16-byte boundaries: tensor cores; anything else: the FP32 pipe
     const bool vec_ok = aligned16(a) && aligned16(b) && aligned16(c) && d->k % 4 == 0 && (d->b_transposed || d->n % 4 == 0) &&
-                        d->n % 2 == 0;
+                        d->n % 2 == 0 && ld.lda % 4 == 0 && ld.ldb % 4 == 0 && ld.ldc % 4 == 0;
     if (vec_ok) return gemm_tf32x3_launch(err, d, a, b, c, s);
     return gemm_simt_launch<float, float>(err, d, a, b, c, s);
   }
@@ -577,6 +712,7 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
   // TMA needs 16-byte-multiple row pitches; the epilogue stores 16-byte vectors.
   const bool tma_ok = status != nullptr && aligned16(a) && aligned16(b) && aligned16(c) && (d->k % 8 == 0) &&
                       (d->b_transposed || d->n % 8 == 0) && (d->n * dtype_size(d->out_dtype)) % 16 == 0 &&
+                      ld.lda % 8 == 0 && ld.ldb % 8 == 0 && (ld.ldc * dtype_size(d->out_dtype)) % 16 == 0 &&
                       (static_cast<int64_t>((d->m + 127) / 128) * ((d->n + 255) / 256) * d->batch < 0x7fffffff);
   if (tma_ok) {
     const bool pair = d->m > 128 && d->n > 128;  // large enough for 256 x 256 tiles on CTA pairs
@@ -620,7 +756,7 @@ inline int32_t attention_tf32x3_launch_d(std::string* err, const attn_simt::Para
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many query blocks for one launch");
   auto kern = at::attention_tf32x3_kernel<T, D>;
   constexpr int smem = at::smem_bytes<T, D>();
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = set_dyn_smem_once(kern, smem);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_tf32x3_kernel)");
   kern<<<static_cast<unsigned>(grid), at::kThreads, smem, s>>>(q, k, v, o, p);
   return cuda_ok(err, cudaGetLastError(), "attention_tf32x3_kernel launch");
@@ -704,7 +840,7 @@ inline int32_t attention_prefill_tc_launch(std::string* err, const tsm100_attent
   const int64_t grid = static_cast<int64_t>(p.q_blocks) * d->heads_q;
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention_prefill: too many tiles for one launch");
   auto kern = at::attention_fwd_kernel<kBf16, true>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, at::kSmemBytes);
+  cudaError_t e = set_dyn_smem_once(kern, at::kSmemBytes);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_fwd_kernel, cache)");
   kern<<<static_cast<unsigned>(grid), at::kThreads, at::kSmemBytes, s>>>(tq, tk, tv, static_cast<uint16_t*>(o), p);
   return cuda_ok(err, cudaGetLastError(), "attention_fwd_kernel (prefill) launch");
@@ -752,7 +888,7 @@ inline int32_t attention_decode_launch(std::string* err, const tsm100_attention_
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
   auto kern = ad::attention_decode_kernel<T, G, D>;
   constexpr int smem = ad::smem_floats<T, G, D>() * static_cast<int>(sizeof(float));
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = set_dyn_smem_once(kern, smem);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_decode_kernel)");
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -799,10 +935,10 @@ inline int32_t attention_decode_mma_launch(std::string* err, const tsm100_attent
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
   auto kern = DecodeTc<T, D, STAGES, WARPS>::kernel();
   constexpr int smem = DecodeTc<T, D, STAGES, WARPS>::smem();
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = set_dyn_smem_once(kern, smem);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_decode_mma_kernel)");
   if (splits > ad::kMaxSplits) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    e = allow_wide_clusters_once(kern);
     if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_decode_mma_kernel, wide clusters)");
   }
   cudaLaunchConfig_t cfg = {};
@@ -957,7 +1093,7 @@ inline int32_t attention_tc_launch(std::string* err, const tsm100_attention_desc
   const int64_t grid = static_cast<int64_t>(p.q_blocks) * nq;
   if (grid > 0x7fffffff) return op_fail(err, TSM100_ERR_INVALID, "attention: too many tiles for one launch");
   auto kern = at::attention_fwd_kernel<kBf16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, at::kSmemBytes);
+  cudaError_t e = set_dyn_smem_once(kern, at::kSmemBytes);
   if (e != cudaSuccess) return cuda_ok(err, e, "cudaFuncSetAttribute(attention_fwd_kernel)");
   kern<<<static_cast<unsigned>(grid), at::kThreads, at::kSmemBytes, s>>>(tq, tk, tv, static_cast<uint16_t*>(o), p);
   return cuda_ok(err, cudaGetLastError(), "attention_fwd_kernel launch");

@@ -89,11 +89,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait on an mbarrier phase.  Returns false after kWaitLimitNs (or as
-// soon as another thread of the CTA has raised *abort_flag in shared memory),
-// having written kStatusWaitTimeout|site to *status (global) on a timeout.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t site) {
+// Bounded wait on an mbarrier phase.  Returns false after `limit_ns` (or as soon
+// as another thread of the CTA has raised *abort_flag in shared memory), having
+// written kStatusWaitTimeout|site to *status (global) on a timeout.
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                              uint32_t* status, uint32_t site, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
@@ -101,13 +101,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ffu) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1u;
         atomicCAS(status, kStatusOk, kStatusWaitTimeout | site);
         return false;
       }
     }
   }
+}
+// The form every kernel uses: the limit is kWaitLimitNs.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status, uint32_t site) {
+  return mbar_wait_for(bar, parity, abort_flag, status, site, kWaitLimitNs);
 }
 
 // The same bounded wait without acquire semantics.  For threads that only hand the

@@ -398,8 +398,9 @@ class CudaSm100Device:
         check(capi.lib().tsm100_silu_mul(self._h, C.byref(d), gate, up or None, y, stream or None))
 
     def gemm(self, dtype: int, m: int, n: int, k: int, a: int, b: int, c: int, *, out_dtype: Optional[int] = None,
-             b_transposed: bool = False, batch: int = 1, stream: int = 0) -> None:
-        d = capi.GemmDesc(dtype, dtype if out_dtype is None else out_dtype, int(b_transposed), batch, m, n, k)
+             b_transposed: bool = False, batch: int = 1, lda: int = 0, ldb: int = 0, ldc: int = 0, stream: int = 0) -> None:
+        """C = A * B; lda / ldb / ldc are row pitches in elements (0: packed rows)."""
+        d = capi.GemmDesc(dtype, dtype if out_dtype is None else out_dtype, int(b_transposed), batch, m, n, k, lda, ldb, ldc)
         check(capi.lib().tsm100_gemm(self._h, C.byref(d), a, b, c, stream or None))
 
     def attention(self, dtype: int, batch: int, heads_q: int, heads_kv: int, seq: int, head_dim: int, q: int, k: int,
@@ -437,8 +438,9 @@ class CudaSm100Device:
         check(capi.lib().tsm100_softmax_host(self._h, C.byref(d), x, y))
 
     def gemm_host(self, dtype: int, m: int, n: int, k: int, a: int, b: int, c: int, *, out_dtype: Optional[int] = None,
-                  b_transposed: bool = False, batch: int = 1) -> None:
-        d = capi.GemmDesc(dtype, dtype if out_dtype is None else out_dtype, int(b_transposed), batch, m, n, k)
+                  b_transposed: bool = False, batch: int = 1, lda: int = 0, ldb: int = 0, ldc: int = 0) -> None:
+        """The same on host buffers; the pitches describe the HOST matrices (device copies are packed)."""
+        d = capi.GemmDesc(dtype, dtype if out_dtype is None else out_dtype, int(b_transposed), batch, m, n, k, lda, ldb, ldc)
         check(capi.lib().tsm100_gemm_host(self._h, C.byref(d), a, b, c))
 
     def attention_host(self, dtype: int, batch: int, heads_q: int, heads_kv: int, seq: int, head_dim: int, q: int,
