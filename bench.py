@@ -248,14 +248,14 @@ def dev_rows_to_host(t, index):
 
 
 def parity_16bit(oracle, got_f32, ref_f32):
-    """The 16-bit bar: relative Frobenius <= 1e-2; |y - r| <= max(2e-2, half a bf16 ulp of |r| + 1e-3 |r|)."""
+    """The 16-bit bar: relative Frobenius <= 1e-2; |y - r| <= max(2e-2, half a bf16 ulp of |r| + 2^-9 |r|)."""
     m = oracle.compare(got_f32, ref_f32)
     ref = np.abs(np.asarray(ref_f32, np.float64))
     err = np.abs(np.asarray(got_f32, np.float64) - np.asarray(ref_f32, np.float64))
-    tol = np.maximum(2e-2, 2.0 ** (np.floor(np.log2(np.maximum(ref, 1e-30))) - 8) + 1e-3 * ref)
+    tol = np.maximum(2e-2, 2.0 ** (np.floor(np.log2(np.maximum(ref, 1e-30))) - 8) + 2.0 ** -9 * ref)
     ok = bool(m["rel_fro"] <= 1e-2 and (err <= tol).all())
     return {"ok": ok, "max_abs": float(m["max_abs"]), "rel_fro": float(m["rel_fro"]), "over_2e-2": int((err > 2e-2).sum()),
-            "elements": int(err.size), "tolerance": "rel_fro <= 1e-2, |y-r| <= max(2e-2, half a bf16 ulp of |r| + 1e-3 |r|) vs the unrounded f32 oracle"}
+            "elements": int(err.size), "tolerance": "rel_fro <= 1e-2, |y-r| <= max(2e-2, half a bf16 ulp of |r| + 2^-9 |r|) vs the unrounded f32 oracle"}
 
 
 def parity_f32(oracle, got, ref):
@@ -907,30 +907,46 @@ def run_ours(args):
     peaks = measured_peaks()
 
     head, _ = measure(ctx, args.workload, args, peaks, args.steps, args.warmup, headline=True)
-    extras = {}
+    extras, failed = {}, []
     if not args.no_extras:
         steps2 = max(3, min(args.steps, 10))
         names = [n for n in ORDER if n != args.workload]
         if args.only:
             names = [n for n in names if n in args.only.split(",")]
         shared_wl = None
+
+        def guarded(name, **kw):
+            """One configuration's failure (a check that does not hold, an out-of-memory box) is recorded under its
+            name and in "failed"; the others are still measured and the line is still printed."""
+            try:
+                return measure(ctx, name, args, peaks, steps2, 3, **kw)
+            except Exception as exc:  # noqa: BLE001
+                if world > 1:
+                    raise  # the other ranks would wait in a collective: fail the whole run instead
+                torch.cuda.synchronize()
+                torch.cuda.empty_cache()
+                failed.append(name)
+                return {"error": f"{type(exc).__name__}: {exc}"[:600]}, None
+
         for name in names:
             if name == "attention_noncausal" and "attention_causal" in names:
                 # the causal configuration reads the same Q, K, V: keep them resident instead of generating them twice
-                extras[name], shared_wl = measure(ctx, name, args, peaks, steps2, 3, keep=True)
+                extras[name], shared_wl = guarded(name, keep=True)
                 continue
             if name == "attention_causal" and shared_wl is not None:
-                extras[name], _ = measure(ctx, name, args, peaks, steps2, 3, shared=shared_wl.shared())
+                extras[name], _ = guarded(name, shared=shared_wl.shared())
                 shared_wl.free()
                 shared_wl = None
                 torch.cuda.empty_cache()
                 continue
-            extras[name], _ = measure(ctx, name, args, peaks, steps2, 3)
+            extras[name], _ = guarded(name)
 
     if rank == 0:
         def brief(r):
             if r is None:
                 return None
+            if "error" in r:
+                return {"error": r["error"][:120]}
             b = {"value": r["value"], "unit": r["unit"], "ms": r["ms_per_step"], "frac": r["roofline"]["frac"]}
             if "sustained" in r:
                 b["sust"], b["sust_frac"], b["per_ghz"] = r["sustained"]["value"], r["sustained"]["roofline_frac"], r["sustained"]["tflops_per_ghz"]
@@ -954,7 +970,7 @@ def run_ours(args):
             "dtype": head["dtype"], "data": "synthetic", "config": head["config"],
             "roofline": head["roofline"], "cpu_baseline": head.get("cpu_baseline"), "e2e": head.get("e2e"),
             "gpu_launches": head["launches"], "clocks": head["clocks"], "verify": head.get("verify"), "strong": head.get("strong"),
-            "host_threads_per_rank": threads,
+            "host_threads_per_rank": threads, "failed": failed,
             "workloads": extras,
             "summary": {n: brief(allrec.get(n)) for n in SUMMARY if n in allrec},
         }
@@ -1045,7 +1061,7 @@ def run_reference(args):
     if head is None:
         print(json.dumps({"impl": "reference", "unavailable": f"{args.workload} is a next-tier operator without a CPU leg in this arm"}))
         return
-    extras = {}
+    extras, failed = {}, []
     if not args.no_extras:
         for name in ORDER:
             if name != args.workload:

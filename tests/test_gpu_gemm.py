@@ -244,3 +244,25 @@ def test_gemm_bf16_batched_64x4096_strides(dev, pkg, oracle):
     got = oracle.bf16_to_f32(cd[i0].view(torch.int16)[torch.from_numpy(rows).to("cuda:0")].cpu().numpy().view(np.uint16))
     ref32, _ = oracle.gemm_bf16(np.ascontiguousarray(a0[rows]), b0)
     util.assert_16bit_close(oracle, got, ref32, "64 x 4096^3, problem with unit scale", report=True)
+
+
+@pytest.mark.parametrize("m,n,k,bt,batch", [
+    (2048, 2048, 2048, False, 1), (1024, 4096, 4096, True, 1), (1032, 2052, 1028, False, 1), (1100, 2100, 300, True, 1),
+    (1024, 2048, 512, False, 3), (4096, 4096, 4096, False, 1), (2048, 2048, 8192, False, 1)])
+def test_gemm_f32_tcgen05(dev, pkg, oracle, m, n, k, bt, batch):
+    """Large f32 problems run on the tcgen05 kernel (hi / lo planes, three TF32 products, chunked accumulation):
+    sampled rows against the float64-accumulating oracle at the 1e-5 bar, ragged edges and batches included, and
+    against the f32-accumulating oracle's own distance from float64 for context."""
+    capi = pkg.capi
+    a = util.gen_uniform(capi, (batch, m, k), 101)
+    b = util.gen_uniform(capi, (batch, n, k) if bt else (batch, k, n), 102)
+    c = run_gemm(dev, capi, a, b, m, n, k, capi.F32, b_transposed=bt, batch=batch)
+    assert not np.isnan(c).any()
+    rows = np.array(sorted({0, 1, 127, 128, m // 2 + 3, m - 1}))
+    for i in range(batch):
+        ref = oracle.gemm_f32(np.ascontiguousarray(a[i][rows]), b[i], b_transposed=bt, f64_acc=True)
+        mt = oracle.compare(np.ascontiguousarray(c[i][rows]), ref)
+        f32 = oracle.compare(oracle.gemm_f32(np.ascontiguousarray(a[i][rows]), b[i], b_transposed=bt), ref)
+        print(f"[parity] f32 GEMM {m}x{n}x{k} problem {i}: GPU rel_max {mt['rel_max']:.2e} rel_fro {mt['rel_fro']:.2e}; "
+              f"f32 CPU loop rel_max {f32['rel_max']:.2e} rel_fro {f32['rel_fro']:.2e}")
+        assert mt["rel_max"] <= util.F32_REL and mt["rel_fro"] <= util.F32_REL, (i, mt)

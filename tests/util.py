@@ -68,13 +68,15 @@ def cur_stream(torch):
 
 def tol_16bit(ref_f32, significant_bits=8):
     """Element-wise absolute bound for a 16-bit result against the UNROUNDED f32 oracle:
-    max(2e-2, half a unit in the last place of the storage type at |r| + 1e-3 * |r|).
+    max(2e-2, half a unit in the last place of the storage type at |r| + 2^-9 * |r|).
     Rounding a correct f32 value to bf16 (8 significant bits) alone moves it by up to half an ulp,
     2^(floor(log2 |r|) - 8), which passes 2e-2 once |r| >= 8 (0.0156 on [4, 8), 0.031 on [8, 16));
-    the 1e-3 * |r| term is the room left for the arithmetic itself."""
+    the 2^-9 * |r| term is one 16-bit rounding of an intermediate: the attention kernels hand the
+    probabilities to the P V product in the storage type, and where one key dominates a row that
+    rounding reaches the output undiminished (measured: 0.0045 at |r| = 4.1 with heads scaled by up to 4)."""
     ref = np.abs(np.asarray(ref_f32, np.float64))
     half_ulp = 2.0 ** (np.floor(np.log2(np.maximum(ref, 1e-30))) - significant_bits)
-    return np.maximum(BF16_MAX_ABS, half_ulp + 1e-3 * ref)
+    return np.maximum(BF16_MAX_ABS, half_ulp + 2.0 ** -9 * ref)
 
 
 def assert_16bit_close(oracle, got_f32, ref_f32, what="", report=False):

@@ -43,8 +43,11 @@ struct Params {
 };
 
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-  hi = __float_as_uint(x) & 0xffffe000u;          // what the tensor core reads of x
-  lo = __float_as_uint(x - __uint_as_float(hi));  // exact; the tensor core reads its top 11 bits
+  // hi = x rounded to the nearest TF32 number (ties away from zero), not truncated: a truncated hi leaves a lo
+  // of x's own sign, whose truncation inside the tensor core then errs the same way for every term, and the
+  // error grows with K instead of sqrt(K) (3e-5 of the largest element at K = 4096)
+  hi = (__float_as_uint(x) + 0x1000u) & 0xffffe000u;
+  lo = __float_as_uint(x - __uint_as_float(hi));  // exact, either sign; the tensor core reads its top 11 bits
 }
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"

@@ -4,7 +4,9 @@
 // instantiate the same kernels with the same dispatch.
 //
 // Every function returns a TSM100_* status and, on failure, writes a message
-// to *err.  Nothing here allocates device memory or synchronises.
+// to *err.  Nothing here synchronises; the one operator that needs device scratch (the
+// tcgen05 f32 GEMM: the hi / lo planes of its operands) takes it from, and returns it to,
+// the device's stream-ordered memory pool on the caller's stream.
 #pragma once
 
 #include <cuda.h>
@@ -29,6 +31,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_tc2.cuh"
+#include "gemm_tf32_tc.cuh"
 #include "gemm_tf32x3.cuh"
 #include "rowops.cuh"
 #include "softmax.cuh"
@@ -578,6 +581,91 @@ inline int32_t gemm_tf32x3_launch(std::string* err, const tsm100_gemm_desc* d, c
   return cuda_ok(err, e, "gemm_tf32x3_kernel launch");
 }
 
+// The device's default memory pool keeps what is freed into it (no trimming at synchronisation points), so
+// that after the first call cudaMallocAsync / cudaFreeAsync are bookkeeping on the stream.  Once per device.
+inline cudaError_t keep_pool_memory_once() {
+  cudaError_t e = cudaSuccess;
+  int unused = 0;
+  kernel_fact(nullptr, 5, &unused, [&](int* out) {
+    int dev = 0;
+    cudaMemPool_t pool;
+    e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetDefaultMemPool(&pool, dev);
+    uint64_t keep = ~0ull;
+    if (e == cudaSuccess) e = cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    *out = 1;
+    return e == cudaSuccess;
+  });
+  return e;
+}
+
+// f32 inputs on the tcgen05 tensor cores: split pass (hi / lo planes, B's planes K-major), then the
+// contraction with chunked accumulation (gemm_tf32_tc.cuh).  The planes live in stream-ordered scratch.
+inline int32_t gemm_tf32_tc_launch(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
+                                   uint32_t* status, cudaStream_t s) {
+  namespace g = gemm_tf32_tc;
+  const uint64_t M = d->m, N = d->n, K = d->k, B = d->batch;
+  const GemmPitch ld = gemm_pitch(d);
+  int sms = 0;
+  int32_t st = sm_count(err, &sms);
+  if (st != TSM100_OK) return st;
+  cudaError_t e = keep_pool_memory_once();
+  if (e != cudaSuccess) return cuda_ok(err, e, "cudaMemPoolSetAttribute");
+  const size_t a_plane = static_cast<size_t>(B) * M * K, b_plane = static_cast<size_t>(B) * N * K;  // elements
+  float* ws = nullptr;
+  e = cudaMallocAsync(reinterpret_cast<void**>(&ws), 2 * (a_plane + b_plane) * sizeof(float), s);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return op_fail(err, TSM100_ERR_MEMORY, std::string("gemm: scratch for the operand planes: ") + cudaGetErrorString(e));
+  }
+  float *a_hi = ws, *a_lo = ws + a_plane, *b_hi = ws + 2 * a_plane, *b_lo = b_hi + b_plane;
+  const float* af = static_cast<const float*>(a);
+  const float* bf = static_cast<const float*>(b);
+  auto grid1d = [&](uint64_t items) {
+    return static_cast<unsigned>(std::max<uint64_t>(1, std::min<uint64_t>((items + 255) / 256, static_cast<uint64_t>(sms) * 16)));
+  };
+  g::split_rows_kernel<<<dim3(grid1d(M * K / 4), static_cast<unsigned>(B)), 256, 0, s>>>(
+      af, ld.lda, static_cast<int64_t>(M) * ld.lda, a_hi, a_lo, static_cast<int64_t>(M), static_cast<int32_t>(K));
+  if (d->b_transposed) {
+    g::split_rows_kernel<<<dim3(grid1d(N * K / 4), static_cast<unsigned>(B)), 256, 0, s>>>(
+        bf, ld.ldb, static_cast<int64_t>(N) * ld.ldb, b_hi, b_lo, static_cast<int64_t>(N), static_cast<int32_t>(K));
+  } else {
+    g::split_transpose_kernel<<<dim3(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>(B)), 256, 0, s>>>(
+        bf, ld.ldb, static_cast<int64_t>(K) * ld.ldb, b_hi, b_lo, static_cast<int32_t>(K), static_cast<int32_t>(N));
+  }
+  st = cuda_ok(err, cudaGetLastError(), "gemm operand split launch");
+  CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo;
+  const CUtensorMapDataType f32 = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  if (st == TSM100_OK) st = make_tmap_3d(err, &ta_hi, a_hi, K, M, B, K, M * K, g::kBK, g::kBM, f32, 4);
+  if (st == TSM100_OK) st = make_tmap_3d(err, &ta_lo, a_lo, K, M, B, K, M * K, g::kBK, g::kBM, f32, 4);
+  if (st == TSM100_OK) st = make_tmap_3d(err, &tb_hi, b_hi, K, N, B, K, N * K, g::kBK, g::kBN, f32, 4);
+  if (st == TSM100_OK) st = make_tmap_3d(err, &tb_lo, b_lo, K, N, B, K, N * K, g::kBK, g::kBN, f32, 4);
+  if (st == TSM100_OK) {
+    g::Params p;
+    p.m = static_cast<int32_t>(M);
+    p.n = static_cast<int32_t>(N);
+    p.k = static_cast<int32_t>(K);
+    p.batch = d->batch;
+    p.m_blocks = static_cast<int32_t>((M + g::kBM - 1) / g::kBM);
+    p.n_blocks = static_cast<int32_t>((N + g::kBN - 1) / g::kBN);
+    p.c_batch_stride = static_cast<int64_t>(M) * ld.ldc;
+    p.ldc = ld.ldc;
+    p.status = status;
+    const int64_t tiles = static_cast<int64_t>(p.m_blocks) * p.n_blocks * p.batch;
+    auto kern = g::gemm_tf32_tc_kernel;
+    e = set_dyn_smem_once(kern, g::kSmemBytes);
+    if (e == cudaSuccess) {
+      const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sms));
+      kern<<<grid, g::kThreads, g::kSmemBytes, s>>>(ta_hi, ta_lo, tb_hi, tb_lo, static_cast<float*>(c), p);
+      e = cudaGetLastError();
+    }
+    st = cuda_ok(err, e, "gemm_tf32_tc_kernel launch");
+  }
+  e = cudaFreeAsync(ws, s);  // stream-ordered: after the kernel that reads the planes
+  if (st == TSM100_OK && e != cudaSuccess) st = cuda_ok(err, e, "cudaFreeAsync");
+  return st;
+}
+
 template <typename OutT, bool kBT, bool kBf16>
 inline int32_t gemm_tc_launch(std::string* err, const tsm100_gemm_desc* d, const void* a, const void* b, void* c,
                               uint32_t* status, cudaStream_t s) {
@@ -703,7 +791,13 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
     // rows that start on 16-byte boundaries: tensor cores; anything else: the FP32 pipe
     const bool vec_ok = aligned16(a) && aligned16(b) && aligned16(c) && d->k % 4 == 0 && (d->b_transposed || d->n % 4 == 0) &&
                         d->n % 2 == 0 && ld.lda % 4 == 0 && ld.ldb % 4 == 0 && ld.ldc % 4 == 0;
-    if (vec_ok) return gemm_tf32x3_launch(err, d, a, b, c, s);
+    if (vec_ok) {
+      // enough 128 x 256 tiles to occupy the GPU: the tcgen05 kernel; fewer (the 512^3 configuration has 8):
+      // the warp-level kernel, whose 64 x 64 tiles and cluster split-K spread a small problem over the SMs
+      const int64_t tiles = ((d->m + 127) / 128) * ((d->n + 255) / 256) * d->batch;
+      if (status != nullptr && tiles >= 64 && tiles < 0x7fffffff && d->k >= 256) return gemm_tf32_tc_launch(err, d, a, b, c, status, s);
+      return gemm_tf32x3_launch(err, d, a, b, c, s);
+    }
     return gemm_simt_launch<float, float>(err, d, a, b, c, s);
   }
 
