@@ -91,6 +91,25 @@ def softmax_bf16_io(name="softmax_bf16_io", rows=1, cols=4096):
         "llvm.call @__tile_store_bf16(%arg1, %t3, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
 
 
+def narrow_then_softmax(name="narrow_then_softmax", rows=1, cols=1024):
+    """f32 load -> cast to f16 -> softmax_f16 -> f16 store: the operator would have to see ROUNDED inputs."""
+    return module(name, 2, consts(c0=0, r=rows, c=cols) + [
+        "%t0 = llvm.call @__tile_load_f32(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        "%t1 = llvm.call @__tile_cast_f32_f16(%c0, %t0, %r, %c) : (i32, i32, i32, i32) -> i32",
+        "%t2 = llvm.call @__tile_softmax_f16(%c0, %t1, %r, %c) : (i32, i32, i32, i32) -> i32",
+        "llvm.call @__tile_store_f16(%arg1, %t2, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+
+
+def cast_round_trip(name="cast_round_trip", rows=1, cols=1024, dt="bf16"):
+    """f32 load -> cast to bf16 -> cast back to f32 -> f32 store (the reference's bf16 round-trip test,
+    crates/rustc_codegen_tile/src/mlir_to_linalg.rs:2249-2263): a rounding in the middle of the kernel."""
+    return module(name, 2, consts(c0=0, r=rows, c=cols) + [
+        "%t0 = llvm.call @__tile_load_f32(%arg0, %r, %c) : (!llvm.ptr<1>, i32, i32) -> i32",
+        f"%t1 = llvm.call @__tile_cast_f32_{dt}(%c0, %t0, %r, %c) : (i32, i32, i32, i32) -> i32",
+        f"%t2 = llvm.call @__tile_cast_{dt}_f32(%c0, %t1, %r, %c) : (i32, i32, i32, i32) -> i32",
+        "llvm.call @__tile_store_f32(%arg1, %t2, %r, %c) : (!llvm.ptr<1>, i32, i32, i32) -> ()"])
+
+
 GENERIC_SOFTMAX = '''"builtin.module"() ({
   "llvm.func"() <{CConv = #llvm.cconv<ccc>, function_type = !llvm.func<void (ptr<1>, ptr<1>)>, linkage = #llvm.linkage<external>, sym_name = "softmax_generic"}> ({
   ^bb0(%arg0: !llvm.ptr<1>, %arg1: !llvm.ptr<1>):

@@ -126,6 +126,11 @@ def test_non_entry_functions_are_ignored(target):
     (F.softmax().replace("(%c0, %t0, %r, %c)", "(%c0, %t0, %r, %7)"), "not a compile-time integer constant"),
     (F.softmax().replace("(%arg0, %r, %c)", "(%c0, %r, %c)"), "not a global-memory pointer"),
     (F.matmul(dt="f16", out_dt="bf16"), "matmul output must be the input type or f32"),
+    # casts are relabels only where they change no value; a rounding in the middle of a kernel is refused, not skipped
+    (F.narrow_then_softmax(), "an operator reads a value narrowed to f16"),
+    (F.cast_round_trip(), "already narrowed to bf16"),
+    (F.softmax_bf16_io().replace("__tile_cast_f32_bf16", "__tile_cast_f32_f16"), "a value narrowed to f16 is stored as bf16"),
+    (F.softmax_bf16_io().replace("__tile_cast_bf16_f32", "__tile_cast_f16_f32"), "must widen a freshly loaded f16 tile"),
     (F.matmul().replace("%m, %n) : (!llvm.ptr<1>, i32, i32, i32) -> ()", "%n, %n) : (!llvm.ptr<1>, i32, i32, i32) -> ()")
      .replace("%n = llvm.mlir.constant(128", "%n = llvm.mlir.constant(64"), "shapes disagree"),
 ])

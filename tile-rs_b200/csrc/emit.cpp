@@ -268,6 +268,8 @@ struct Tile {
   double scalar2 = 0;           // Ewise clamp: hi
   std::string ew;               // Ewise: operator name ("add", "exp", "clamp", ...)
   long heads = 0, kv_heads = 0, seq = 0, dim = 0;  // Attention*
+  bool narrowed = false;        // the value went through an f32 -> 16-bit cast ...
+  Dt narrow_to = Dt::F32;       // ... to this type; only a store of that type may consume it (the store is the rounding)
 };
 
 struct Kernel {
@@ -547,7 +549,31 @@ Kernel lower(const Func& f) {
         store_cols = cx.int_of(c.args[3], "cols");
       } else if (starts_with(fn, "__tile_cast_")) {
         need(4);
-        Tile t = cx.tile_of(c.args[1]);  // a cast only relabels: arithmetic is f32 inside every kernel
+        // Arithmetic is f32 inside every kernel and values are rounded once, when they are stored.  A cast can
+        // therefore be a relabel only where the reference's arith.extf / arith.truncf
+        // (crates/rustc_codegen_tile/src/mlir_to_linalg.rs:1249-1303) would not change a value either:
+        //  * widening a freshly loaded 16-bit tile (exact), and
+        //  * narrowing the result right before a store of the narrow type (the store is that rounding).
+        // Anything else - an operator fed with narrowed values, a round trip through a 16-bit type - would need
+        // a rounding in the middle of the kernel and is refused instead of being silently skipped.
+        const std::string nm = fn.substr(std::strlen("__tile_cast_"));  // "f32_f16"
+        const size_t us = nm.find('_');
+        Dt from = Dt::F32, to = Dt::F32;
+        if (us == std::string::npos || !suffix_dtype("_" + nm.substr(0, us), &from) || !suffix_dtype("_" + nm.substr(us + 1), &to))
+          reject("kernel " + f.name + ": unknown cast " + fn);
+        Tile t = cx.tile_of(c.args[1]);
+        if (t.narrowed)
+          reject("kernel " + f.name + ": " + fn + " casts a value that was already narrowed to " + dt_name(t.narrow_to) +
+                 "; a round trip through a 16-bit type inside one kernel is not supported (values are rounded once, at the store)");
+        if (from != Dt::F32 && to == Dt::F32) {
+          if (t.kind != Kind::Load || t.dtype != from)
+            reject("kernel " + f.name + ": " + fn + " must widen a freshly loaded " + dt_name(from) + " tile");
+        } else if (from == Dt::F32 && to != Dt::F32) {
+          t.narrowed = true;
+          t.narrow_to = to;
+        } else {
+          reject("kernel " + f.name + ": " + fn + " is neither a widening nor a narrowing cast");
+        }
         cx.tiles[c.result] = t;
       } else if (starts_with(fn, "__tile_softmax_") && has_dt) {
         need(4);
@@ -724,7 +750,16 @@ Kernel lower(const Func& f) {
   }
 
   if (stored_tile.empty()) reject("kernel " + f.name + ": no tile store; nothing to compute");
+  for (const auto& kv : cx.tiles)
+    for (const std::string& in : kv.second.in) {
+      auto it = cx.tiles.find(in);
+      if (it != cx.tiles.end() && it->second.narrowed)
+        reject("kernel " + f.name + ": an operator reads a value narrowed to " + dt_name(it->second.narrow_to) +
+               " by a cast; it would see the unrounded f32 values here - cast after the operator, or load the narrow type");
+    }
   const Tile& root = cx.tile_of(stored_tile);
+  if (root.narrowed && root.narrow_to != store_dt)
+    reject("kernel " + f.name + ": a value narrowed to " + dt_name(root.narrow_to) + " is stored as " + dt_name(store_dt));
   std::ostringstream body, inst, sum;
   const Dt out_dt = store_dt;
 
