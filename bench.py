@@ -702,6 +702,40 @@ class Ctx:
     pass
 
 
+def copy_probe(ctx, nbytes=1 << 30):
+    """What the box gives plain page-locked copies, so that the end-to-end figure can be read against it: 1 GiB
+    host-to-device alone, device-to-host alone, and both at once on two streams; every rank at the same time,
+    slowest rank's time, aggregate GB/s per direction."""
+    torch = _torch()
+    h_in, h_out = HostBuf(ctx, (nbytes // 4,), np.float32), HostBuf(ctx, (nbytes // 4,), np.float32)
+    d_in = torch.empty(nbytes // 4, dtype=torch.float32, device=ctx.tdev)
+    d_out = torch.zeros(nbytes // 4, dtype=torch.float32, device=ctx.tdev)
+    s1, s2 = ctx.dev.create_stream(), ctx.dev.create_stream()
+    up = lambda: ctx.hal.check(ctx.lib.tsm100_memcpy_h2d(ctx.dev._h, d_in.data_ptr(), h_in.ptr, nbytes, s1.raw))
+    down = lambda: ctx.hal.check(ctx.lib.tsm100_memcpy_d2h(ctx.dev._h, h_out.ptr, d_out.data_ptr(), nbytes, s2.raw))
+
+    def timed(*fns):
+        best = None
+        for _ in range(3):
+            torch.cuda.synchronize()
+            if ctx.world > 1:
+                ctx.dist.barrier()
+            t0 = time.perf_counter()
+            for fn in fns:
+                fn()
+            s1.synchronize()
+            s2.synchronize()
+            dt = max_over_ranks(ctx, time.perf_counter() - t0)
+            best = dt if best is None else min(best, dt)
+        return round(ctx.world * nbytes / best / 1e9, 1)
+
+    out = {"bytes_each": nbytes, "h2d_alone_gbs": timed(up), "d2h_alone_gbs": timed(down), "both_gbs_per_direction": timed(up, down),
+           "note": "aggregate over ranks, plain cudaMemcpyAsync of page-locked memory, best of 3"}
+    h_in.free()
+    h_out.free()
+    return out
+
+
 # --------------------------------------------------------------------------- timing
 def time_steps(ctx, fn, steps, warmup):
     """Returns (total ms over `steps`, maximum over ranks; list of this rank's per-step ms), device-timed on the launching stream."""
@@ -864,6 +898,9 @@ def measure(ctx, name, args, peaks, steps, warmup, headline=False, shared=None, 
         assert same, f"{name}: the host-buffer call and the device-buffer call disagree"
         rec["e2e"] = {"value": round(ctx.world * wl.work() / dt / scale, 2), "unit": unit, "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo,
                       "ms_per_step": round(dt * 1e3, 3), "steps": n_e2e, "api": api, "matches_device_path": same}
+        if headline:
+            rec["e2e"]["gbs_per_direction"] = round(ctx.world * bi / dt / 1e9, 1)
+            rec["e2e"]["copy_probe"] = copy_probe(ctx)
 
     if ctx.rank == 0 and ctx.world == 1 and not args.no_cpu_baseline and hasattr(wl, "cpu_run") and not reduced:
         v, sample = wl.cpu_run(ctx.oracle, args.cpu_seconds if headline else min(args.cpu_seconds, 5.0))

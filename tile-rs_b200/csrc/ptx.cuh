@@ -65,6 +65,10 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+__device__ __forceinline__ void st_shared_v4(uint32_t smem_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)
@@ -113,6 +117,25 @@ __device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, vo
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t site) {
   return mbar_wait_for(bar, parity, abort_flag, status, site, kWaitLimitNs);
+}
+
+// Bounded wait until a word in shared memory, which only ever grows, has reached `value`.
+__device__ __forceinline__ bool wait_counter_ge(volatile uint32_t* counter, uint32_t value, volatile uint32_t* abort_flag,
+                                                uint32_t* status, uint32_t site) {
+  if (*counter >= value) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (*counter >= value) return true;
+    if ((++spins & 0x3ffu) == 0u) {
+      if (*abort_flag != 0u) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1u;
+        atomicCAS(status, kStatusOk, kStatusWaitTimeout | site);
+        return false;
+      }
+    }
+  }
 }
 
 // The same bounded wait without acquire semantics.  For threads that only hand the
