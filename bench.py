@@ -426,6 +426,19 @@ class GemmWL(Workload):
     def strong_units(self):
         return self.n if self.single else self.units
 
+    def step(self):
+        """The whole configuration through the C ABI with a descriptor built once (the 512^3 problem is latency-bound:
+        building a ctypes structure per call costs as much as a tenth of its kernel)."""
+        if not hasattr(self, "_desc"):
+            capi = self.ctx.pkg.capi
+            self._desc = capi.GemmDesc(self.code, self.code, 0, self.units, self.m, self.n, self.k, 0, 0, 0)
+            self._call = (self.ctx.lib.tsm100_gemm, self.ctx.dev._h, C.byref(self._desc), self.a.data_ptr(), self.b.data_ptr(),
+                          self.c.data_ptr(), self.ctx.stream or None)
+        fn = self._call
+        st = fn[0](*fn[1:])
+        if st != 0:
+            self.ctx.hal.check(st)
+
     def step_range(self, first, count):
         d, es = self.ctx.dev, self.es
         if self.single:  # columns [first, first + count) of C = A * B, in place inside the full matrices
@@ -905,6 +918,23 @@ def measure(ctx, name, args, peaks, steps, warmup, headline=False, shared=None, 
     if ctx.rank == 0 and ctx.world == 1 and not args.no_cpu_baseline and hasattr(wl, "cpu_run") and not reduced:
         v, sample = wl.cpu_run(ctx.oracle, args.cpu_seconds if headline else min(args.cpu_seconds, 5.0))
         rec["cpu_baseline"] = {"value": round(v, 4), "unit": unit, "cores": ctx.oracle.num_threads(), "kind": "port", "sample": sample}
+    if name == "gemm_f32_512" and not reduced:
+        # a latency-bound configuration: what one call costs the host, and the GPU, apart from the per-step event above
+        n = 200
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            wl.step()
+        host_us = (time.perf_counter() - t0) / n * 1e6  # the queue holds 200 small launches: nothing blocks
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            wl.step()
+        e1.record()
+        torch.cuda.synchronize()
+        rec["latency"] = {"host_us_per_call": round(host_us, 2), "device_us_per_call_back_to_back": round(e0.elapsed_time(e1) / n * 1e3, 2),
+                          "note": "host: Python + ctypes + launch, no synchronisation; device: 200 launches between two events"}
     if hasattr(wl, "context") and ctx.world == 1 and not reduced and not args.no_context:
         c = wl.context()
         if c:
@@ -999,6 +1029,8 @@ def run_ours(args):
                 b["strong_x"] = r["strong"]["speedup_vs_one_gpu"]
             if "context" in r and r["context"].get("torch_sdpa_tflops"):
                 b["sdpa"] = r["context"]["torch_sdpa_tflops"]
+            if "latency" in r:
+                b["host_us"], b["dev_us"] = r["latency"]["host_us_per_call"], r["latency"]["device_us_per_call_back_to_back"]
             return b
 
         allrec = {args.workload: head, **extras}

@@ -343,5 +343,253 @@ gemm_tf32_tc_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_
   }
 }
 
+// ---------------------------------------------------------------------------
+// the contraction on CTA pairs (tcgen05 cta_group::2): a 256 x 256 output tile per pair of SMs
+// ---------------------------------------------------------------------------
+// With hi and lo planes a single CTA's stage is 96 KiB: two stages fit, and the loads of a stage have one
+// stage of MMA time to arrive (measured: tensor pipe 75 % busy).  In a pair each CTA stages its own 128 rows of
+// A and its own 128 columns of B (64 KiB per k-block, three stages), the hardware feeds both halves of B to both
+// SMs, and the leader's thread issues for both.  No TMA multicast: every CTA loads exactly the bytes it keeps,
+// completion bytes counted on the leader's mbarrier.  Chunked accumulation as above; each CTA's eight epilogue
+// warps keep the running sums of its own 128 x 256 half.
+namespace pair {
+constexpr int kPairM = 256;
+constexpr int kCtaM = 128;
+constexpr int kCtaN = 128;             // columns of B staged by each CTA
+constexpr int kStages = 3;
+constexpr int kPlane = kCtaM * kBK * 4;            // 16 KiB: every plane a CTA stages
+constexpr int kStageBytes = 4 * kPlane;            // A_hi, A_lo, B_hi, B_lo
+constexpr int kGroupM = 8;             // pair tiles per band
+
+struct alignas(8) Barriers {
+  uint64_t full[kStages];      // used in the leader: both CTAs' bytes of a stage have landed
+  uint64_t empty[kStages];     // in each CTA: the MMAs reading the stage have retired
+  uint64_t acc_full[2];        // in each CTA: chunk accumulator complete
+  uint64_t acc_empty[2];       // used in the leader: 16 epilogue warps of the pair have drained it
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+constexpr int kSmemBytes = kStages * kStageBytes + sizeof(Barriers) + 1024;
+
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int& b, int& mb, int& nb) {
+  const int per_batch = p.m_blocks * p.n_blocks;
+  b = tile / per_batch;
+  int t = tile - b * per_batch;
+  const int band_tiles = kGroupM * p.n_blocks;
+  const int band = t / band_tiles;
+  const int first_m = band * kGroupM;
+  const int rows_in_band = min(kGroupM, p.m_blocks - first_m);
+  t -= band * band_tiles;
+  mb = first_m + t % rows_in_band;
+  nb = t / rows_in_band;
+}
+
+__device__ __forceinline__ void tcgen05_mma_tf32_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// m_blocks / n_blocks of Params count 256 x 256 pair tiles here.
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tf32_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_constant__ CUtensorMap tmap_a_lo,
+                     const __grid_constant__ CUtensorMap tmap_b_hi, const __grid_constant__ CUtensorMap tmap_b_lo,
+                     float* __restrict__ c, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.batch * p.m_blocks * p.n_blocks;
+  const int num_kb = (p.k + kBK - 1) / kBK;
+  const int num_chunks = (num_kb + kChunkKb - 1) / kChunkKb;
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&bars->full[s], 1);
+      ptx::mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&bars->acc_full[a], 1);
+      ptx::mbar_init(&bars->acc_empty[a], 16);  // 8 epilogue warps in each CTA of the pair
+    }
+    bars->abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(&bars->tmem_base, kTmemCols);
+    ptx::tmem_relinquish_alloc_permit_pair();
+  }
+  ptx::tcgen05_fence_before_thread_sync();
+  ptx::cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  ptx::tcgen05_fence_after_thread_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_a_hi);
+      ptx::prefetch_tensormap(&tmap_a_lo);
+      ptx::prefetch_tensormap(&tmap_b_hi);
+      ptx::prefetch_tensormap(&tmap_b_lo);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        int b, mb, nb;
+        pair::tile_coords(p, tile, b, mb, nb);
+        const int row0 = mb * kPairM + static_cast<int>(rank) * kCtaM;
+        const int col0 = nb * kBN + static_cast<int>(rank) * kCtaN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag, p.status, 45)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = ptx::mapa_shared(ptx::smem_u32(&bars->full[stage]), 0);
+          if (rank == 0) ptx::mbar_arrive_expect_tx(&bars->full[stage], 2 * kStageBytes);
+          uint8_t* st = smem + stage * kStageBytes;
+          ptx::tma_load_3d_pair(st, &tmap_a_hi, full_leader, kb * kBK, row0, b);
+          ptx::tma_load_3d_pair(st + kPlane, &tmap_a_lo, full_leader, kb * kBK, row0, b);
+          ptx::tma_load_3d_pair(st + 2 * kPlane, &tmap_b_hi, full_leader, kb * kBK, col0, b);
+          ptx::tma_load_3d_pair(st + 3 * kPlane, &tmap_b_lo, full_leader, kb * kBK, col0, b);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) --------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(kPairM, kBN);
+      constexpr uint64_t kmajor = ptx::make_smem_desc_base(16, 1024);
+      constexpr uint32_t kstep = kUmmaK * 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      uint32_t chunk_count = 0;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        for (int ch = 0; ch < num_chunks && ok; ++ch, ++chunk_count) {
+          const uint32_t acc = chunk_count & 1u;
+          const uint32_t acc_phase = (chunk_count >> 1) & 1u;
+          if (!ptx::mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 46)) {
+            ok = false;
+            break;
+          }
+          ptx::tcgen05_fence_after_thread_sync();
+          const uint32_t d_tmem = tmem_base + acc * kBN;
+          const int kb_end = min(num_kb, (ch + 1) * kChunkKb);
+          for (int kb = ch * kChunkKb; kb < kb_end; ++kb) {
+            if (!ptx::mbar_wait_relaxed(&bars->full[stage], phase, abort_flag, p.status, 47)) {
+              ok = false;
+              break;
+            }
+            ptx::tcgen05_fence_after_thread_sync();
+            const uint32_t a_hi = ptx::smem_u32(smem + stage * kStageBytes);
+            const uint32_t a_lo = a_hi + kPlane, b_hi = a_hi + 2 * kPlane, b_lo = a_hi + 3 * kPlane;
+            const bool first_kb = kb == ch * kChunkKb;
+#pragma unroll
+            for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+              const uint32_t off = kk * kstep;
+              tcgen05_mma_tf32_ss_pair(d_tmem, ptx::smem_desc(kmajor, a_lo + off), ptx::smem_desc(kmajor, b_hi + off), idesc,
+                                       (first_kb && kk == 0) ? 0u : 1u);
+              tcgen05_mma_tf32_ss_pair(d_tmem, ptx::smem_desc(kmajor, a_hi + off), ptx::smem_desc(kmajor, b_lo + off), idesc, 1u);
+              tcgen05_mma_tf32_ss_pair(d_tmem, ptx::smem_desc(kmajor, a_hi + off), ptx::smem_desc(kmajor, b_hi + off), idesc, 1u);
+            }
+            ptx::tcgen05_commit_pair(&bars->empty[stage], 3);  // frees the stage in both CTAs
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (ok) ptx::tcgen05_commit_pair(&bars->acc_full[acc], 3);
+        }
+      }
+    }
+  } else {
+    // ------------------------------ chunk drain and output (both CTAs) ----------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * 128;
+    uint32_t chunk_count = 0;
+    bool alive = true;
+    for (int tile = pair_id; tile < num_tiles && alive; tile += num_pairs) {
+      int b, mb, nb;
+      pair::tile_coords(p, tile, b, mb, nb);
+      float sum[4][32];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sum[cc][i] = 0.f;
+      for (int ch = 0; ch < num_chunks; ++ch, ++chunk_count) {
+        const uint32_t acc = chunk_count & 1u;
+        const uint32_t acc_phase = (chunk_count >> 1) & 1u;
+        const bool ready = ptx::mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, p.status, 48);
+        if (!__all_sync(0xffffffffu, ready)) {
+          alive = false;
+          break;
+        }
+        ptx::tcgen05_fence_after_thread_sync();
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(lane_addr + acc * kBN + cc * 32, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sum[cc][i] += __uint_as_float(v[i]);
+        }
+        ptx::tcgen05_fence_before_thread_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(&bars->acc_empty[acc]), 0));
+      }
+      if (!alive) break;
+      const int row = mb * kPairM + static_cast<int>(rank) * kCtaM + quad * 32 + lane;
+      if (row < p.m) {
+        float* crow = c + static_cast<int64_t>(b) * p.c_batch_stride + static_cast<int64_t>(row) * p.ldc;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int col = nb * kBN + half * 128 + cc * 32;
+          if (col + 32 <= p.n) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              reinterpret_cast<float4*>(crow + col)[i] = make_float4(sum[cc][4 * i], sum[cc][4 * i + 1], sum[cc][4 * i + 2], sum[cc][4 * i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col + i < p.n) crow[col + i] = sum[cc][i];
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  if (*abort_flag != 0u) {
+    const unsigned long long t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 1000000ull) {
+    }
+  }
+  ptx::tcgen05_fence_before_thread_sync();
+  // Neither CTA may leave while the other can still read its shared memory (the leader's MMAs) or signal its barriers.
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tcgen05_fence_after_thread_sync();
+    ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+}  // namespace pair
+
 }  // namespace gemm_tf32_tc
 }  // namespace tsm100

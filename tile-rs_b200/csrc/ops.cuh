@@ -636,30 +636,67 @@ inline int32_t gemm_tf32_tc_launch(std::string* err, const tsm100_gemm_desc* d, 
   st = cuda_ok(err, cudaGetLastError(), "gemm operand split launch");
   CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo;
   const CUtensorMapDataType f32 = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  // Problems with more than one 128-row and 128-column block run on CTA pairs (256 x 256 tiles, each CTA staging
+  // 128 rows of A and 128 columns of B); the rest on single CTAs (128 x 256 tiles).
+  const bool pairs = M > 128 && N > 128;
+  const uint32_t box_b = pairs ? g::pair::kCtaN : g::kBN;
   if (st == TSM100_OK) st = make_tmap_3d(err, &ta_hi, a_hi, K, M, B, K, M * K, g::kBK, g::kBM, f32, 4);
   if (st == TSM100_OK) st = make_tmap_3d(err, &ta_lo, a_lo, K, M, B, K, M * K, g::kBK, g::kBM, f32, 4);
-  if (st == TSM100_OK) st = make_tmap_3d(err, &tb_hi, b_hi, K, N, B, K, N * K, g::kBK, g::kBN, f32, 4);
-  if (st == TSM100_OK) st = make_tmap_3d(err, &tb_lo, b_lo, K, N, B, K, N * K, g::kBK, g::kBN, f32, 4);
+  if (st == TSM100_OK) st = make_tmap_3d(err, &tb_hi, b_hi, K, N, B, K, N * K, g::kBK, box_b, f32, 4);
+  if (st == TSM100_OK) st = make_tmap_3d(err, &tb_lo, b_lo, K, N, B, K, N * K, g::kBK, box_b, f32, 4);
   if (st == TSM100_OK) {
     g::Params p;
     p.m = static_cast<int32_t>(M);
     p.n = static_cast<int32_t>(N);
     p.k = static_cast<int32_t>(K);
     p.batch = d->batch;
-    p.m_blocks = static_cast<int32_t>((M + g::kBM - 1) / g::kBM);
+    p.m_blocks = static_cast<int32_t>((M + (pairs ? g::pair::kPairM : g::kBM) - 1) / (pairs ? g::pair::kPairM : g::kBM));
     p.n_blocks = static_cast<int32_t>((N + g::kBN - 1) / g::kBN);
     p.c_batch_stride = static_cast<int64_t>(M) * ld.ldc;
     p.ldc = ld.ldc;
     p.status = status;
     const int64_t tiles = static_cast<int64_t>(p.m_blocks) * p.n_blocks * p.batch;
-    auto kern = g::gemm_tf32_tc_kernel;
-    e = set_dyn_smem_once(kern, g::kSmemBytes);
-    if (e == cudaSuccess) {
-      const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sms));
-      kern<<<grid, g::kThreads, g::kSmemBytes, s>>>(ta_hi, ta_lo, tb_hi, tb_lo, static_cast<float*>(c), p);
-      e = cudaGetLastError();
+    if (pairs) {
+      auto kern = g::pair::gemm_tf32_tc2_kernel;
+      e = set_dyn_smem_once(kern, g::pair::kSmemBytes);
+      if (e == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.blockDim = dim3(g::kThreads);
+        cfg.dynamicSmemBytes = g::pair::kSmemBytes;
+        cfg.stream = s;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1));
+        int max_clusters = sms / 2;
+        kernel_fact(reinterpret_cast<const void*>(kern), kFactClusters, &max_clusters, [&](int* out) {
+          int n = 0;
+          if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+            (void)cudaGetLastError();
+            return false;
+          }
+          *out = n;
+          return true;
+        });
+        const int64_t npairs = std::min<int64_t>(tiles, std::min<int64_t>(max_clusters, sms / 2));
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * npairs));
+        e = cudaLaunchKernelEx(&cfg, kern, ta_hi, ta_lo, tb_hi, tb_lo, static_cast<float*>(c), p);
+      }
+      st = cuda_ok(err, e, "gemm_tf32_tc2_kernel launch");
+    } else {
+      auto kern = g::gemm_tf32_tc_kernel;
+      e = set_dyn_smem_once(kern, g::kSmemBytes);
+      if (e == cudaSuccess) {
+        const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sms));
+        kern<<<grid, g::kThreads, g::kSmemBytes, s>>>(ta_hi, ta_lo, tb_hi, tb_lo, static_cast<float*>(c), p);
+        e = cudaGetLastError();
+      }
+      st = cuda_ok(err, e, "gemm_tf32_tc_kernel launch");
     }
-    st = cuda_ok(err, e, "gemm_tf32_tc_kernel launch");
   }
   e = cudaFreeAsync(ws, s);  // stream-ordered: after the kernel that reads the planes
   if (st == TSM100_OK && e != cudaSuccess) st = cuda_ok(err, e, "cudaFreeAsync");
