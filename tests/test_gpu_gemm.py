@@ -26,7 +26,10 @@ def run_gemm(dev, capi, a, b, m, n, k, dtype, out_dtype=None, b_transposed=False
 @pytest.mark.parametrize("m,n,k,bt", [(512, 512, 512, False), (512, 512, 512, True), (65, 33, 17, False),
                                        (1, 1, 1, False), (100, 300, 77, True), (130, 70, 260, False),
                                        (100, 300, 76, True), (130, 72, 260, False), (64, 64, 4096, False), (1, 4, 8, False),
-                                       (1024, 1024, 1024, False), (70, 2, 128, True), (3, 1000, 36, False)])
+                                       (1024, 1024, 1024, False), (70, 2, 128, True), (3, 1000, 36, False),
+                                       # more small and ragged shapes of the warp-level kernel
+                                       (384, 640, 512, False), (384, 640, 512, True), (128, 128, 64, False), (129, 132, 68, True),
+                                       (1200, 1400, 128, False), (256, 256, 2048, False), (200, 12, 300, False)])
 def test_gemm_f32(dev, pkg, oracle, m, n, k, bt):
     capi = pkg.capi
     a = util.gen_uniform(capi, (m, k), 101)

@@ -827,12 +827,13 @@ inline int32_t gemm(std::string* err, const tsm100_gemm_desc* d, const void* a, 
   if (d->dtype == TSM100_F32) {
     // rows that start on 16-byte boundaries: tensor cores; anything else: the FP32 pipe
     const bool vec_ok = aligned16(a) && aligned16(b) && aligned16(c) && d->k % 4 == 0 && (d->b_transposed || d->n % 4 == 0) &&
-                        d->n % 2 == 0 && ld.lda % 4 == 0 && ld.ldb % 4 == 0 && ld.ldc % 4 == 0;
+                        d->n % 2 == 0 && ld.lda % 4 == 0 && ld.ldb % 4 == 0 && ld.ldc % 2 == 0;
     if (vec_ok) {
-      // enough 128 x 256 tiles to occupy the GPU: the tcgen05 kernel; fewer (the 512^3 configuration has 8):
-      // the warp-level kernel, whose 64 x 64 tiles and cluster split-K spread a small problem over the SMs
+      // enough 128 x 256 tiles to occupy the GPU: the persistent tcgen05 kernels (operand planes from a split pass)
       const int64_t tiles = ((d->m + 127) / 128) * ((d->n + 255) / 256) * d->batch;
       if (status != nullptr && tiles >= 64 && tiles < 0x7fffffff && d->k >= 256) return gemm_tf32_tc_launch(err, d, a, b, c, status, s);
+      // fewer tiles (the 512^3 configuration has 8): the warp-level kernel, whose 64 x 64 tiles and cluster split-K
+      // spread a small problem over the SMs
       return gemm_tf32x3_launch(err, d, a, b, c, s);
     }
     return gemm_simt_launch<float, float>(err, d, a, b, c, s);
