@@ -751,7 +751,9 @@ def copy_probe(ctx, nbytes=1 << 30):
 
 # --------------------------------------------------------------------------- timing
 def time_steps(ctx, fn, steps, warmup):
-    """Returns (total ms over `steps`, maximum over ranks; list of this rank's per-step ms), device-timed on the launching stream."""
+    """Returns (total ms over `steps`, maximum over ranks; list of this rank's per-step ms), device-timed on the launching
+    stream.  The total is taken between two events around the whole loop (an event after every step would add a few
+    microseconds to each, a fifth of the 512^3 GEMM's own time); the per-step spread comes from a second, untimed pass."""
     torch = _torch()
     for _ in range(warmup):
         fn()
@@ -759,17 +761,22 @@ def time_steps(ctx, fn, steps, warmup):
     if ctx.world > 1:
         ctx.dist.barrier()
     torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if ctx.world > 1:
+        ctx.dist.barrier()
+    total = max_over_ranks(ctx, e0.elapsed_time(e1))
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     evs[0].record()
     for i in range(steps):
         fn()
         evs[i + 1].record()
     torch.cuda.synchronize()
-    if ctx.world > 1:
-        ctx.dist.barrier()
-    total = evs[0].elapsed_time(evs[-1])
     per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
-    total = max_over_ranks(ctx, total)
     assert ctx.dev.status() == 0, "a kernel reported a timed-out device-side wait"
     return total, per
 
@@ -855,7 +862,7 @@ def measure(ctx, name, args, peaks, steps, warmup, headline=False, shared=None, 
     ms = total_ms / steps
     rec = {"value": round(ctx.world * wl.work() / (ms * 1e-3) / scale, 2), "unit": unit, "ms_per_step": round(ms, 4),
            "ms_per_step_min": round(min(per), 4), "ms_per_step_max": round(max(per), 4), "dtype": wl.dtype, "steps": steps}
-    roof = roofline_for(wl, statistics.mean(per) / wl.launches_per_step, peaks)
+    roof = roofline_for(wl, ms / wl.launches_per_step, peaks)
     roof["traffic"] = NCU_TRAFFIC.get(name)
     rec["roofline"] = roof
     rec["clocks"] = clk.summary()
