@@ -838,8 +838,9 @@ NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per full-size la
     "softmax_f32": 4 * (268.5e6 + 215.7e6),       # captured on a quarter of the rows, scaled by rows
     "softmax_bf16": 4 * (134.2e6 + 79.0e6),
     "gemm_bf16_8192": 1064.7e6 + 127.0e6,
-    "attention_causal": 4 * (201.4e6 + 48.2e6),   # captured on 64 of 256 heads, scaled by heads
-    "attention_noncausal": 4 * (201.4e6 + 48.0e6),
+    "gemm_f32_4096": 629.1e6 + 63.6e6 + 134.2e6 + 156.8e6,  # contraction + the two split kernels
+    "attention_causal": 4 * (201.4e6 + 48.6e6),   # captured on 64 of 256 heads, scaled by heads
+    "attention_noncausal": 4 * (201.4e6 + 49.2e6),
     "rms_norm_f32": 4 * (268.4e6 + 214.9e6),
     "reduce_sum_f32": 4 * (268.5e6 + 3.2e6),
     "silu_mul_f32": 4 * (536.9e6 + 229.3e6),
@@ -871,7 +872,7 @@ def measure(ctx, name, args, peaks, steps, warmup, headline=False, shared=None, 
         wl.step()
         torch.cuda.synchronize()
 
-    # sampled check of this rank's result against the CPU oracle (untimed); the verdicts of all ranks are combined
+    # sampled check of this rank's result against the CPU oracle (untimed); the outcomes of all ranks are combined
     if hasattr(wl, "verify") and not args.no_verify and not reduced:
         v = wl.verify(ctx.oracle)
         v["ok"] = all_ranks_ok(ctx, v["ok"])
