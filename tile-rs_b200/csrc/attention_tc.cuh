@@ -78,6 +78,7 @@ struct Params {
   int32_t heads_q, heads_kv, batch;
   int32_t causal;
   int32_t q_blocks;        // ceil(seq / 256)
+  int32_t kv_band;         // causal launch order: KV heads per band (>= 1), see the block index mapping in the kernel
   float scale_log2;        // (1/sqrt(d)) * log2(e)
   uint32_t* status;
   // prefill against a KV cache (kCache kernels only): query row i sits at position q_offset + i of seq_kv
@@ -121,13 +122,26 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int lane = threadIdx.x & 31;
   volatile uint32_t* abort_flag = &bars->abort_flag;
 
-  // blockIdx -> (head, query block): heads of a KV group vary fastest, then the query
-  // blocks of that group (heaviest first when causal), then the (batch, KV head) groups.
+  // blockIdx -> (head, query block).  Heads of a KV group vary fastest.  Non-causal: then the query blocks of that
+  // group, then the (batch, KV head) groups.  Causal: a query block's work grows with its position, so within a band
+  // of kv_band KV heads (whose K and V fit the L2 together) all heads' heaviest blocks come first, then the next
+  // lighter ones, ...: longest-first over 16+ times more blocks than one head has, which is what keeps the SMs evenly
+  // loaded when a launch has only a few blocks per SM (a shard of the heads on one of several GPUs).
   const int group = p.heads_q / p.heads_kv;
   const int hg = blockIdx.x % group;
   const int t_rest = blockIdx.x / group;
-  const int qb_raw = t_rest % p.q_blocks;
-  const int kvh = t_rest / p.q_blocks;       // flattened (batch, KV head)
+  int qb_raw, kvh;                           // kvh: flattened (batch, KV head)
+  if (p.causal) {
+    const int total_kv = static_cast<int>(gridDim.x) / (group * p.q_blocks);
+    const int per_band = p.kv_band * p.q_blocks;
+    const int band = t_rest / per_band, rem = t_rest - band * per_band;
+    const int heads_here = min(p.kv_band, total_kv - band * p.kv_band);  // the last band may be smaller
+    qb_raw = rem / heads_here;
+    kvh = band * p.kv_band + rem - qb_raw * heads_here;
+  } else {
+    qb_raw = t_rest % p.q_blocks;
+    kvh = t_rest / p.q_blocks;
+  }
   const int bh = kvh * group + hg;           // flattened (batch, query head)
   const int qb = p.causal ? (p.q_blocks - 1 - qb_raw) : qb_raw;
   const int q0 = qb * 2 * kBQ;

@@ -945,6 +945,15 @@ inline int32_t attention_prefill_simt_launch(std::string* err, const tsm100_atte
   return cuda_ok(err, cudaGetLastError(), "attention_simt (prefill) launch");
 }
 
+// KV heads per band of the causal launch order: as many as keep K and V of the band (16-bit, head_dim 128) within
+// 32 MiB, a quarter of the L2, so that the blocks in flight - a few weight levels of one band, at a band's end
+// together with the start of the next - read K and V from DRAM once.
+inline int32_t attention_kv_band(uint64_t kv_len, int64_t kv_heads) {
+  const uint64_t per_head = std::max<uint64_t>(1, kv_len * attn::kD * 2 * 2);
+  const int64_t band = static_cast<int64_t>((32ull << 20) / per_head);
+  return static_cast<int32_t>(std::max<int64_t>(1, std::min<int64_t>(band, std::max<int64_t>(kv_heads, 1))));
+}
+
 template <bool kBf16>
 inline int32_t attention_prefill_tc_launch(std::string* err, const tsm100_attention_prefill_desc* d, const void* q, const void* k,
                                            const void* v, void* o, uint32_t* status, cudaStream_t s) {
@@ -963,6 +972,7 @@ inline int32_t attention_prefill_tc_launch(std::string* err, const tsm100_attent
   p.batch = 1;
   p.causal = 1;
   p.q_blocks = (d->seq_len + 2 * at::kBQ - 1) / (2 * at::kBQ);
+  p.kv_band = attention_kv_band(kv_len, d->heads_kv);
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
   p.status = status;
   p.seq_kv = static_cast<int32_t>(kv_len);
@@ -1217,6 +1227,7 @@ inline int32_t attention_tc_launch(std::string* err, const tsm100_attention_desc
   p.batch = d->batch;
   p.causal = d->causal ? 1 : 0;
   p.q_blocks = (d->seq + 2 * at::kBQ - 1) / (2 * at::kBQ);
+  p.kv_band = attention_kv_band(S, static_cast<int64_t>(nkv));
   p.scale_log2 = static_cast<float>((1.0 / std::sqrt(static_cast<double>(D))) * 1.4426950408889634);
   p.status = status;
   p.seq_kv = d->seq;
