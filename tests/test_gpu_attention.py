@@ -234,3 +234,10 @@ def test_attention_b8_h32_s4096_head_indexing(dev, pkg, oracle, causal):
 
 def test_attention_gqa_b2_64_8_s16384_head_indexing(dev, pkg, oracle):
     _sampled_heads_check(dev, pkg, oracle, 2, 64, 8, 16384, True, [(0, 0), (0, 63), (1, 9), (1, 56)], "gqa b2 64/8 s16384")
+
+
+def test_attention_causal_launch_order_ragged_last_band(dev, pkg, oracle):
+    """The causal launch order walks bands of KV heads whose K and V fit the L2 together; at seq 16384 a band is
+    4 KV heads, so 6 heads leave a last band of 2 (MHA) and 3 KV heads of a 6/3 GQA a single short one."""
+    _sampled_heads_check(dev, pkg, oracle, 1, 6, 6, 16384, True, [(0, 0), (0, 3), (0, 4), (0, 5)], "b1 h6 s16384")
+    _sampled_heads_check(dev, pkg, oracle, 3, 2, 1, 16384, True, [(0, 1), (1, 0), (2, 1)], "gqa b3 2/1 s16384")
