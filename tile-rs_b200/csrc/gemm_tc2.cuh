@@ -34,7 +34,7 @@ constexpr int kABytes = kCtaM * kBK * 2;  // 16 KiB
 constexpr int kBBytes = kCtaN * kBK * 2;  // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 512;
-constexpr int kGroupM = 8;  // pair tiles per band: the band's rows of A stay in L2 while B streams
+constexpr int kGroupM = 16;  // pair tiles per band: a wave of 74 tiles is 16 x 4.6 tiles; the band's rows of A are re-used from the L2 by the next wave (see the producer)
 
 struct alignas(8) Barriers {
   uint64_t full[kStages];      // used in the leader: both CTAs' bytes of a stage have landed
@@ -114,7 +114,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         gemm_tc2::tile_coords(p, tile, b, mb, nb);
         const int row0 = mb * kPairM + static_cast<int>(rank) * kCtaM;
         const int col0 = nb * kBN + static_cast<int>(rank) * kCtaN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        // Every other wave of tiles walks K backwards.  All pairs sweep K in step, so the band's rows of A a wave
+        // touched last are its last K slices; the next wave, which needs the same rows, starts with those and finds
+        // them in the L2 still (walking forwards again it would start with the slices touched longest ago).  The
+        // direction is a function of the tile's place in its own problem, so equal problems of a batch are summed
+        // in the same order and give the same bits.
+        const bool backward = (((tile % (p.m_blocks * p.n_blocks)) / num_pairs) & 1) != 0;
+        for (int kq = 0; kq < num_kb; ++kq) {
+          const int kb = backward ? num_kb - 1 - kq : kq;
           if (!ptx::mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag, p.status, 31)) {
             ok = false;
             break;
