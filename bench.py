@@ -837,7 +837,7 @@ def sustained_run(ctx, wl, seconds, peaks, gpu_index):
 NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per full-size launch (profiles/*.md)
     "softmax_f32": 4 * (268.5e6 + 215.7e6),       # captured on a quarter of the rows, scaled by rows
     "softmax_bf16": 4 * (134.2e6 + 79.0e6),
-    "gemm_bf16_8192": 1064.7e6 + 127.0e6,
+    "gemm_bf16_8192": 944.3e6 + 127.6e6,
     "gemm_f32_4096": 629.1e6 + 63.6e6 + 134.2e6 + 156.8e6,  # contraction + the two split kernels
     "attention_causal": 4 * (202.0e6 + 47.3e6),   # captured on 64 of 256 heads, scaled by heads
     "attention_noncausal": 4 * (201.4e6 + 49.2e6),
