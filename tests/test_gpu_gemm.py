@@ -270,3 +270,33 @@ def test_gemm_f32_tcgen05(dev, pkg, oracle, m, n, k, bt, batch):
         print(f"[parity] f32 GEMM {m}x{n}x{k} problem {i}: GPU rel_max {mt['rel_max']:.2e} rel_fro {mt['rel_fro']:.2e}; "
               f"f32 CPU loop rel_max {f32['rel_max']:.2e} rel_fro {f32['rel_fro']:.2e}")
         assert mt["rel_max"] <= util.F32_REL and mt["rel_fro"] <= util.F32_REL, (i, mt)
+
+
+@pytest.mark.parametrize("bt", [False, True])
+def test_gemm_bf16_row_blocks_give_the_bits_of_the_whole_problem(dev, pkg, bt):
+    """The pair kernel walks K forwards or backwards depending on a tile's column only, so an output element is summed
+    in the same order whether its rows are computed as part of the whole problem, as a row block of it (what the
+    host-buffer call streams), or as one problem of a batch."""
+    capi = pkg.capi
+    m, n, k = 4352, 4096, 2048   # 17 row tiles: a full band of 16 and a band of one
+    g = torch.Generator(device="cuda:0").manual_seed(77)
+    a = (torch.randn(m, k, device="cuda:0", generator=g) * k ** -0.25).to(torch.bfloat16)
+    b = (torch.randn((n, k) if bt else (k, n), device="cuda:0", generator=g) * k ** -0.25).to(torch.bfloat16)
+    whole = torch.empty(m, n, dtype=torch.bfloat16, device="cuda:0")
+    st = util.cur_stream(torch)
+    dev.gemm(capi.BF16, m, n, k, a.data_ptr(), b.data_ptr(), whole.data_ptr(), b_transposed=bt, stream=st)
+    for r0, rows in ((0, 1024), (1024, 256), (1280, 3072)):
+        part = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda:0")
+        dev.gemm(capi.BF16, rows, n, k, a[r0:].data_ptr(), b.data_ptr(), part.data_ptr(), b_transposed=bt, stream=st)
+        torch.cuda.synchronize()
+        assert torch.equal(part.view(torch.int16), whole[r0:r0 + rows].view(torch.int16)), (r0, rows)
+    # the same problem twice in a batch of three, beside a different one
+    a3 = torch.stack([a[:1024], a[1024:2048], a[:1024]]).contiguous()
+    b3 = b[None].expand(3, *b.shape).contiguous()
+    c3 = torch.empty(3, 1024, n, dtype=torch.bfloat16, device="cuda:0")
+    dev.gemm(capi.BF16, 1024, n, k, a3.data_ptr(), b3.data_ptr(), c3.data_ptr(), b_transposed=bt, batch=3, stream=st)
+    torch.cuda.synchronize()
+    assert dev.status() == 0
+    assert torch.equal(c3[0].view(torch.int16), c3[2].view(torch.int16))
+    assert torch.equal(c3[0].view(torch.int16), whole[:1024].view(torch.int16))
+    assert torch.equal(c3[1].view(torch.int16), whole[1024:2048].view(torch.int16))
