@@ -505,9 +505,19 @@ class GemmWL(Workload):
         self.ctx.dev.gemm_host(self.code, self.m, self.n, self.k, self.a_host.addr, self.b_host.addr, self.c_host.addr, batch=self.units)
 
     def e2e_check(self):
+        # The host-buffer call streams a large A in row blocks, each a launch of its own; the 16-bit pair kernel
+        # orders its f32 sums by the waves of a launch, so a block may round a few results the other way: equal to
+        # one 16-bit rounding step, and nearly all bits equal.  f32 results and single-block problems are bit-equal.
         rows = sorted({0, self.m // 2 + 1, self.m - 1})
         p = self.units - 1
-        return bool(np.array_equal(self.c_host.array[p][rows], dev_rows_to_host(self.c[p], rows)))
+        x, y = self.c_host.array[p][rows], dev_rows_to_host(self.c[p], rows)
+        if np.array_equal(x, y):
+            return True
+        if self.dtype == "f32":
+            return False
+        xf, yf = self.ctx.oracle.bf16_to_f32(x), self.ctx.oracle.bf16_to_f32(y)
+        step = np.maximum(np.abs(xf), np.abs(yf)) * np.float32(2.0 ** -7) + np.float32(1e-5)  # near zero: the f32 sums' own error (results are O(1))
+        return bool((np.abs(xf - yf) <= step).all() and np.count_nonzero(x != y) <= 0.02 * x.size)
 
     def cpu_run(self, oracle, seconds):
         rows = min(self.m, 512 if self.dtype == "f32" and self.m <= 512 else 32)

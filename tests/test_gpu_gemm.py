@@ -273,10 +273,11 @@ def test_gemm_f32_tcgen05(dev, pkg, oracle, m, n, k, bt, batch):
 
 
 @pytest.mark.parametrize("bt", [False, True])
-def test_gemm_bf16_row_blocks_give_the_bits_of_the_whole_problem(dev, pkg, bt):
-    """The pair kernel walks K forwards or backwards depending on a tile's column only, so an output element is summed
-    in the same order whether its rows are computed as part of the whole problem, as a row block of it (what the
-    host-buffer call streams), or as one problem of a batch."""
+def test_gemm_bf16_batch_members_give_equal_bits_and_row_blocks_agree(dev, pkg, bt):
+    """The pair kernel walks K backwards in every other wave of tiles, counted inside a tile's own problem: equal
+    problems give equal bits wherever they stand in a batch and when launched alone.  A row block of a problem
+    launched on its own (what the host-buffer call streams) has other waves, so its f32 sums are taken in another
+    order: it agrees with the whole problem to one rounding of the 16-bit result."""
     capi = pkg.capi
     m, n, k = 4352, 4096, 2048   # 17 row tiles: a full band of 16 and a band of one
     g = torch.Generator(device="cuda:0").manual_seed(77)
@@ -289,14 +290,19 @@ def test_gemm_bf16_row_blocks_give_the_bits_of_the_whole_problem(dev, pkg, bt):
         part = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda:0")
         dev.gemm(capi.BF16, rows, n, k, a[r0:].data_ptr(), b.data_ptr(), part.data_ptr(), b_transposed=bt, stream=st)
         torch.cuda.synchronize()
-        assert torch.equal(part.view(torch.int16), whole[r0:r0 + rows].view(torch.int16)), (r0, rows)
-    # the same problem twice in a batch of three, beside a different one
+        x, y = part.float(), whole[r0:r0 + rows].float()
+        # one bf16 step at that magnitude, at most; results near zero (cancelling sums of O(1) terms) differ by the f32 sums' own error
+        ulp = torch.maximum(x.abs(), y.abs()) * 2.0 ** -7 + 1e-5
+        assert bool(((x - y).abs() <= ulp).all()), (r0, rows)
+        assert float((x != y).float().mean()) <= 0.02, (r0, rows)
+    # the same problem twice in a batch of three beside a different one, and alone
     a3 = torch.stack([a[:1024], a[1024:2048], a[:1024]]).contiguous()
     b3 = b[None].expand(3, *b.shape).contiguous()
     c3 = torch.empty(3, 1024, n, dtype=torch.bfloat16, device="cuda:0")
     dev.gemm(capi.BF16, 1024, n, k, a3.data_ptr(), b3.data_ptr(), c3.data_ptr(), b_transposed=bt, batch=3, stream=st)
+    alone = torch.empty(1024, n, dtype=torch.bfloat16, device="cuda:0")
+    dev.gemm(capi.BF16, 1024, n, k, a.data_ptr(), b.data_ptr(), alone.data_ptr(), b_transposed=bt, stream=st)
     torch.cuda.synchronize()
     assert dev.status() == 0
     assert torch.equal(c3[0].view(torch.int16), c3[2].view(torch.int16))
-    assert torch.equal(c3[0].view(torch.int16), whole[:1024].view(torch.int16))
-    assert torch.equal(c3[1].view(torch.int16), whole[1024:2048].view(torch.int16))
+    assert torch.equal(c3[0].view(torch.int16), alone.view(torch.int16))

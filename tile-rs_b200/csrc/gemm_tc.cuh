@@ -59,7 +59,6 @@ struct Params {
   int64_t c_batch_stride;  // elements
   int64_t ldc;             // row pitch of C in elements
   uint32_t* status;
-  int32_t wave_pairs;      // CTA pairs the GPU runs at once (SMs / 2): sets the K direction pattern of the pair kernel
 };
 
 __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& b, int& mb, int& nb) {

@@ -116,11 +116,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         const int col0 = nb * kBN + static_cast<int>(rank) * kCtaN;
         // Every other wave of tiles walks K backwards.  All pairs sweep K in step, so the band's rows of A a wave
         // touched last are its last K slices; the next wave, which needs the same rows, starts with those and finds
-        // them in the L2 still (walking forwards again it would start with the slices touched longest ago).  A wave
-        // of a full band is wave_pairs / kGroupM columns of tiles wide; the direction is taken from the tile's column
-        // alone, so the order of summation of an output element does not depend on how the rows of the problem are
-        // blocked or batched (a row block streamed from the host gives the same bits as the whole problem).
-        const bool backward = (((nb * kGroupM) / p.wave_pairs) & 1) != 0;
+        // them in the L2 still (walking forwards again it would start with the slices touched longest ago).  The
+        // wave is counted inside the tile's own problem, so equal problems of a batch are summed in the same order
+        // and give the same bits wherever they stand in the batch.
+        const bool backward = (((tile % (p.m_blocks * p.n_blocks)) / num_pairs) & 1) != 0;
         for (int kq = 0; kq < num_kb; ++kq) {
           const int kb = backward ? num_kb - 1 - kq : kq;
           if (!ptx::mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag, p.status, 31)) {

@@ -728,7 +728,6 @@ inline int32_t gemm_tc_launch(std::string* err, const tsm100_gemm_desc* d, const
   p.c_batch_stride = static_cast<int64_t>(M) * ld.ldc;
   p.ldc = ld.ldc;
   p.status = status;
-  p.wave_pairs = 1;  // not read by the single-CTA kernel
   int sms = 0;
   st = sm_count(err, &sms);
   if (st != TSM100_OK) return st;
@@ -773,7 +772,6 @@ inline int32_t gemm_tc2_launch(std::string* err, const tsm100_gemm_desc* d, cons
   int sms = 0;
   st = sm_count(err, &sms);
   if (st != TSM100_OK) return st;
-  p.wave_pairs = std::max(1, sms / 2);  // a property of the GPU, not of the problem: see the producer's K direction
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
