@@ -791,6 +791,36 @@ def time_steps(ctx, fn, steps, warmup):
     return total, per
 
 
+def time_alternating(ctx, fn_a, fn_b, steps, warmup, block=5):
+    """Times two loops against each other in the same thermal and power state: blocks of `block` steps of fn_a and of
+    fn_b alternate, each block between two events.  Returns (ms per step of fn_a, of fn_b), each the maximum over ranks."""
+    torch = _torch()
+    for _ in range(warmup):
+        fn_a()
+        fn_b()
+    torch.cuda.synchronize()
+    if ctx.world > 1:
+        ctx.dist.barrier()
+    torch.cuda.synchronize()
+    rounds = max(1, (steps + block - 1) // block)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(2 * rounds + 1)]
+    evs[0].record()
+    for r in range(rounds):
+        for _ in range(block):
+            fn_a()
+        evs[2 * r + 1].record()
+        for _ in range(block):
+            fn_b()
+        evs[2 * r + 2].record()
+    torch.cuda.synchronize()
+    if ctx.world > 1:
+        ctx.dist.barrier()
+    a = sum(evs[2 * r].elapsed_time(evs[2 * r + 1]) for r in range(rounds)) / (rounds * block)
+    b = sum(evs[2 * r + 1].elapsed_time(evs[2 * r + 2]) for r in range(rounds)) / (rounds * block)
+    assert ctx.dev.status() == 0, "a kernel reported a timed-out device-side wait"
+    return max_over_ranks(ctx, a), max_over_ranks(ctx, b)
+
+
 def max_over_ranks(ctx, value: float) -> float:
     if ctx.world == 1:
         return value
@@ -877,6 +907,24 @@ def measure(ctx, name, args, peaks, steps, warmup, headline=False, shared=None, 
     roof["traffic"] = NCU_TRAFFIC.get(name)
     rec["roofline"] = roof
     rec["clocks"] = clk.summary()
+    # strong scaling: this rank's shard of the SAME resident configuration (rows, problems, N columns, KV groups), timed
+    # against the whole configuration in alternating blocks, so that both are timed at the same clocks and temperature
+    # (one after the other, whichever ran second found the GPU hotter, or cooler after an oracle check, by 10 %)
+    if name == "gemm_f32_512" and ctx.world > 1:
+        rec["strong"] = {"note": "replicas only: 8 output tiles are too few to split; every GPU runs the same 512^3 problem"}
+    elif ctx.world > 1 and not reduced and not isinstance(wl, (RowOpWL, DecodeWL)):
+        sh = ctx.pkg.launcher.shard_range(wl.strong_units(), ctx.world, ctx.rank)
+        if name.startswith("gemm_") and wl.single:
+            sh = ctx.pkg.launcher.gemm_job(wl.code, wl.m, wl.n, wl.k, 0, 0, 0).plan(ctx.world, ctx.rank)
+        fn = (lambda: wl.step_range(sh.first, sh.count)) if sh.count else (lambda: None)
+        w_ms, s_ms = time_alternating(ctx, wl.step, fn, steps, 3)
+        strong = {"value": round(wl.work() / (s_ms * 1e-3) / scale, 2), "unit": unit, "ms_per_step": round(s_ms, 4),
+                  "one_gpu_ms_per_step": round(w_ms, 4), "speedup_vs_one_gpu": round(w_ms / s_ms, 3),
+                  "split": wl.strong_unit or wl.unit_name, "this_rank": [int(sh.first), int(sh.count)], "of": int(wl.strong_units()),
+                  "note": "blocks of 5 whole-configuration steps and of 5 shard steps alternate (same clocks and temperature "
+                          "for both); every GPU carries the whole configuration in the former, its shard in the latter"}
+        rec["strong"] = strong
+
     if wl.bound != "hbm" and args.sustained_seconds > 0 and not reduced:
         rec["sustained"] = sustained_run(ctx, wl, args.sustained_seconds, peaks, ctx.local)
         wl.step()
@@ -890,29 +938,16 @@ def measure(ctx, name, args, peaks, steps, warmup, headline=False, shared=None, 
         rec["verify"] = v
         assert v["ok"], f"{name}: verification against the CPU oracle failed: {v}"
 
-    # strong scaling: this rank's shard of the SAME resident configuration (rows, problems, N columns, KV groups)
-    if name == "gemm_f32_512" and ctx.world > 1:
-        rec["strong"] = {"note": "replicas only: 8 output tiles are too few to split; every GPU runs the same 512^3 problem"}
-    elif ctx.world > 1 and not reduced and not isinstance(wl, (RowOpWL, DecodeWL)):
-        sh = ctx.pkg.launcher.shard_range(wl.strong_units(), ctx.world, ctx.rank)
-        if name.startswith("gemm_") and wl.single:
-            sh = ctx.pkg.launcher.gemm_job(wl.code, wl.m, wl.n, wl.k, 0, 0, 0).plan(ctx.world, ctx.rank)
-        fn = (lambda: wl.step_range(sh.first, sh.count)) if sh.count else (lambda: None)
-        s_total, s_per = time_steps(ctx, fn, steps, 3)
-        s_ms = s_total / steps
-        strong = {"value": round(wl.work() / (s_ms * 1e-3) / scale, 2), "unit": unit, "ms_per_step": round(s_ms, 4),
-                  "speedup_vs_one_gpu": round(ms / s_ms, 3), "split": wl.strong_unit or wl.unit_name,
-                  "this_rank": [int(sh.first), int(sh.count)], "of": int(wl.strong_units()),
-                  "note": "the one-GPU time is this run's own weak-scaling step (every GPU carries the whole configuration)"}
-        if hasattr(wl, "verify_strong") and not args.no_verify:
-            vs = wl.verify_strong(ctx.oracle, sh.first, sh.count) if sh.count else None
-            if vs is not None:
-                vs["ok"] = all_ranks_ok(ctx, vs["ok"])
-                strong["verify"] = vs
-                assert vs["ok"], f"{name}: the column block of rank {ctx.rank} does not match the oracle: {vs}"
-            else:
-                all_ranks_ok(ctx, True)
-        rec["strong"] = strong
+    if "strong" in rec and "value" in rec["strong"] and hasattr(wl, "verify_strong") and not args.no_verify:
+        strong = rec["strong"]
+        sh_first, sh_count = strong["this_rank"]
+        vs = wl.verify_strong(ctx.oracle, sh_first, sh_count) if sh_count else None
+        if vs is not None:
+            vs["ok"] = all_ranks_ok(ctx, vs["ok"])
+            strong["verify"] = vs
+            assert vs["ok"], f"{name}: the column block of rank {ctx.rank} does not match the oracle: {vs}"
+        else:
+            all_ranks_ok(ctx, True)
 
     # end to end through the host-buffer C-ABI call (pinned host memory, copies inside the timed region)
     if hasattr(wl, "e2e_prepare") and not args.no_e2e and not reduced:
