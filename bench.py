@@ -15,8 +15,9 @@ Inputs are generated once on the host (counter-based generator of the library, t
 laws of each configuration), uploaded, and read by the oracle from the same host buffers.
 Under torchrun (N > 1) every rank carries the one-GPU configuration (weak scaling, the
 reported value) and then its shard of that configuration (strong scaling: rows, batches,
-N-column blocks, KV groups); there is no collective on the data path.  Times are CUDA-event
-times on the launching stream, maximum over ranks.
+N-column blocks, KV groups), the two in alternating blocks of steps for the strong-scaling
+ratio; there is no collective on the data path.  Times are CUDA-event times on the launching
+stream, maximum over ranks.
 
 --impl reference times the CPU restatement of the reference's linalg semantics (the
 oracle) on all host cores for the same configurations, each step a bounded sample.
