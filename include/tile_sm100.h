@@ -335,7 +335,11 @@ int32_t tsm100_attention_decode(tsm100_device_t dev, const tsm100_attention_deco
 /* The path a tile_hal host program takes per kernel: alloc_from_slice ->
  * launch -> copy_to_host (crates/tile_hal/src/cuda.rs:348-371, :245-288,
  * :190-199), here chunked through page-locked staging so that copies in both
- * directions overlap the kernel.  Pointers are ordinary host memory. */
+ * directions overlap the kernel.  Pointers are ordinary host memory.
+ * tsm100_gemm_host keeps B resident and streams A and C in row blocks, each a
+ * launch of its own: a 16-bit result may differ from tsm100_gemm on the whole
+ * problem by one rounding of the stored type in a few elements (the f32 sums
+ * are taken in another order); f32 results do not differ. */
 int32_t tsm100_softmax_host(tsm100_device_t dev, const tsm100_softmax_desc* desc, const void* x,
                             void* y);
 int32_t tsm100_gemm_host(tsm100_device_t dev, const tsm100_gemm_desc* desc, const void* a,
